@@ -1,0 +1,209 @@
+/* C ABI of libxfb200: attention forward (prefill, split-K decode, LSE merge)
+ * for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only.  All tensor pointers are DEVICE pointers
+ * unless a field says "host".  Strides are in ELEMENTS of the tensor's dtype.
+ * Every launch goes to the stream passed by the caller (a cudaStream_t cast to
+ * void*), performs no host synchronisation and reads sequence lengths, sequence
+ * starts and page tables from device memory when the kernel runs, so a
+ * captured CUDA graph may be replayed after those arrays were updated in place
+ * (contract of the reference's callers: examples/llama_inference/generate.py:144-187).
+ *
+ * Return value: 0 on success, a negative XFB200_E_* code otherwise;
+ * xfb200_last_error() then returns a message for the calling thread.
+ *
+ * The entry points replace, for this path, what the reference binds as torch
+ * operators.  Its own NVIDIA kernels sit in the un-vendored `mslk` package;
+ * the in-tree statement of the same boundary is the schema
+ *   efficient_attention_forward_ck(query, key, value, attn_bias, seqstart_q,
+ *       seqstart_k, max_seqlen_q, dropout_p, compute_logsumexp,
+ *       custom_mask_type, scale, seqlen_k, window_size, block_tables, page_size)
+ * (xformers/csrc/attention/attention.cpp:12-16) and
+ *   efficient_attention_forward_decoder_splitk_ck
+ * (xformers/csrc/attention/hip_decoder/attention_forward_splitk.cpp:94-248).
+ */
+#ifndef XFB200_H_
+#define XFB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define XFB200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define XFB200_API __attribute__((visibility("default")))
+#else
+#define XFB200_API
+#endif
+
+enum {
+  XFB200_OK = 0,
+  XFB200_E_INVALID = -1,     /* argument rejected by host-side validation */
+  XFB200_E_UNSUPPORTED = -2, /* valid but no kernel covers it            */
+  XFB200_E_CUDA = -3,        /* a CUDA runtime / driver call failed       */
+  XFB200_E_DEVICE = -4       /* a kernel reported a timed-out wait        */
+};
+
+enum { XFB200_BF16 = 0, XFB200_F16 = 1, XFB200_F32 = 2 };
+
+/* custom_mask_type of the reference boundary (attention.cpp:12-16):
+ * 0 none, 1 causal aligned top-left, 2 causal aligned bottom-right. */
+enum { XFB200_MASK_NONE = 0, XFB200_MASK_CAUSAL_TOP_LEFT = 1, XFB200_MASK_CAUSAL_BOTTOM_RIGHT = 2 };
+
+enum { XFB200_KV_PLAIN = 0, XFB200_KV_INT4_ROWWISE = 1 };
+
+/* [B, M, G, H, D] view of a tensor; a 4-D BMHK tensor has G = 1.  The head
+ * stride of K/V may be 0 (MQA/GQA: one KV head broadcast over H query heads);
+ * K/V are never expanded. */
+typedef struct {
+  int64_t b, m, g, h; /* last dim has stride 1 */
+} xfb200_strides;
+
+/* ---- prefill ----------------------------------------------------------------
+ * O = softmax(Q K^T * scale + mask) V with optional LSE (natural log, fp32).
+ * Replaces: fmha.memory_efficient_attention_forward / _forward_requires_grad
+ * with a prefill operator (xformers/ops/fmha/__init__.py:40-42), schema as in
+ * xformers/csrc/attention/attention.cpp:12-16.
+ *
+ * Dense mode  : seqstart_q == NULL; q [batch, mq, G, H, D], k/v [batch, mkv, G, H|1, D].
+ * Varlen mode : seqstart_q/seqstart_k int32 [batch+1] on device, tensors carry
+ *               batch 1 with sequences concatenated ("1MHK mode",
+ *               hip_fmha/attention_forward_generic_ck_tiled.cpp:45-63); mq is the
+ *               static bound max_seqlen_q used to size the grid.  If seqlen_k
+ *               (int32 [batch]) is given, sequence b uses keys
+ *               [seqstart_k[b], seqstart_k[b] + seqlen_k[b]) (padded keys).
+ * kv_offset   : global index of this call's first key for the causal test;
+ *               non-zero when the key axis is sharded across devices.
+ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse; /* NULL: not written.  [batch, G, H, lse_stride_h>=mq] dense; varlen: [G, H, total_q] */
+  const int32_t* seqstart_q;
+  const int32_t* seqstart_k;
+  const int32_t* seqlen_k;
+  int32_t dtype; /* XFB200_BF16 | XFB200_F16 for q, k, v, out */
+  int32_t batch;
+  int32_t mq;
+  int32_t mkv;     /* dense: keys per batch; varlen: total key rows in the tensor */
+  int32_t total_q; /* rows in q/out along dim 1 */
+  int32_t groups;
+  int32_t heads_per_group;
+  int32_t head_dim;
+  xfb200_strides q_strides, k_strides, v_strides, o_strides;
+  int64_t lse_stride_b, lse_stride_g, lse_stride_h;
+  int32_t mask_type;
+  int32_t kv_offset;
+  int32_t window_left; /* < 0: no window; else keys j >= i + shift - window_left */
+  float scale;
+  int32_t out_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
+  int32_t reserved;
+} xfb200_prefill_params;
+
+XFB200_API int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream);
+
+/* ---- split-K decode -----------------------------------------------------------
+ * Few queries per sequence against a long KV cache that is padded
+ * (sequence b at rows [b*kv_padding, b*kv_padding+seqlen_k[b])) or paged
+ * (logical token t of sequence b at physical row
+ *  block_tables[b*block_table_stride + t/page_size]*page_size + t%page_size),
+ * in bf16/f16 or in the int4 row-wise format (one row = num_quant_groups int32
+ * {scale: low fp16, shift: high fp16} followed by head_dim/8 int32 of nibbles,
+ * element e of a word at bits [4e,4e+4)).
+ * Replaces: fmha.triton_splitk.FwOp (xformers/ops/fmha/triton_splitk.py:18-27);
+ * two-kernel structure as hip_decoder/attention_forward_splitk.cpp:58-89.
+ *
+ * q   [1, batch*mq, kv_heads, q_per_kv, D]   (strides m, g, h)
+ * k,v [1, rows,     kv_heads, (1), D or words] (strides m, g)
+ * out like q.  The key range of every sequence is cut into split_k chunks of
+ * chunk_tokens(kv bound, split_k) tokens; partials go to the caller-provided
+ * scratch (see xfb200_decode_scratch_bytes) and a second kernel merges them.
+ */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;         /* NULL or [kv_heads, q_per_kv, batch*mq] */
+  void* scratch;      /* xfb200_decode_scratch_bytes() bytes, 256-B aligned */
+  const int32_t* seqlen_k;     /* [batch]; NULL: every sequence has kv_padding keys */
+  const int32_t* block_tables; /* NULL: padded cache */
+  int32_t dtype;     /* of q and out (and of k/v when kv_format == PLAIN) */
+  int32_t kv_format; /* XFB200_KV_PLAIN | XFB200_KV_INT4_ROWWISE */
+  int32_t num_quant_groups;
+  int32_t batch;
+  int32_t mq; /* queries per sequence (uniform) */
+  int32_t kv_heads;
+  int32_t q_per_kv;
+  int32_t head_dim;
+  int32_t kv_padding; /* padded: slot size; paged: block_table_stride*page_size */
+  int32_t page_size;
+  int32_t block_table_stride;
+  int32_t split_k;
+  int64_t q_stride_m, q_stride_g, q_stride_h;
+  int64_t k_stride_m, k_stride_g;
+  int64_t v_stride_m, v_stride_g;
+  int64_t o_stride_m, o_stride_g, o_stride_h;
+  int64_t lse_stride_g, lse_stride_h;
+  int32_t mask_type; /* NONE or CAUSAL_BOTTOM_RIGHT (w.r.t. seqlen_k[b]) */
+  float scale;
+  int32_t out_dtype;
+  int32_t reserved;
+} xfb200_decode_params;
+
+XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t kv_heads, int32_t q_per_kv, int32_t head_dim,
+                                   int32_t split_k);
+XFB200_API int xfb200_decode_forward(const xfb200_decode_params* p, void* stream);
+
+/* ---- merge ---------------------------------------------------------------------
+ * m = max_s lse_s; w_s = exp(lse_s - m); out = sum w_s O_s / sum w_s;
+ * lse = m + log sum w_s.  A partial with lse = -inf has weight 0.
+ * Replaces: fmha.merge_attentions (xformers/ops/fmha/__init__.py:49,
+ * xformers/ops/fmha/triton_splitk.py:29-33); arithmetic as
+ * tests/test_fmha_merge_attentions.py:513-538.
+ *
+ * attn[s] [B, M, G, H, D] (strides b, m, g, h), lse[s] [B, G, H, M] (strides b, g, h; m has stride 1).
+ * Either num_splits pointers in attn_ptrs/lse_ptrs (HOST arrays, <= XFB200_MERGE_MAX_PTRS),
+ * or attn_ptrs[0]/lse_ptrs[0] plus split strides for a stacked tensor.
+ */
+#define XFB200_MERGE_MAX_PTRS 32
+typedef struct {
+  const void* const* attn_ptrs; /* host array */
+  const float* const* lse_ptrs; /* host array */
+  int32_t num_splits;
+  int32_t stacked; /* 1: use pointer 0 and attn_stride_s / lse_stride_s */
+  int64_t attn_stride_s, lse_stride_s;
+  xfb200_strides attn_strides;
+  int64_t lse_in_stride_b, lse_in_stride_g, lse_in_stride_h;
+  void* out;
+  float* lse_out; /* NULL: not written */
+  xfb200_strides out_strides;
+  int64_t lse_out_stride_b, lse_out_stride_g, lse_out_stride_h;
+  int32_t B, M, G, H, D;
+  int32_t in_dtype;  /* XFB200_F32 | XFB200_BF16 | XFB200_F16 */
+  int32_t out_dtype; /* same set */
+  int32_t reserved;
+} xfb200_merge_params;
+
+XFB200_API int xfb200_merge_attentions(const xfb200_merge_params* p, void* stream);
+
+/* ---- misc ---------------------------------------------------------------------- */
+XFB200_API int xfb200_abi_version(void);
+XFB200_API const char* xfb200_last_error(void);
+/* Device-side status word of the last prefill launch on the current device
+ * (0 = no timed-out wait).  Synchronises the given stream. */
+XFB200_API int xfb200_prefill_device_status(void* stream, int32_t* status_out);
+/* Testing knob: 0 = choose automatically, 1 = always the mma.sync kernel,
+ * 2 = fail unless the tcgen05 kernel covers the input. */
+XFB200_API int xfb200_debug_set_prefill_path(int path);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XFB200_H_ */

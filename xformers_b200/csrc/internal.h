@@ -1,0 +1,43 @@
+// Host-side helpers shared by the translation units of libxfb200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/xfb200.h"
+
+namespace xfb {
+
+// Per-thread message for xfb200_last_error().
+char* error_buffer();
+constexpr size_t kErrorBufferSize = 512;
+
+inline int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(error_buffer(), kErrorBufferSize, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(XFB200_E_CUDA, "%s: launch failed: %s", what, cudaGetErrorString(e));
+  return XFB200_OK;
+}
+
+inline int cuda_fail(const char* what, cudaError_t e) {
+  return set_error(XFB200_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// Entry points implemented in other translation units.
+int prefill_sm100_supported(const xfb200_prefill_params* p);
+int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream);
+int prefill_generic_launch(const xfb200_prefill_params* p, cudaStream_t stream);
+
+}  // namespace xfb

@@ -1,0 +1,26 @@
+// Error reporting and device queries shared by all entry points.
+#include "internal.h"
+
+namespace xfb {
+
+char* error_buffer() {
+  static thread_local char buf[kErrorBufferSize] = {0};
+  return buf;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace xfb
+
+extern "C" int xfb200_abi_version(void) { return XFB200_ABI_VERSION; }
+extern "C" const char* xfb200_last_error(void) { return xfb::error_buffer(); }

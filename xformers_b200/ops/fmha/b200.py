@@ -1,0 +1,215 @@
+"""Prefill attention-forward operator for B200 (``fmha.b200.FwOp``).
+
+Slots into the dispatcher next to the reference's forward operators
+(``fmha.cutlass_blackwell.FwOp``, ``fmha.flash.FwOp``; registration record as
+tests/test_mem_eff_attention.py:104-111 reads it).  The arithmetic is done by
+``xfb200_prefill_forward`` of libxfb200.so: a TMA + tcgen05/TMEM kernel for
+head dims 64 and 128, an mma.sync kernel for the other head dims.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any, List, Optional, Tuple
+
+import torch
+
+from ... import _lib
+from .attn_bias import (
+    BlockDiagonalCausalFromBottomRightMask,
+    BlockDiagonalCausalLocalAttentionFromBottomRightMask,
+    BlockDiagonalCausalLocalAttentionMask,
+    BlockDiagonalCausalMask,
+    BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    BlockDiagonalMask,
+    BlockDiagonalPaddedKeysMask,
+    LowerTriangularFromBottomRightMask,
+    LowerTriangularMask,
+    LowerTriangularMaskLocalAttention,
+)
+from .common import AttentionFwOpBase, Context, Inputs, check_lastdim_alignment_stride1
+
+_DTYPE_CODE = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
+
+
+def _strides4(t: torch.Tensor) -> _lib.Strides:
+    """(b, m, g, h) element strides of a 5-D BMGHK tensor."""
+    return _lib.Strides(t.stride(0), t.stride(1), t.stride(2), t.stride(3))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _mask_of(bias: Any) -> Tuple[int, int]:
+    """(mask_type, window_left) of a bias object."""
+    if bias is None or type(bias) in (BlockDiagonalMask, BlockDiagonalPaddedKeysMask):
+        return _lib.MASK_NONE, -1
+    if type(bias) in (LowerTriangularMask, BlockDiagonalCausalMask):
+        return _lib.MASK_CAUSAL_TOP_LEFT, -1
+    if type(bias) in (
+        LowerTriangularFromBottomRightMask,
+        BlockDiagonalCausalFromBottomRightMask,
+        BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    ):
+        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, -1
+    if type(bias) in (LowerTriangularMaskLocalAttention, BlockDiagonalCausalLocalAttentionMask):
+        return _lib.MASK_CAUSAL_TOP_LEFT, bias._window_size - 1
+    if type(bias) is BlockDiagonalCausalLocalAttentionFromBottomRightMask:
+        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, bias._window_size - 1
+    raise NotImplementedError(f"bias {type(bias)}")
+
+
+class FwOp(AttentionFwOpBase):
+    """softmax(Q K^T * scale + mask) V on sm_100a, with optional LSE."""
+
+    OPERATOR = _lib.load().xfb200_prefill_forward if _lib.is_built() else None
+    NAME = "b200F"
+    SUPPORTED_DTYPES = {torch.bfloat16, torch.half}
+    SUPPORTED_MAX_K = 256
+    SUPPORTED_MIN_K = 8
+    SUPPORTED_ATTN_BIAS_TYPES = (
+        type(None),
+        LowerTriangularMask,
+        LowerTriangularFromBottomRightMask,
+        LowerTriangularMaskLocalAttention,
+        BlockDiagonalMask,
+        BlockDiagonalCausalMask,
+        BlockDiagonalCausalFromBottomRightMask,
+        BlockDiagonalCausalLocalAttentionMask,
+        BlockDiagonalCausalLocalAttentionFromBottomRightMask,
+        BlockDiagonalPaddedKeysMask,
+        BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    )
+    SUPPORTS_DROPOUT = False
+    SUPPORTS_CUSTOM_SCALE = True
+    SUPPORTS_DIFFERENT_VALUE_EMBED = False
+    SUPPORTS_OUTPUT_DTYPE = True
+    SUPPORTS_PARTIAL = True
+    SUPPORTS_BMGHK = True
+    VARLEN_LSE_PACKED = True
+    _TEST_K = [32, 64, 128, 256]
+    # 0 = automatic; 1 = force the mma.sync kernel; 2 = require the tcgen05 kernel
+    KERNEL_PATH = 0
+
+    @classmethod
+    def shape_not_supported_reasons(cls, Mq: int, Mkv: int, K: int, Kv: int) -> List[str]:
+        reasons = super().shape_not_supported_reasons(Mq, Mkv, K, Kv)
+        if K % 8 != 0:
+            reasons.append(f"query.shape[-1] = {K} is not a multiple of 8")
+        return reasons
+
+    @classmethod
+    def not_supported_reasons(cls, d: Inputs) -> List[str]:
+        reasons = super().not_supported_reasons(d)
+        if d.key.dtype == torch.int32:
+            reasons.append("quantised K/V caches are read by the split-K decode operator only")
+            return reasons
+        check_lastdim_alignment_stride1(reasons, "query", d.query, 8)
+        check_lastdim_alignment_stride1(reasons, "key", d.key, 8)
+        check_lastdim_alignment_stride1(reasons, "value", d.value, 8)
+        for name, t in (("query", d.query), ("key", d.key), ("value", d.value)):
+            if t.numel() and any(s % 8 for s in t.stride()[:-1]):
+                reasons.append(f"{name}: every stride but the last must be a multiple of 8 elements, got {t.stride()}")
+            if t.numel() and t.data_ptr() % 16:
+                reasons.append(f"{name} is not 16-byte aligned")
+        if d.scale is not None and not d.scale > 0:
+            pass  # handled by the mma.sync kernel
+        if d.output_dtype is not None and d.output_dtype not in _DTYPE_CODE:
+            reasons.append(f"output_dtype={d.output_dtype}")
+        if isinstance(d.attn_bias, torch.Tensor):
+            reasons.append("additive tensor biases are not supported")
+        return reasons
+
+    @classmethod
+    def apply(cls, inp: Inputs, needs_gradient: bool) -> Tuple[torch.Tensor, Optional[Context]]:
+        return cls._apply(inp, needs_gradient or inp.is_partial, kv_offset=0)
+
+    @classmethod
+    def _apply(cls, inp: Inputs, want_lse: bool, kv_offset: int = 0) -> Tuple[torch.Tensor, Optional[Context]]:
+        if cls.OPERATOR is None:
+            raise RuntimeError("libxfb200.so is not built; there is no fallback")
+        q, k, v = inp.get_qkv_in_bmghk()
+        if q.device.type != "cuda":
+            raise ValueError("b200.FwOp runs on CUDA tensors only")
+        B, Mq, G, H, D = q.shape
+        Mkv = k.shape[1]
+        out_dtype = inp.output_dtype or q.dtype
+        out = torch.empty((B, Mq, G, H, D), dtype=out_dtype, device=q.device)
+        bias = inp.attn_bias
+        varlen = isinstance(bias, (BlockDiagonalMask, BlockDiagonalPaddedKeysMask))
+        lse = torch.empty((B, G, H, Mq), dtype=torch.float32, device=q.device) if want_lse else None
+
+        if out.numel() > 0:
+            if Mkv == 0:
+                out.zero_()
+                if lse is not None:
+                    lse.fill_(float("-inf"))
+            else:
+                mask_type, window_left = _mask_of(bias)
+                p = _lib.PrefillParams()
+                p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
+                p.lse = _ptr(lse)
+                p.dtype = _DTYPE_CODE[q.dtype]
+                p.out_dtype = _DTYPE_CODE[out_dtype]
+                if varlen:
+                    qi, ki = bias.q_seqinfo, bias.k_seqinfo
+                    p.seqstart_q = qi.seqstart.data_ptr()
+                    p.seqstart_k = ki.seqstart.data_ptr()
+                    p.seqlen_k = ki.seqlen.data_ptr() if isinstance(bias, BlockDiagonalPaddedKeysMask) else None
+                    p.batch = len(qi.seqstart_py) - 1
+                    p.mq = max(qi.max_seqlen, 0)
+                else:
+                    p.batch, p.mq = B, Mq
+                p.mkv, p.total_q = Mkv, Mq
+                p.groups, p.heads_per_group, p.head_dim = G, H, D
+                p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides4(q), _strides4(k), _strides4(v), _strides4(out)
+                if lse is not None:
+                    p.lse_stride_b, p.lse_stride_g, p.lse_stride_h = lse.stride(0), lse.stride(1), lse.stride(2)
+                p.mask_type, p.kv_offset, p.window_left = mask_type, kv_offset, window_left
+                p.scale = inp.scale_float
+                lib = _lib.load()
+                if cls.KERNEL_PATH:
+                    lib.xfb200_debug_set_prefill_path(cls.KERNEL_PATH)
+                try:
+                    rc = lib.xfb200_prefill_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
+                finally:
+                    if cls.KERNEL_PATH:
+                        lib.xfb200_debug_set_prefill_path(0)
+                _lib.check(rc, "b200.FwOp")
+
+        if inp.query.ndim == 4:
+            out = out[:, :, 0]
+            lse = lse[:, 0] if lse is not None else None
+        elif inp.query.ndim == 3:
+            out = out[:, :, 0, 0]
+            lse = lse[:, 0, 0] if lse is not None else None
+        ctx = Context(out=out, lse=lse) if lse is not None else None
+        return out, ctx
+
+
+class FwOp_Generic(FwOp):
+    """Same operator pinned to the mma.sync kernel (tests, comparisons)."""
+
+    NAME = "b200F-mma"
+    KERNEL_PATH = 1
+
+
+class FwOp_Tcgen05(FwOp):
+    """Same operator, failing unless the tcgen05 kernel covers the input."""
+
+    NAME = "b200F-tc5"
+    KERNEL_PATH = 2
+    SUPPORTED_MAX_K = 128
+    _TEST_K = [64, 128]
+
+
+def prefill_device_status(device=None) -> int:
+    """Status word of the tcgen05 kernel on ``device`` (0 = every wait was
+    satisfied).  Synchronises the current stream; meant for tests."""
+    dev = torch.device("cuda" if device is None else device)
+    with torch.cuda.device(dev):
+        st = C.c_int32(0)
+        rc = _lib.load().xfb200_prefill_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st))
+        _lib.check(rc, "prefill_device_status")
+    return st.value
