@@ -1,0 +1,425 @@
+#!/usr/bin/env python
+"""Benchmark of the attention-forward hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one
+batch of synthetic input:
+
+* headline (`value`): forward attention TFLOP/s of the causal prefill
+  configuration B=4, Mq=Mkv=4096, Hq=Hkv=32, D=128, bf16 (FLOP convention of
+  the reference: 4*Mq*Mkv*D per head, halved for causal).  With N > 1 every
+  rank runs the same configuration on its own batch shard (batch x head work is
+  sharded without communication: weak scaling).
+* `e2e`: the same metric through the public API with HOST (pinned) q/k/v and a
+  host copy of the output inside the timed region.
+* `roofline`: tensor-pipe roofline of the prefill kernel against the measured
+  cuBLAS bf16 peak of this pool (MEASURED_PEAKS.json), `decode_bf16` /
+  `decode_int4`: KV-read GB/s of the split-K decode configuration (64
+  sequences, lengths U[1024,32768], paged 256, Hq=64/Hkv=8) with their HBM
+  rooflines, `varlen_gqa`: the packed varlen GQA prefill configuration,
+  `long_context`: one 131072-token causal sequence with the key axis sharded
+  over the N ranks (NCCL all-gather of partials + LSE merge).
+* `cpu_baseline`: the CPU oracle timed on a bounded slice of the headline
+  configuration on this box's host cores (a reported baseline only).
+
+`--impl reference` times the reference algorithm's CPU restatement (the oracle;
+the reference's own kernels live in the un-vendored `mslk` package) on the same
+slice, on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "fwd attn TFLOP/s (prefill) & KV-read GB/s (split-K decode), 1-8 B200"
+UNIT = "TFLOP/s"
+WORKLOAD = "causal prefill B=4 Mq=Mkv=4096 Hq=Hkv=32 D=128 bf16 BMHK LowerTriangularMask"
+CFG2 = dict(B=4, M=4096, H=32, D=128)
+CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
+
+
+def causal_flops(B, M, H, D):
+    return 4.0 * M * M * D * B * H / 2.0
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p["bf16_tflops"]),
+                    bf16_tflops_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed regions."""
+
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.samples = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, windows):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        mhz, mx, reasons = [], None, set()
+        for t, line in self.samples:
+            if not any(a <= t <= b for a, b in windows):
+                continue
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                mhz.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(mhz)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm (reference algorithm restated by the oracle)
+# ---------------------------------------------------------------------------
+def cpu_sample_inputs():
+    g = torch.Generator().manual_seed(0)
+    B, H, M, D = CPU_SAMPLE["B"], CPU_SAMPLE["H"], CFG2["M"], CFG2["D"]
+    q, k, v = (torch.randn(B, M, H, D, generator=g).bfloat16().float() for _ in range(3))
+    return q, k, v
+
+
+def cpu_step(q, k, v):
+    import oracle
+    from xformers_b200.ops.fmha.attn_bias import LowerTriangularMask
+
+    return oracle.ref_attention_with_lse(q, k, v, LowerTriangularMask())
+
+
+def time_cpu(budget_s: float, max_reps: int, warmup: int = 1):
+    q, k, v = cpu_sample_inputs()
+    for _ in range(warmup):
+        cpu_step(q, k, v)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_reps and (time.perf_counter() - t_start < budget_s or len(times) < 3):
+        t0 = time.perf_counter()
+        cpu_step(q, k, v)
+        times.append(time.perf_counter() - t0)
+    flops = causal_flops(CPU_SAMPLE["B"], CFG2["M"], CPU_SAMPLE["H"], CFG2["D"])
+    return flops, times
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    q, k, v = cpu_sample_inputs()
+    for _ in range(max(args.warmup, 1)):
+        cpu_step(q, k, v)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(q, k, v)
+    dt = time.perf_counter() - t0
+    flops = causal_flops(CPU_SAMPLE["B"], CFG2["M"], CPU_SAMPLE["H"], CFG2["D"])
+    val = flops * args.steps / dt / 1e12
+    sample = f"B={CPU_SAMPLE['B']} x H={CPU_SAMPLE['H']} heads of the headline configuration per step (fp32 dense softmax(QK^T)V with LSE)"
+    line = {
+        "impl": "reference",
+        "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference attention (oracle); mslk, which holds the reference kernels, is not installable offline"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def event_time_ms(fn, steps, warmup, barrier=None):
+    for _ in range(warmup):
+        fn()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    if barrier is not None:
+        barrier()
+    return e0.elapsed_time(e1), (t0, t1)
+
+
+def gpu_quantize_int4(x):
+    """Device-side restatement of the int4 row quantiser, used only to prepare
+    synthetic caches (benchmarks/benchmark_attn_decoding.py:38-72)."""
+    xf = x.float()
+    mx, mn = xf.max(-1, keepdim=True).values, xf.min(-1, keepdim=True).values
+    scale = ((mx - mn) / 15).half()
+    shift = mn.half()
+    qv = ((xf - shift.float()) / scale.float() + 0.5).to(torch.uint8) & 0xF
+    packed = qv[..., ::2] + (qv[..., 1::2] << 4)
+    ss = torch.cat([scale.view(torch.uint8), shift.view(torch.uint8)], dim=-1)
+    return torch.cat([ss, packed], dim=-1).contiguous().view(torch.int32)
+
+
+def decode_workload(dev, quant: bool, seed: int = 0):
+    from xformers_b200.ops.fmha import attn_bias as ab
+
+    g = torch.Generator().manual_seed(seed)
+    B, page, Hkv, G, D = 64, 256, 8, 8, 128
+    lens = torch.randint(1024, 32769, (B,), generator=g)
+    pages = (lens + page - 1) // page
+    pool = int(pages.sum())
+    max_pages = 32768 // page
+    perm = torch.randperm(pool, generator=g).int()
+    table = torch.zeros(B, max_pages, dtype=torch.int32)
+    s = 0
+    for b in range(B):
+        n = int(pages[b])
+        table[b, :n] = perm[s : s + n]
+        s += n
+    gd = torch.Generator(device=dev).manual_seed(seed)
+    q = torch.randn(1, B, Hkv, G, D, generator=gd, device=dev, dtype=torch.bfloat16)
+    shape = (1, pool * page, Hkv, 1, D)
+    k = torch.randn(shape, generator=gd, device=dev, dtype=torch.bfloat16)
+    v = torch.randn(shape, generator=gd, device=dev, dtype=torch.bfloat16)
+    if quant:
+        kq = torch.empty(shape[:-1] + (D // 8 + 1,), dtype=torch.int32, device=dev)
+        vq = torch.empty_like(kq)
+        step = 64 * page
+        for lo in range(0, pool * page, step):
+            kq[:, lo : lo + step] = gpu_quantize_int4(k[:, lo : lo + step])
+            vq[:, lo : lo + step] = gpu_quantize_int4(v[:, lo : lo + step])
+        k, v = kq, vq
+        row_bytes = (D // 8 + 1) * 4
+    else:
+        row_bytes = D * 2
+    k = k.expand(-1, -1, -1, G, -1)
+    v = v.expand(-1, -1, -1, G, -1)
+    bias = ab.PagedBlockDiagonalPaddedKeysMask.from_seqlens([1] * B, lens.tolist(), table.to(dev), page)
+    kv_bytes = float(lens.sum()) * Hkv * 2 * row_bytes
+    qo_bytes = 2.0 * B * Hkv * G * D * 2
+    return q, k, v, bias, kv_bytes + qo_bytes + table.numel() * 4
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-extras", action="store_true", help="headline only (no decode / varlen / long-context / CPU legs)")
+    ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,varlen,long,cpu")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch.distributed as dist
+
+    import xformers_b200.ops as xops
+    from xformers_b200.ops import fmha
+    from xformers_b200.ops.fmha import attn_bias as ab
+    from xformers_b200.ops.fmha.sharded import shard_bounds, sharded_kv_attention_forward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the operators")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "varlen", "long", "cpu"}
+    if args.skip_extras:
+        legs &= {"prefill", "e2e"}
+    peaks = load_peaks()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    windows = []
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out_line = {
+        "metric": METRIC, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "per_gpu_batch": CFG2["B"], "l2": "inputs (512 MiB per step) exceed the 126 MB L2",
+                   "parallelism": f"batch-sharded x{world}, no communication", "peaks": peaks["source"]},
+    }
+
+    # ------------------------------------------------------------- headline
+    B, M, H, D = CFG2["B"], CFG2["M"], CFG2["H"], CFG2["D"]
+    gd = torch.Generator(device=dev).manual_seed(rank)
+    q, k, v = (torch.randn(B, M, H, D, generator=gd, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    causal = ab.LowerTriangularMask()
+    flops = causal_flops(B, M, H, D)
+    launches = 0
+    if "prefill" in legs:
+        fn = lambda: xops.memory_efficient_attention_forward(q, k, v, causal, op=fmha.b200.FwOp)
+        ms, win = event_time_ms(fn, args.steps, args.warmup, barrier)
+        windows.append(win)
+        ms = max_over_ranks(ms)
+        status = fmha.b200.prefill_device_status()
+        per_step = ms / args.steps
+        tfs = flops / (per_step * 1e-3) / 1e12
+        launches = args.steps
+        out_line.update({"value": tfs * world, "ms_per_step": per_step, "gpu_launches": launches})
+        out_line["roofline"] = {"bound": "tensor", "achieved": tfs, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                                "frac": tfs / peaks["bf16_tflops"], "traffic": None, "kernel": "prefill_sm100_kernel<128,bf16>",
+                                "of": peaks["source"], "frac_of_nominal_2250": tfs / 2250.0, "device_status": status}
+    # ------------------------------------------------------------------ e2e
+    if "e2e" in legs:
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        ho = torch.empty((B, M, H, D), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+            o = xops.memory_efficient_attention_forward(dq, dk, dv, causal)
+            ho.copy_(o, non_blocking=True)
+
+        e_steps = max(3, min(args.steps, 20))
+        ms, win = event_time_ms(e2e_step, e_steps, 3, barrier)
+        windows.append(win)
+        ms = max_over_ranks(ms)
+        nbytes = q.numel() * 2
+        out_line["e2e"] = {"value": world * flops / (ms / e_steps * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes,
+                           "d2h_bytes_per_step": nbytes, "ms_per_step": ms / e_steps, "steps": e_steps}
+        del hq, hk, hv, ho
+    del q, k, v
+    torch.cuda.empty_cache()
+
+    # --------------------------------------------------- decode (rank 0 only)
+    for name, quant in (("decode_bf16", False), ("decode_int4", True)):
+        if name in legs and rank == 0:
+            dq, dk, dv, dbias, nbytes = decode_workload(dev, quant)
+            fn = lambda: xops.memory_efficient_attention_forward(dq, dk, dv, dbias, op=fmha.b200_splitk.FwOp)
+            d_steps = max(5, min(args.steps, 30))
+            ms, win = event_time_ms(fn, d_steps, 3)
+            windows.append(win)
+            gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
+            split = fmha.b200_splitk.FwOp.get_split_k(64, 32768, 8, 68 if quant else 256)
+            out_line[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes, "split_k": split,
+                              "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                           "frac": gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"]},
+                              "workload": "64 seqs, kv len U[1024,32768], paged 256, Hq=64 Hkv=8 D=128, 1 query each; cache far larger than L2"}
+            del dq, dk, dv, dbias
+            torch.cuda.empty_cache()
+        barrier()
+
+    # ------------------------------------------- packed varlen GQA (rank 0)
+    if "varlen" in legs and rank == 0:
+        g = torch.Generator().manual_seed(0)
+        lens = torch.randint(256, 4097, (16,), generator=g).tolist()
+        total = sum(lens)
+        gd = torch.Generator(device=dev).manual_seed(0)
+        vq = torch.randn(1, total, 8, 4, 128, generator=gd, device=dev, dtype=torch.bfloat16)
+        vk = torch.randn(1, total, 8, 1, 128, generator=gd, device=dev, dtype=torch.bfloat16).expand(-1, -1, -1, 4, -1)
+        vv = torch.randn(1, total, 8, 1, 128, generator=gd, device=dev, dtype=torch.bfloat16).expand(-1, -1, -1, 4, -1)
+        vbias = ab.BlockDiagonalCausalMask.from_seqlens(lens, device=dev)
+        fn = lambda: xops.memory_efficient_attention_forward(vq, vk, vv, vbias, op=fmha.b200.FwOp)
+        v_steps = max(5, min(args.steps, 30))
+        ms, win = event_time_ms(fn, v_steps, 3)
+        windows.append(win)
+        vflops = 8192.0 * sum(l * l for l in lens)
+        vt = vflops / (ms / v_steps * 1e-3) / 1e12
+        out_line["varlen_gqa"] = {"value": vt, "unit": UNIT, "ms_per_step": ms / v_steps, "frac_of_peak": vt / peaks["bf16_tflops"],
+                                  "workload": f"16 seqs U[256,4096] (total {total}), BlockDiagonalCausalMask, Hq=32 Hkv=8 D=128 bf16"}
+        del vq, vk, vv
+        torch.cuda.empty_cache()
+    barrier()
+
+    # ------------------------------------------------ long context (all ranks)
+    if "long" in legs:
+        S, Hkv, G, D = 131072, 8, 8, 128
+        lo, hi = shard_bounds(S, world, rank)
+        gd = torch.Generator(device=dev).manual_seed(1234)
+        lq = torch.randn(1, S, Hkv, G, D, generator=gd, device=dev, dtype=torch.bfloat16)
+        lk_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
+        lv_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
+        lk = lk_full[:, lo:hi].expand(-1, -1, -1, G, -1)
+        lv = lv_full[:, lo:hi].expand(-1, -1, -1, G, -1)
+        fn = lambda: sharded_kv_attention_forward(lq, lk, lv, kv_offset=lo, causal=True)
+        l_steps = 3
+        ms, win = event_time_ms(fn, l_steps, 1, barrier)
+        windows.append(win)
+        ms = max_over_ranks(ms)
+        lflops = 4.0 * S * S * D * Hkv * G / 2.0
+        lt = lflops / (ms / l_steps * 1e-3) / 1e12
+        out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms / l_steps, "scaling": "strong",
+                                    "ideal_speedup_contiguous_causal_shards": world * world / (2.0 * world - 1.0),
+                                    "workload": "1 x 131072 causal, Hq=64 Hkv=8 D=128 bf16; KV sharded contiguously over ranks, NCCL all-gather of (O, LSE) + LSE merge"}
+        del lq, lk, lv, lk_full, lv_full
+        torch.cuda.empty_cache()
+
+    if rank == 0:
+        out_line["clocks"] = sampler.stop(windows) if sampler is not None else None
+        if "cpu" in legs:
+            cflops, times = time_cpu(budget_s=12.0, max_reps=20)
+            best = min(times)
+            out_line["cpu_baseline"] = {
+                "value": cflops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"B={CPU_SAMPLE['B']} x H={CPU_SAMPLE['H']} heads of the headline configuration, best of {len(times)} runs (median {statistics.median(times):.3f} s); fp32 oracle",
+            }
+        print(json.dumps(out_line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,292 @@
+"""Prefill operator on the GPU against the oracle: both kernels (tcgen05 for
+head dims 64/128, mma.sync for the rest), every supported bias, BMK / BMHK /
+BMGHK layouts, LSE, sharded keys + merge."""
+
+import pytest
+import torch
+
+import oracle
+from gpu_utils import ATOL_O, assert_o_lse, gpu, rand_qkv, ref, require_cuda
+from xformers_b200.ops import fmha
+from xformers_b200.ops.fmha import attn_bias as ab
+
+P = fmha.b200
+KERNELS = [P.FwOp_Tcgen05, P.FwOp_Generic]
+
+
+def _status_ok():
+    assert P.prefill_device_status() == 0, "a wait inside the tcgen05 kernel timed out"
+
+
+@gpu
+def test_baseline_config1_on_gpu():
+    """B=2, M=128, H=4, D=64, causal, seed 0 (the CPU-runnable baseline
+    configuration) -- inputs cast to bf16, compared with the fp32 golden."""
+    require_cuda()
+    import numpy as np
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "cfg1_seed0.npz"))
+    gen = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(2, 128, 4, 64, generator=gen) for _ in range(3))
+    for dtype in (torch.bfloat16, torch.float16):
+        qd, kd, vd = (t.to(dtype).cuda() for t in (q, k, v))
+        ro, rl = ref(qd, kd, vd, ab.LowerTriangularMask())
+        for op in KERNELS:
+            out, lse = fmha.memory_efficient_attention_forward_requires_grad(qd, kd, vd, ab.LowerTriangularMask(), op=op)
+            assert out.shape == (2, 128, 4, 64) and lse.shape == (2, 4, 128)
+            assert_o_lse(out, lse, ro, rl, dtype, f"cfg1 {op.NAME}")
+            # and against the stored fp32 vectors: only input rounding separates them
+            assert np.abs(out.float().cpu().numpy() - g["out"]).max() < 5e-2
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("B,Mq,Mkv,H", [(1, 128, 128, 1), (2, 256, 256, 3), (1, 384, 640, 2), (3, 32, 1024, 1), (1, 1024, 16, 2),
+                                        (2, 3, 15, 1), (1, 31, 33, 2), (1, 132, 136, 1), (1, 90, 72, 5), (1, 2, 2, 1), (1, 257, 511, 1)])
+def test_dense_bmhk(op, dtype, D, causal, B, Mq, Mkv, H):
+    # shape grid of tests/test_mem_eff_attention.py:143-161 restricted to supported head dims
+    require_cuda()
+    q, k, v = rand_qkv(B, Mq, Mkv, 1, H, D, dtype, seed=B * Mq + Mkv * D, gqa=False)
+    q, k, v = q[:, :, 0], k[:, :, 0], v[:, :, 0]
+    bias = ab.LowerTriangularMask() if causal else None
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, f"{op.NAME} dense")
+    out2 = fmha.memory_efficient_attention_forward(q, k, v, bias, op=op)
+    assert torch.equal(out, out2), "must be bit-reproducible"
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("D", [8, 16, 32, 40, 72, 96, 120, 160, 256])
+@pytest.mark.parametrize("causal", [False, True])
+def test_other_head_dims_use_the_mma_kernel(D, causal):
+    require_cuda()
+    dtype = torch.bfloat16
+    q, k, v = rand_qkv(2, 68, 132, 1, 3, D, dtype, seed=D, gqa=False)
+    q, k, v = q[:, :, 0], k[:, :, 0], v[:, :, 0]
+    bias = ab.LowerTriangularMask() if causal else None
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias)
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, f"D={D}")
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+def test_bmk_layout_and_packed_qkv(op):
+    # tests/test_mem_eff_attention.py:560-585: q/k/v as non-contiguous views of one tensor
+    require_cuda()
+    dtype = torch.float16
+    B, M, H, D = 2, 200, 4, 64
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(B, M, 3, H, D, generator=g).to(dtype).cuda()
+    q, k, v = qkv.unbind(2)
+    assert not q.is_contiguous()
+    out = fmha.memory_efficient_attention_forward(q, k, v, op=op)
+    ro, _ = ref(q, k, v)
+    assert_o_lse(out, None, ro, None, dtype, "packed BMHK")
+    # BMK: [B*H, M, K]
+    q3, k3, v3 = (t.permute(0, 2, 1, 3).reshape(B * H, M, D) for t in (q, k, v))
+    out3, lse3 = fmha.memory_efficient_attention_forward_requires_grad(q3, k3, v3, ab.LowerTriangularMask(), op=op)
+    assert out3.shape == (B * H, M, D) and lse3.shape == (B * H, M)
+    ro3, rl3 = oracle.ref_attention_with_lse(q3.float().cpu(), k3.float().cpu(), v3.float().cpu(), ab.LowerTriangularMask())
+    assert_o_lse(out3, lse3, ro3, rl3, dtype, "BMK")
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("Mq", [1, 13, 512])
+@pytest.mark.parametrize("bias_kind", ["none", "causal_br", "causal_tl"])
+def test_gqa_bmghk(op, Mq, bias_kind):
+    # tests/test_mem_eff_attention.py:2031-2064: B=3, Mkv=512, G=2, H=16, K=128, fp16, stride-0 heads
+    require_cuda()
+    if bias_kind == "causal_tl" and Mq == 1:
+        pytest.skip("top-left causal with one query sees a single key; covered elsewhere")
+    dtype = torch.float16
+    q, k, v = rand_qkv(3, Mq, 512, 2, 16, 128, dtype, seed=Mq, gqa=True)
+    assert k.stride(3) == 0
+    bias = {"none": None, "causal_br": ab.LowerTriangularFromBottomRightMask(), "causal_tl": ab.LowerTriangularMask()}[bias_kind]
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    assert out.shape == q.shape and lse.shape == (3, 2, 16, Mq)
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, "GQA")
+    _status_ok()
+
+
+def _varlen_case(lens_q, lens_k, G, H, D, dtype, seed, gqa):
+    q, k, v = rand_qkv(1, sum(lens_q), sum(lens_k), G, H, D, dtype, seed=seed, gqa=gqa)
+    return q, k, v
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("kind", ["plain", "causal", "bottomright", "local", "local_br"])
+def test_block_diagonal_varlen(op, kind):
+    require_cuda()
+    dtype = torch.bfloat16
+    lens_q = [3, 130, 1, 256, 77, 128]
+    lens_k = [5, 130, 9, 300, 77, 129] if kind in ("plain", "bottomright", "local_br") else lens_q
+    q, k, v = _varlen_case(lens_q, lens_k, 2, 2, 128, dtype, seed=11, gqa=True)
+    base = ab.BlockDiagonalMask.from_seqlens(lens_q, lens_k, device="cuda")
+    bias = {
+        "plain": base,
+        "causal": base.make_causal(),
+        "bottomright": base.make_causal_from_bottomright(),
+        "local": base.make_local_attention(37),
+        "local_br": base.make_local_attention_from_bottomright(150),
+    }[kind]
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    assert lse.shape == (1, 2, 2, sum(lens_q)), "varlen LSE is packed"
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, f"varlen {kind}")
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+def test_padded_keys_prefill_and_nan_padding(op):
+    """tests/test_mem_eff_attention.py:1590-1646 (q lengths 4,1,1,...; keys in
+    padded slots; bottom-right causal) and :3036-3163 (NaN beyond kv_seqlen)."""
+    require_cuda()
+    dtype = torch.float16
+    bsize, n_heads, d, padding = 8, 3, 64, 160
+    k_seqlen = [5, 8, 7, 1, 9, 3, 140, 160]
+    q_seqlen = [4] + [1] * 7
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, sum(q_seqlen), n_heads, d, generator=g).to(dtype).cuda()
+    k = torch.randn(1, bsize * padding, n_heads, d, generator=g).to(dtype).cuda()
+    v = torch.randn(1, bsize * padding, n_heads, d, generator=g).to(dtype).cuda()
+    for cls in (ab.BlockDiagonalCausalWithOffsetPaddedKeysMask, ab.BlockDiagonalPaddedKeysMask):
+        bias = cls.from_seqlens(q_seqlen=q_seqlen, kv_seqlen=k_seqlen, kv_padding=padding, device="cuda")
+        out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, scale=1.0 / 8, op=op)
+        ro, rl = ref(q, k, v, bias, scale=1.0 / 8)
+        assert_o_lse(out, lse, ro, rl, dtype, "padded keys")
+        kn, vn = k.clone(), v.clone()
+        for b, n in enumerate(k_seqlen):
+            kn[0, b * padding + n : (b + 1) * padding] = float("nan")
+            vn[0, b * padding + n : (b + 1) * padding] = float("nan")
+        out_n, lse_n = fmha.memory_efficient_attention_forward_requires_grad(q, kn, vn, bias, scale=1.0 / 8, op=op)
+        assert not out_n.isnan().any() and not lse_n.isnan().any(), "NaN in padding leaked"
+        assert torch.equal(out, out_n) and torch.equal(lse, lse_n)
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+def test_no_out_of_bounds_reads(op):
+    # tests/test_mem_eff_attention.py:499-506,591-598: inputs re-homed in NaN-padded storage
+    require_cuda()
+    dtype = torch.bfloat16
+    B, Mq, Mkv, H, D = 2, 90, 200, 2, 128
+
+    def nan_padded(shape):
+        big = torch.full((shape[0], 256 * ((shape[1] + 255) // 256), shape[2], shape[3]), float("nan"), dtype=dtype, device="cuda")
+        view = big[:, : shape[1]]
+        view.copy_(torch.randn(shape, device="cuda").to(dtype))
+        return view
+
+    q, k, v = nan_padded((B, Mq, H, D)), nan_padded((B, Mkv, H, D)), nan_padded((B, Mkv, H, D))
+    for bias in (None, ab.LowerTriangularMask()):
+        out = fmha.memory_efficient_attention_forward(q, k, v, bias, op=op)
+        assert not out.isnan().any()
+        ro, _ = ref(q, k, v, bias)
+        assert_o_lse(out, None, ro, None, dtype, "NaN-padded storage")
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("shards", [2, 4])
+def test_sharded_keys_merge_to_full_causal(op, shards):
+    """Long-context algebra: each shard of the key axis gives a partial
+    (O, LSE) with the causal diagonal offset by the shard start; the merge
+    equals the full result.  Rows that see nothing in a shard have lse = -inf."""
+    require_cuda()
+    dtype = torch.bfloat16
+    B, S, G, H, D = 1, 1024, 2, 4, 128
+    q, k, v = rand_qkv(B, S, S, G, H, D, dtype, seed=5, gqa=True)
+    full, lse_full = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, ab.LowerTriangularMask(), op=op)
+    outs, lses = [], []
+    n = S // shards
+    for r in range(shards):
+        inp = fmha.Inputs(q, k[:, r * n : (r + 1) * n], v[:, r * n : (r + 1) * n], ab.LowerTriangularMask(), output_dtype=torch.float32, is_partial=True)
+        o, ctx = op._apply(inp, want_lse=True, kv_offset=r * n)
+        outs.append(o)
+        lses.append(ctx.lse)
+        if r > 0:
+            assert torch.isneginf(ctx.lse[..., : r * n]).all() and (o[:, : r * n] == 0).all()
+    merged, lse_m = fmha.merge_attentions(outs, lses, output_dtype=dtype)
+    ro, rl = ref(q, k, v, ab.LowerTriangularMask())
+    assert_o_lse(merged, lse_m, ro, rl, dtype, "sharded+merged")
+    assert (merged.float() - full.float()).abs().max() <= ATOL_O[dtype]
+    _status_ok()
+
+
+@gpu
+def test_partial_chunks_merge_to_full_decode():
+    # tests/test_fmha_merge_attentions.py:234-363: chunked attention + merge == full (1e-3 there)
+    require_cuda()
+    dtype = torch.bfloat16
+    B, max_t, H, D = 16, 2048, 8, 128
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(1, B, 1, H, D, generator=g).to(dtype).cuda()
+    k = torch.randn(1, B * max_t, 1, 1, D, generator=g).to(dtype).cuda().expand(-1, -1, -1, H, -1)
+    v = torch.randn(1, B * max_t, 1, 1, D, generator=g).to(dtype).cuda().expand(-1, -1, -1, H, -1)
+    lens = torch.randint(1, max_t + 1, (B,), generator=g).tolist()
+    bias = ab.BlockDiagonalPaddedKeysMask.from_seqlens([1] * B, max_t, lens, device="cuda")
+    full, lse_full = fmha.memory_efficient_attention_partial(q, k, v, bias, output_dtype=torch.float32)
+    bounds = [0, 100, 101, 900, max_t]
+    outs, lses = [], []
+    for lo, hi in zip(bounds, bounds[1:]):
+        # chunk [lo, hi) of every sequence: a padded-keys bias over a strided view of the cache
+        kk = k.view(1, B, max_t, 1, H, D)[:, :, lo:hi].reshape(1, B * (hi - lo), 1, H, D)
+        vv = v.view(1, B, max_t, 1, H, D)[:, :, lo:hi].reshape(1, B * (hi - lo), 1, H, D)
+        kk = kk[:, :, :, :1].expand(-1, -1, -1, H, -1)
+        vv = vv[:, :, :, :1].expand(-1, -1, -1, H, -1)
+        clens = [max(0, min(n, hi) - lo) for n in lens]
+        cb = ab.BlockDiagonalPaddedKeysMask.from_seqlens([1] * B, hi - lo, clens, device="cuda")
+        o, l = fmha.memory_efficient_attention_partial(q, kk, vv, cb, output_dtype=torch.float32)
+        outs.append(o)
+        lses.append(l)
+    merged, lse_m = fmha.merge_attentions(outs, lses)
+    torch.testing.assert_close(merged, full, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(lse_m, lse_full, rtol=1e-3, atol=1e-3)
+
+
+@gpu
+def test_empty_tensors():
+    # tests/test_mem_eff_attention.py:2316-2386
+    require_cuda()
+    dtype = torch.bfloat16
+    q = torch.randn(2, 0, 4, 64, device="cuda").to(dtype)
+    k = torch.randn(2, 16, 4, 64, device="cuda").to(dtype)
+    assert fmha.memory_efficient_attention_forward(q, k, k).shape == (2, 0, 4, 64)
+    q = torch.randn(2, 8, 4, 64, device="cuda").to(dtype)
+    k = torch.randn(2, 0, 4, 64, device="cuda").to(dtype)
+    out = fmha.memory_efficient_attention_forward(q, k, k, op=P.FwOp)
+    assert out.shape == q.shape and (out == 0).all()
+    q = torch.randn(0, 8, 4, 64, device="cuda").to(dtype)
+    assert fmha.memory_efficient_attention_forward(q, q, q).shape == (0, 8, 4, 64)
+
+
+@gpu
+def test_custom_stream_and_output_dtype():
+    # tests/test_mem_eff_attention.py:1153-1216: work is enqueued on the current stream
+    require_cuda()
+    dtype = torch.bfloat16
+    q, k, v = rand_qkv(1, 256, 256, 1, 2, 128, dtype, seed=2, gqa=False)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        out = fmha.memory_efficient_attention_forward(q, k, v, ab.LowerTriangularMask(), output_dtype=torch.float32)
+    s.synchronize()
+    assert out.dtype == torch.float32
+    ro, _ = ref(q, k, v, ab.LowerTriangularMask())
+    assert (out.cpu() - ro).abs().max() <= ATOL_O[dtype]
+    _status_ok()

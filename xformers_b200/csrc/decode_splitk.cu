@@ -722,13 +722,14 @@ static int launch_decode_t(const DecodeArgs& a, int head_blocks, cudaStream_t st
   const size_t cmb = size_t(kDecConsumerWarps) * 16 * MT * (D + 2) * 4;
   const size_t smem = (ring > cmb ? ring : cmb) + qbytes;
   auto kern = decode_splitk_kernel<D, MT, kInt4, kBf16>;
-  static bool configured = false;  // per instantiation
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  // 227 KB per CTA includes the static part (the mbarriers)
+  if (smem + 1024 > 227 * 1024) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
+  static size_t configured = 0;  // per instantiation: largest size opted into so far
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail("decode: cudaFuncSetAttribute", e);
-    configured = true;
+    configured = smem;
   }
-  if (smem > 227 * 1024) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
   dim3 grid(a.split_k, a.batch, head_blocks * a.row_blocks);
   kern<<<grid, kDecThreads, smem, stream>>>(a);
   int rc = check_launch("decode_splitk_kernel");
@@ -794,6 +795,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   a.rows = R, a.row_blocks = row_blocks;
   a.q_sm = p->q_stride_m, a.q_sg = p->q_stride_g, a.q_sh = p->q_stride_h;
   a.k_sm = p->k_stride_m, a.k_sg = p->k_stride_g, a.v_sm = p->v_stride_m, a.v_sg = p->v_stride_g;
+  if (p->kv_heads == 1) a.k_sg = a.v_sg = 0;  // the stride of an extent-1 axis is meaningless
   a.o_sm = p->o_stride_m, a.o_sg = p->o_stride_g, a.o_sh = p->o_stride_h;
   a.lse_sg = p->lse_stride_g, a.lse_sh = p->lse_stride_h;
   a.causal = p->mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT;
@@ -816,16 +818,16 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   // how the producer may copy: whole stripes by TMA when alignment allows
   const int elem = int4 ? 4 : 2;
   const int head_elems = int4 ? (1 + p->head_dim / 8) : p->head_dim;
-  const bool heads_contig = hb == 1 || (p->k_stride_g == head_elems && p->v_stride_g == head_elems);
+  const bool heads_contig = hb == 1 || (a.k_sg == head_elems && a.v_sg == head_elems);
   auto al16 = [&](int64_t elems) { return (elems * elem) % 16 == 0; };
   const bool base_al = (reinterpret_cast<uintptr_t>(p->k) % 16 == 0) && (reinterpret_cast<uintptr_t>(p->v) % 16 == 0);
   a.copy_group = 1;
   if (!base_al) {
     a.copy_mode = 2;
   } else if (heads_contig && al16(p->k_stride_m) && al16(p->v_stride_m) && al16(int64_t(hb) * head_elems) &&
-             al16(p->k_stride_g * hb) && al16(p->v_stride_g * hb)) {
+             al16(a.k_sg * hb) && al16(a.v_sg * hb)) {
     a.copy_mode = 0;
-  } else if (al16(p->k_stride_m) && al16(p->v_stride_m) && al16(p->k_stride_g) && al16(p->v_stride_g) && al16(head_elems)) {
+  } else if (al16(p->k_stride_m) && al16(p->v_stride_m) && al16(a.k_sg) && al16(a.v_sg) && al16(head_elems)) {
     a.copy_mode = 1;
   } else if (int4 && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
              p->v_stride_m == p->k_stride_m) {

@@ -29,6 +29,7 @@ inline int check_launch(const char* what) {
 }
 
 inline int cuda_fail(const char* what, cudaError_t e) {
+  (void)cudaGetLastError();  // do not leave the error behind for the next launch check
   return set_error(XFB200_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
