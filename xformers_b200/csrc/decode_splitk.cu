@@ -8,7 +8,7 @@
 // mma.sync.m16n8k16 (query heads of a GQA group are the M rows, tokens the N
 // columns; K/V are never expanded), the online softmax lives in registers.
 // The int4 row-wise cache is unpacked in registers: nibbles become bf16/f16
-// values 2^k + n by one shift+lop3 per element pair, and scale/shift are folded
+// values 16 + n by one shift+lop3 per element pair, and scale/shift are folded
 // into the scores (K) and into the probabilities (V) so no per-element FMA is
 // spent on dequantisation.
 //
@@ -48,6 +48,8 @@ struct DecodeArgs {
   int32_t row_blocks;  // ceil(R / (16*MT))
   int32_t copy_mode;   // 0: one bulk copy per token stripe of hb heads; 1: per (token, head); 2: word copies (no TMA)
   int32_t copy_group;  // tokens per bulk copy (int4 only, mode 0)
+  int32_t stages;         // depth of the shared-memory ring
+  int32_t q_first_stage;  // stages >= this one hold the staged Q until q_done
   int64_t q_sm, q_sg, q_sh;
   int64_t k_sm, k_sg, v_sm, v_sg;
   int64_t o_sm, o_sg, o_sh;
@@ -104,7 +106,8 @@ struct DecStage {
   }
 };
 
-__host__ __device__ constexpr int decode_stages(int d, int mt) { return (d == 64 ? 2 : 1) * (mt == 1 ? 3 : 2); }
+constexpr int kDecMaxStages = 12;
+constexpr int kDecRingBudget = 212 * 1024;  // bytes of cache in flight per SM
 
 template <int D, int MT, bool kInt4, bool kBf16>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
@@ -114,12 +117,13 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
   constexpr int KS = D / 16;    // k-steps of the QK^T product
   constexpr int NT = D / 8;     // n-tiles of the PV product
 
-  // bytes in flight per SM are what hide HBM latency: 3 stages of 64 KB at
-  // D = 128 (2 when two query m-tiles need the room), twice as many at D = 64
-  constexpr int kDecStages = decode_stages(D, MT);
+  // bytes in flight per SM are what hide HBM latency: the ring takes ~200 KB,
+  // i.e. 3 stages of 64 KB (bf16, D = 128) up to 12 stages of 17 KB (int4)
+  const int kDecStages = a.stages;
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  __shared__ uint64_t full_bar[kDecStages];
-  __shared__ uint64_t empty_bar[kDecStages];
+  __shared__ uint64_t full_bar[kDecMaxStages];
+  __shared__ uint64_t empty_bar[kDecMaxStages];
+  __shared__ uint64_t q_done_bar;
 
   const int split = blockIdx.x;
   const int b = blockIdx.y;
@@ -159,7 +163,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
   const int kv_bytes = Stage::kv_bytes(hb);
   const int row_bytes = Stage::row_bytes(hb);
   uint8_t* stage_base = smem_raw;                                  // kDecStages * 2 * kv_bytes
-  uint8_t* q_smem = smem_raw + kDecStages * 2 * kv_bytes;          // 8 warps * 16*MT rows * D*2 B (read once)
+  // Q is staged once in the region of the LAST stages; the producer does not
+  // fill those before every consumer warp has taken its Q fragments
+  uint8_t* q_smem = smem_raw + a.q_first_stage * 2 * kv_bytes;     // 8 warps * 16*MT rows * D*2 B
   constexpr int kQRowBytes = D * 2;
 
   if (threadIdx.x == 0) {
@@ -167,6 +173,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], kDecConsumerWarps);
     }
+    mbar_init(&q_done_bar, kDecConsumerWarps);
     mbar_fence_init();
   }
   __syncthreads();
@@ -183,6 +190,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
       if (tile >= kDecStages) {
         if (!mbar_wait(&empty_bar[st], ((tile / kDecStages) - 1) & 1)) {
           if (lane == 0) atomicExch(a.status, 1);
+          return;
+        }
+      } else if (tile == a.q_first_stage) {
+        if (!mbar_wait(&q_done_bar, 0)) {
+          if (lane == 0) atomicExch(a.status, 3);
           return;
         }
       }
@@ -315,6 +327,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
     }
   }
 
+  // Q now lives in registers: release the staging area to the producer
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&q_done_bar);
+
   // per-row visibility limit: token t visible iff t < lim
   int lim[MT][2];
 #pragma unroll
@@ -337,8 +353,19 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
     l_run[mt][0] = l_run[mt][1] = 0.f;
     corr[mt][0] = corr[mt][1] = 0.f;
   }
-  constexpr uint32_t kMagic = kBf16 ? 0x43004300u : 0x64006400u;  // 128+n (bf16) / 1024+n (f16)
-  constexpr float kMagicF = kBf16 ? 128.f : 1024.f;
+  // A nibble n dropped into the top four mantissa bits of 16.0 reads as 16 + n
+  // exactly (bf16: mantissa bits [3,7); f16: bits [6,10)).  The offset is of the
+  // size of the values themselves, so removing it later costs no precision.
+  constexpr uint32_t kMagic = kBf16 ? 0x41804180u : 0x4C004C00u;
+  constexpr uint32_t kNibMask = kBf16 ? 0x00780078u : 0x03C003C0u;
+  constexpr int kNibPos = kBf16 ? 3 : 6;
+  constexpr float kMagicF = 16.f;
+  // nibble pair (e, e+4) of a packed word, e = 0..3, as two 16-bit floats 16+n
+  auto unpack_pair = [](uint32_t w, int e) -> uint32_t {
+    const int sh = 4 * e - kNibPos;  // compile-time after unrolling
+    const uint32_t t = sh >= 0 ? (w >> sh) : (w << (-sh));
+    return (t & kNibMask) | kMagic;
+  };
 
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int st = tile % kDecStages;
@@ -379,10 +406,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
 #pragma unroll
           for (int i = 0; i < KS / 2; ++i) {
             const uint32_t w = krow[4 * i + c];
-            const uint32_t b00 = (w & 0x000F000Fu) | kMagic;          // elements 0,4
-            const uint32_t b01 = ((w >> 4) & 0x000F000Fu) | kMagic;   // elements 1,5
-            const uint32_t b10 = ((w >> 8) & 0x000F000Fu) | kMagic;   // elements 2,6
-            const uint32_t b11 = ((w >> 12) & 0x000F000Fu) | kMagic;  // elements 3,7
+            const uint32_t b00 = unpack_pair(w, 0);  // elements 0,4
+            const uint32_t b01 = unpack_pair(w, 1);  // elements 1,5
+            const uint32_t b10 = unpack_pair(w, 2);  // elements 2,6
+            const uint32_t b11 = unpack_pair(w, 3);  // elements 3,7
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               mma_16816<kBf16>(s[mt][j], qf[mt][2 * i], b00, b01);
@@ -507,10 +534,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
           for (int tk = 0; tk < 4; ++tk) {
             const int tl = sub * 16 + 2 * c + (tk & 1) + (tk >> 1) * 8;
             const uint32_t w = *(reinterpret_cast<const uint32_t*>(vs_ + tl * row_bytes + hw * W * 4) + 1 + WPT * r + wi);
-            x[tk][0] = (w & 0x000F000Fu) | kMagic;
-            x[tk][1] = ((w >> 4) & 0x000F000Fu) | kMagic;
-            x[tk][2] = ((w >> 8) & 0x000F000Fu) | kMagic;
-            x[tk][3] = ((w >> 12) & 0x000F000Fu) | kMagic;
+            x[tk][0] = unpack_pair(w, 0);
+            x[tk][1] = unpack_pair(w, 1);
+            x[tk][2] = unpack_pair(w, 2);
+            x[tk][3] = unpack_pair(w, 3);
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -715,12 +742,20 @@ int decode_chunk_tokens(int kv_bound, int split_k) {
 }
 
 template <int D, int MT, bool kInt4, bool kBf16>
-static int launch_decode_t(const DecodeArgs& a, int head_blocks, cudaStream_t stream) {
+static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
   using Stage = DecStage<D, kInt4>;
-  const size_t ring = size_t(decode_stages(D, MT)) * 2 * Stage::kv_bytes(a.hb);
+  const size_t stage_bytes = 2 * size_t(Stage::kv_bytes(a_in.hb));
   const size_t qbytes = size_t(kDecConsumerWarps) * 16 * MT * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * 16 * MT * (D + 2) * 4;
-  const size_t smem = (ring > cmb ? ring : cmb) + qbytes;
+  int stages = int(kDecRingBudget / stage_bytes);
+  stages = stages > kDecMaxStages ? kDecMaxStages : stages;
+  const int q_stages = int((qbytes + stage_bytes - 1) / stage_bytes);
+  if (stages < 2 || q_stages > stages) return set_error(XFB200_E_UNSUPPORTED, "decode: shared-memory ring too small for this shape");
+  DecodeArgs a = a_in;
+  a.stages = stages;
+  a.q_first_stage = stages - q_stages;
+  const size_t ring = stages * stage_bytes;
+  const size_t smem = ring > cmb ? ring : cmb;
   auto kern = decode_splitk_kernel<D, MT, kInt4, kBf16>;
   // 227 KB per CTA includes the static part (the mbarriers)
   if (smem + 1024 > 227 * 1024) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
