@@ -161,6 +161,35 @@ XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t
                                    int32_t split_k);
 XFB200_API int xfb200_decode_forward(const xfb200_decode_params* p, void* stream);
 
+/* Split-K decode that allocates nothing.  No counterpart in the reference.
+ *
+ * For callers that cannot call cudaMalloc around the attention call: a serving
+ * loop that must stay inside the device-memory budget it was handed at
+ * start-up, a plugin inside a host application that owns the allocator, or a
+ * latency-critical loop where an allocation (which may synchronise the whole
+ * device) is not acceptable.  With xfb200_decode_forward such a caller would
+ * have to provide the split-K scratch itself; here the library brings it.
+ *
+ * Same parameters and results as xfb200_decode_forward; p->scratch is ignored.
+ * The per-chunk partials go to an array of XFB200_DECODE_STATIC_SCRATCH_BYTES
+ * (16 MiB) that is part of the library image: every GPU that loads the library
+ * holds it until the process exits.  A shape whose
+ * xfb200_decode_scratch_bytes() exceeds that size is rejected with
+ * XFB200_E_INVALID and a message naming both numbers: lower split_k, or use the
+ * entry point above with your own scratch.  The call makes no cudaMalloc /
+ * cudaFree and uses no allocating library routine.
+ *
+ * The first call on each device resolves the array's device address (a symbol
+ * look-up with that device current, not an allocation); make that first call
+ * before any stream capture.
+ * All calls on a device share the one array, which keeps whatever the last call
+ * wrote.  Nothing in it has to start at zero: every chunk that a call merges
+ * has been written completely by that same call.  Two calls whose kernels may
+ * overlap on the GPU (different streams or host threads) race on the array --
+ * serialise them. */
+#define XFB200_DECODE_STATIC_SCRATCH_BYTES (16u << 20)
+XFB200_API int xfb200_decode_forward_static_scratch(const xfb200_decode_params* p, void* stream);
+
 /* ---- merge ---------------------------------------------------------------------
  * m = max_s lse_s; w_s = exp(lse_s - m); out = sum w_s O_s / sum w_s;
  * lse = m + log sum w_s.  A partial with lse = -inf has weight 0.

@@ -24,6 +24,7 @@ BF16, F16, F32 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL_TOP_LEFT, MASK_CAUSAL_BOTTOM_RIGHT = 0, 1, 2
 KV_PLAIN, KV_INT4_ROWWISE = 0, 1
 MERGE_MAX_PTRS = 32
+DECODE_STATIC_SCRATCH_BYTES = 16 << 20
 
 EXPORTED_SYMBOLS = (
     "xfb200_abi_version",
@@ -33,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "xfb200_debug_set_prefill_path",
     "xfb200_decode_scratch_bytes",
     "xfb200_decode_forward",
+    "xfb200_decode_forward_static_scratch",
     "xfb200_merge_attentions",
 )
 
@@ -182,6 +184,8 @@ def load() -> C.CDLL:
     lib.xfb200_decode_scratch_bytes.restype = C.c_size_t
     lib.xfb200_decode_forward.argtypes = [C.POINTER(DecodeParams), C.c_void_p]
     lib.xfb200_decode_forward.restype = C.c_int
+    lib.xfb200_decode_forward_static_scratch.argtypes = [C.POINTER(DecodeParams), C.c_void_p]
+    lib.xfb200_decode_forward_static_scratch.restype = C.c_int
     lib.xfb200_merge_attentions.argtypes = [C.POINTER(MergeParams), C.c_void_p]
     lib.xfb200_merge_attentions.restype = C.c_int
     if lib.xfb200_abi_version() != ABI_VERSION:

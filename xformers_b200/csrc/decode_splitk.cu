@@ -735,6 +735,10 @@ static int32_t* decode_status_word() {
   return words[dev];
 }
 
+// Set only while xfb200_decode_forward_static_scratch runs on this thread: the
+// status word then lives in the library's own device memory as well.
+static thread_local int32_t* t_status_override = nullptr;
+
 int decode_chunk_tokens(int kv_bound, int split_k) {
   int c = (kv_bound + split_k - 1) / split_k;
   c = (c + kDecChunkAlign - 1) / kDecChunkAlign * kDecChunkAlign;
@@ -841,7 +845,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     a.part_o = reinterpret_cast<float*>(p->scratch);
     a.part_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p->scratch) + ((rows * p->head_dim * 4 + 255) & ~size_t(255)));
   }
-  a.status = decode_status_word();
+  a.status = t_status_override != nullptr ? t_status_override : decode_status_word();
   if (a.status == nullptr) return set_error(XFB200_E_CUDA, "decode: cannot allocate the device status word");
 
   // kv heads per CTA: the largest of 8, 4, 2, 1 that divides kv_heads
@@ -897,4 +901,72 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     XFB_DISPATCH(64)
   }
 #undef XFB_DISPATCH
+}
+
+// ---------------------------------------------------------------------------
+// Split-K decode for callers that cannot allocate device memory.
+//
+// The partial outputs of the key chunks go to a fixed array that is part of the
+// library image instead of caller-provided scratch, and the status word of the
+// bounded waits sits next to it.  Both are file-scope __device__ arrays: in
+// host code their names are host-side stand-ins, not device addresses, so the
+// addresses the kernels receive are looked up once per device with
+// cudaGetSymbolAddress while that device is current.
+// ---------------------------------------------------------------------------
+namespace xfb {
+
+static __device__ __align__(256) unsigned char g_static_scratch[XFB200_DECODE_STATIC_SCRATCH_BYTES];
+static __device__ __align__(256) int32_t g_static_status[64];
+
+struct StaticScratchAddr {
+  void* scratch = nullptr;
+  int32_t* status = nullptr;
+};
+
+// Device addresses of the two arrays on the current device; resolved on the
+// first call per device (a symbol look-up, not an allocation) and cached.
+static int static_scratch_addresses(StaticScratchAddr* out) {
+  static StaticScratchAddr per_device[64];
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail("decode(static scratch): cudaGetDevice", e);
+  if (dev < 0 || dev >= 64) return set_error(XFB200_E_UNSUPPORTED, "decode(static scratch): device index %d out of range", dev);
+  StaticScratchAddr& slot = per_device[dev];
+  if (slot.scratch == nullptr) {
+    void* scratch = nullptr;
+    void* status = nullptr;
+    e = cudaGetSymbolAddress(&scratch, g_static_scratch);
+    if (e != cudaSuccess) return cuda_fail("decode(static scratch): cudaGetSymbolAddress(scratch)", e);
+    e = cudaGetSymbolAddress(&status, g_static_status);
+    if (e != cudaSuccess) return cuda_fail("decode(static scratch): cudaGetSymbolAddress(status)", e);
+    slot.status = static_cast<int32_t*>(status);
+    slot.scratch = scratch;
+  }
+  *out = slot;
+  return XFB200_OK;
+}
+
+}  // namespace xfb
+
+extern "C" int xfb200_decode_forward_static_scratch(const xfb200_decode_params* p, void* stream) {
+  using namespace xfb;
+  if (p == nullptr) return set_error(XFB200_E_INVALID, "decode(static scratch): null params");
+  if (p->batch < 0 || p->mq < 1 || p->kv_heads < 1 || p->q_per_kv < 1 || p->split_k < 1 || p->head_dim < 1)
+    return set_error(XFB200_E_INVALID, "decode(static scratch): bad extents");
+  const size_t need = xfb200_decode_scratch_bytes(p->batch, p->mq, p->kv_heads, p->q_per_kv, p->head_dim, p->split_k);
+  if (need > size_t(XFB200_DECODE_STATIC_SCRATCH_BYTES))
+    return set_error(XFB200_E_INVALID,
+                     "decode(static scratch): this shape needs %zu bytes of split-K scratch, the built-in array holds %zu; "
+                     "use fewer splits or xfb200_decode_forward with your own scratch",
+                     need, size_t(XFB200_DECODE_STATIC_SCRATCH_BYTES));
+  if (p->batch == 0) return XFB200_OK;
+  StaticScratchAddr addr;
+  int rc = static_scratch_addresses(&addr);
+  if (rc != XFB200_OK) return rc;
+  xfb200_decode_params q = *p;
+  q.scratch = addr.scratch;
+  t_status_override = addr.status;
+  rc = xfb200_decode_forward(&q, stream);
+  t_status_override = nullptr;
+  return rc;
 }
