@@ -207,11 +207,11 @@ def gpu_quantize_int4(x):
     return torch.cat([ss, packed], dim=-1).contiguous().view(torch.int32)
 
 
-def decode_workload(dev, quant: bool, seed: int = 0):
+def decode_workload(dev, quant: bool, seed: int = 0, B: int = 64):
     from xformers_b200.ops.fmha import attn_bias as ab
 
     g = torch.Generator().manual_seed(seed)
-    B, page, Hkv, G, D = 64, 256, 8, 8, 128
+    page, Hkv, G, D = 256, 8, 8, 128
     lens = torch.randint(1024, 32769, (B,), generator=g)
     pages = (lens + page - 1) // page
     pool = int(pages.sum())
@@ -255,6 +255,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="headline only (no decode / varlen / long-context / CPU legs)")
     ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,varlen,long,cpu")
+    ap.add_argument("--small", action="store_true",
+                    help="profiling case: one batch of the headline configuration (128 MB of tensors, still larger than L2) and 16 decode sequences; not a bench value")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -303,7 +305,9 @@ def main():
     }
 
     # ------------------------------------------------------------- headline
-    B, M, H, D = CFG2["B"], CFG2["M"], CFG2["H"], CFG2["D"]
+    B, M, H, D = (1 if args.small else CFG2["B"]), CFG2["M"], CFG2["H"], CFG2["D"]
+    if args.small:
+        out_line["config"]["small"] = "profiling case, not a bench value"
     gd = torch.Generator(device=dev).manual_seed(rank)
     q, k, v = (torch.randn(B, M, H, D, generator=gd, device=dev, dtype=torch.bfloat16) for _ in range(3))
     causal = ab.LowerTriangularMask()
@@ -346,13 +350,13 @@ def main():
     # --------------------------------------------------- decode (rank 0 only)
     for name, quant in (("decode_bf16", False), ("decode_int4", True)):
         if name in legs and rank == 0:
-            dq, dk, dv, dbias, nbytes = decode_workload(dev, quant)
+            dq, dk, dv, dbias, nbytes = decode_workload(dev, quant, B=16 if args.small else 64)
             fn = lambda: xops.memory_efficient_attention_forward(dq, dk, dv, dbias, op=fmha.b200_splitk.FwOp)
             d_steps = max(5, min(args.steps, 30))
             ms, win = event_time_ms(fn, d_steps, 3)
             windows.append(win)
             gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
-            split = fmha.b200_splitk.FwOp.get_split_k(64, 32768, 8, 68 if quant else 256)
+            split = fmha.b200_splitk.FwOp.get_split_k(16 if args.small else 64, 32768, 8, 68 if quant else 256)
             out_line[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes, "split_k": split,
                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                            "frac": gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"]},

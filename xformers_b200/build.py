@@ -23,9 +23,10 @@ SOURCES = [
     "decode_splitk.cu",
     "prefill_generic.cu",
     "prefill_sm100.cu",
+    "prefill_sm100_m256.cu",
     "prefill_api.cu",
 ]
-HEADERS = ["internal.h", "ptx.cuh", "../../include/xfb200.h"]
+HEADERS = ["internal.h", "ptx.cuh", "prefill_sm100.h", "../../include/xfb200.h"]
 NVCC_FLAGS = [
     "-gencode",
     "arch=compute_100a,code=sm_100a",

@@ -100,7 +100,11 @@ struct DecStage {
   // plain: one row per token = hb heads * D elements (+16 B pad against bank conflicts)
   // int4 : one row per token = hb heads * (1 + D/8) words, unpadded
   __host__ __device__ static int row_bytes(int hb) { return kInt4 ? hb * (1 + D / 8) * 4 : hb * D * 2 + 16; }
-  __host__ __device__ static int tokens(int hb) { return 16 * (kDecConsumerWarps / hb); }
+  // sub-tiles of 16 tokens each warp takes from one stage: the packed cache is 4x
+  // denser, so its stages hold 4x the tokens to keep the per-stage overhead
+  // (barrier round trip, page-table look-ups of the producer) off the critical path
+  static constexpr int kSubTiles = kInt4 ? 4 : 1;
+  __host__ __device__ static int tokens(int hb) { return 16 * kSubTiles * (kDecConsumerWarps / hb); }
   __host__ __device__ static int kv_bytes(int hb) {  // K or V part of a stage, rounded to 128 B
     return (row_bytes(hb) * tokens(hb) + 127) & ~127;
   }
@@ -133,7 +137,8 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
   const int lane = threadIdx.x & 31;
   const int hb = a.hb;
   const int wph = kDecConsumerWarps / hb;  // consumer warps per kv head
-  const int TOK = 16 * wph;
+  constexpr int kSps = DecStage<D, kInt4>::kSubTiles;
+  const int TOK = 16 * wph * kSps;
 
   const int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
   const int chunk_lo = split * a.chunk_tokens;
@@ -373,7 +378,9 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
       if (lane == 0) atomicExch(a.status, 2);
       break;
     }
-    const int t_sub = chunk_lo + tile * TOK + sub * 16;  // first token of this warp's sub-tile
+    for (int sp = 0; sp < kSps; ++sp) {
+    const int usub = sub + wph * sp;                      // this warp's sub-tile of the stage
+    const int t_sub = chunk_lo + tile * TOK + usub * 16;  // its first token
     if (t_sub < chunk_hi) {
       const uint8_t* ks_ = stage_base + st * 2 * kv_bytes;
       const uint8_t* vs_ = ks_ + kv_bytes;
@@ -387,7 +394,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
         for (int j = 0; j < 2; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
 
       if constexpr (!kInt4) {
-        const int tok = sub * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int tok = usub * 16 + (lane & 7) + (lane >> 4) * 8;
         const uint32_t kaddr = smem_u32(ks_ + tok * row_bytes + hw * D * 2 + ((lane >> 3) & 1) * 16);
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
@@ -402,7 +409,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
       } else {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const uint32_t* krow = reinterpret_cast<const uint32_t*>(ks_ + (sub * 16 + j * 8 + r) * row_bytes + hw * W * 4) + 1;
+          const uint32_t* krow = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + j * 8 + r) * row_bytes + hw * W * 4) + 1;
 #pragma unroll
           for (int i = 0; i < KS / 2; ++i) {
             const uint32_t w = krow[4 * i + c];
@@ -425,7 +432,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int tl = sub * 16 + j * 8 + 2 * c + e;
+          const int tl = usub * 16 + j * 8 + 2 * c + e;
           const int t = t_sub + j * 8 + 2 * c + e;
           if constexpr (kInt4) {
             const uint32_t kw = *reinterpret_cast<const uint32_t*>(ks_ + tl * row_bytes + hw * W * 4);
@@ -507,11 +514,11 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
           for (int i = lane; i < 16 * (D / 8); i += 32) {
             const int tt = i / (D / 8), ch = i % (D / 8);
             if (t_sub + tt >= chunk_hi)
-              *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + (sub * 16 + tt) * row_bytes + hw * D * 2 + ch * 16) = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + (usub * 16 + tt) * row_bytes + hw * D * 2 + ch * 16) = make_uint4(0, 0, 0, 0);
           }
           __syncwarp();
         }
-        const int tok = sub * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int tok = usub * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const uint32_t vaddr = smem_u32(vs_ + tok * row_bytes + hw * D * 2 + (lane >> 4) * 16);
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
@@ -532,7 +539,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
           uint32_t x[4][4];  // [token 2c,2c+1,2c+8,2c+9][element pair i,(i+4)]
 #pragma unroll
           for (int tk = 0; tk < 4; ++tk) {
-            const int tl = sub * 16 + 2 * c + (tk & 1) + (tk >> 1) * 8;
+            const int tl = usub * 16 + 2 * c + (tk & 1) + (tk >> 1) * 8;
             const uint32_t w = *(reinterpret_cast<const uint32_t*>(vs_ + tl * row_bytes + hw * W * 4) + 1 + WPT * r + wi);
             x[tk][0] = unpack_pair(w, 0);
             x[tk][1] = unpack_pair(w, 1);
@@ -554,6 +561,7 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
           }
         }
       }
+    }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[st]);

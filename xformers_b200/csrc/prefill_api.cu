@@ -1,11 +1,16 @@
 // xfb200_prefill_forward: host-side validation and kernel selection.
 #include "internal.h"
+#include "prefill_sm100.h"
 
 namespace xfb {
 
 // Debug/testing knob: 0 = automatic, 1 = force the mma.sync kernel, 2 = require the tcgen05 kernel.
 static int g_prefill_path = 0;
 
+}  // namespace xfb
+
+namespace xfb {
+int prefill_path_override() { return g_prefill_path; }
 }  // namespace xfb
 
 extern "C" int xfb200_debug_set_prefill_path(int path) {
@@ -46,7 +51,7 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool can100 = g_prefill_path != 1 && p->mkv > 0 && prefill_sm100_supported(p);
-  if (g_prefill_path == 2 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
+  if (g_prefill_path >= 2 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
   if (can100) return prefill_sm100_launch(p, st);
   return prefill_generic_launch(p, st);
 }

@@ -24,6 +24,7 @@
 #include <cuda_fp16.h>
 
 #include "internal.h"
+#include "prefill_sm100.h"
 #include "ptx.cuh"
 
 namespace xfb {
@@ -34,23 +35,6 @@ constexpr int kStages = 2;
 constexpr int kSoftmaxWarps = 4;
 constexpr int kThreads = (2 + kSoftmaxWarps) * 32;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-
-struct Sm100Args {
-  CUtensorMap tm_q, tm_k, tm_v;
-  void* out;
-  float* lse;
-  const int32_t* seqstart_q;
-  const int32_t* seqstart_k;
-  const int32_t* seqlen_k;
-  int32_t* status;
-  int32_t batch, mq, mkv, groups, heads_per_group;
-  int32_t kv_h_is_broadcast;  // K/V head stride 0: KV head index is g only
-  xfb200_strides os;
-  int64_t lse_b, lse_g, lse_h;
-  int32_t mask_type, kv_offset, window_left, out_dtype;
-  float scale_log2;
-  int32_t q_tiles;
-};
 
 struct __align__(8) Sm100Barriers {
   uint64_t q_full;
@@ -553,6 +537,10 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.q_tiles = (p->mq + kBM - 1) / kBM;
   const bool bf16 = p->dtype == XFB200_BF16;
+  if (prefill_path_override() != 3) {
+    a.q_tiles = (p->mq + 255) / 256;
+    return prefill_sm100_m256_launch(a, D, bf16, stream);
+  }
   if (D == 128) return bf16 ? launch_sm100_t<128, true>(a, stream) : launch_sm100_t<128, false>(a, stream);
   return bf16 ? launch_sm100_t<64, true>(a, stream) : launch_sm100_t<64, false>(a, stream);
 }

@@ -1,0 +1,509 @@
+// Attention forward (prefill) on tcgen05, 256 query rows per CTA.
+//
+// Two 128-row query tiles share every K/V tile that TMA brings in, and two
+// softmax warpgroups work out of phase so that the tensor pipe always has
+// either a QK^T or a PV product to run:
+//
+//   warps 0-3   softmax of query tile 0   (thread <-> row <-> TMEM lane)
+//   warps 4-7   softmax of query tile 1
+//   warp 8      TMA producer: Q (both tiles) once, then K_j / V_j into 2-deep rings
+//   warp 9      MMA issuer  : ... PV(t,j), QK(t,j+1) for t = 0,1 ...   (one lane issues)
+// The third warpgroup (warps 8-11) hands most of its registers to the two
+// softmax warpgroups with setmaxnreg, so that a whole score row (128 fp32)
+// stays in registers.
+//
+// Tensor memory (all 512 columns): S0 | S1 | O0 | O1, fp32.  The probabilities
+// P_t overwrite the first 64 columns of S_t as packed bf16/f16 pairs and feed
+// the PV product straight from tensor memory (A operand in TMEM), so P never
+// touches shared memory.  tcgen05 operations issued by one thread complete in
+// order: when the barrier of QK(t,j) fires, PV(t,j-1) has finished, hence the
+// softmax may rescale O_t and overwrite S_t/P_t without further hand-shakes.
+//
+// Softmax arithmetic runs on packed f32x2 FMA/ADD, exp2 with the scale folded
+// in, four independent max/sum chains per thread, and a lazy running maximum
+// (raised only when it grows by more than 2^8) so that rescaling the
+// accumulator in tensor memory is rare.
+//
+// Masks, GQA indexing, NaN hygiene and bounded waits as in the 128-row kernel.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "prefill_sm100.h"
+#include "ptx.cuh"
+
+namespace xfb {
+namespace m256 {
+
+constexpr int kBM = 128;      // rows per query tile
+constexpr int kTiles = 2;     // query tiles per CTA
+constexpr int kBN = 128;      // keys per tile
+constexpr int kStages = 2;
+constexpr int kThreads = 384;  // warps 0-3 / 4-7: softmax of tile 0 / 1; warp 8: TMA; warp 9: MMA; 10-11 idle
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
+constexpr float kRescaleThreshold = 8.0f;
+constexpr uint32_t kHalfBytes = 128 * 128;  // one 64-column block of a 128-row tile
+
+struct __align__(8) Barriers {
+  uint64_t q_full;
+  uint64_t k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
+  uint64_t s_full[kTiles], p_full[kTiles], pv_done[kTiles];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template <int D>
+struct Smem {
+  static constexpr int kQTile = kBM * D * 2;
+  static constexpr int kKV = kBN * D * 2;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTiles * kQTile;
+  static constexpr int kV = kK + kStages * kKV;
+  static constexpr int kBar = kV + kStages * kKV;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+// Packed fp32 pairs live in 64-bit registers; building and splitting them with
+// mov.b64 keeps everything in registers (no address-taken locals).
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t fadd2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  } else {
+    __half2 t = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&t);
+  }
+}
+
+template <int D, bool kBf16>
+__global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const __grid_constant__ Sm100Args a) {
+  using L = Smem<D>;
+  constexpr int kHalves = D / 64;
+  extern __shared__ uint8_t smem_dyn[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  Barriers* bar = reinterpret_cast<Barriers*>(smem + L::kBar);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = a.q_tiles - 1 - int(blockIdx.x);  // heaviest (latest) rows first
+  const int gh = blockIdx.y;
+  const int g = gh / a.heads_per_group, h = gh % a.heads_per_group;
+  const int b = blockIdx.z;
+
+  if (*reinterpret_cast<volatile int32_t*>(a.status) != 0) return;  // an earlier CTA gave up: drain the grid
+
+  int q_row0 = 0, k_row0 = 0, qlen = a.mq, klen = a.mkv, tb = b;
+  if (a.seqstart_q != nullptr) {
+    q_row0 = a.seqstart_q[b];
+    qlen = a.seqstart_q[b + 1] - q_row0;
+    k_row0 = a.seqstart_k[b];
+    klen = a.seqlen_k != nullptr ? a.seqlen_k[b] : a.seqstart_k[b + 1] - k_row0;
+    tb = 0;
+  }
+  const int m0 = qt * kBM * kTiles;
+  if (m0 >= qlen) return;
+  const bool causal = a.mask_type != XFB200_MASK_NONE;
+  const int shift = (a.mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT ? klen - qlen : 0) - a.kv_offset;
+
+  // Key-tile range [jlo_t, jhi_t) of each query tile, in units of kBN keys from n_base.
+  int jlo[kTiles], jhi[kTiles];
+  int n_base = 0;
+  if (a.window_left >= 0) n_base = max(0, m0 + shift - a.window_left) / kBN * kBN;
+  int j_end = 0;
+#pragma unroll
+  for (int t = 0; t < kTiles; ++t) {
+    const int mt0 = m0 + t * kBM;
+    int hi = klen, lo = n_base;
+    if (causal) hi = min(hi, mt0 + kBM + shift);
+    if (a.window_left >= 0) lo = max(n_base, max(0, mt0 + shift - a.window_left) / kBN * kBN);
+    if (mt0 >= qlen) hi = lo;  // no valid row in this tile
+    jlo[t] = (lo - n_base) / kBN;
+    jhi[t] = hi > lo ? (hi - n_base + kBN - 1) / kBN : jlo[t];
+    j_end = max(j_end, jhi[t]);
+  }
+  const int j_begin = min(jlo[0], jlo[1]);
+  const int kv_head = g * (a.kv_h_is_broadcast ? 1 : a.heads_per_group) + (a.kv_h_is_broadcast ? 0 : h);
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bar->q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&bar->k_full[i], 1);
+      mbar_init(&bar->v_full[i], 1);
+      mbar_init(&bar->k_empty[i], 1);
+      mbar_init(&bar->v_empty[i], 1);
+    }
+    for (int t = 0; t < kTiles; ++t) {
+      mbar_init(&bar->s_full[t], 1);
+      mbar_init(&bar->p_full[t], 128);
+      mbar_init(&bar->pv_done[t], 1);
+    }
+    bar->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&bar->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bar->tmem_base;
+  volatile uint32_t* abort_flag = &bar->abort_flag;
+
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  if (warp == kTmaWarp) {
+    // ============================================================ TMA producer
+    if (lane == 0 && j_end > j_begin) {
+      prefetch_tensormap(&a.tm_q);
+      prefetch_tensormap(&a.tm_k);
+      prefetch_tensormap(&a.tm_v);
+      mbar_expect_tx(&bar->q_full, kTiles * L::kQTile);
+#pragma unroll
+      for (int t = 0; t < kTiles; ++t)
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tma_load_4d(smem + L::kQ + t * L::kQTile + hf * kHalfBytes, &a.tm_q, &bar->q_full, hf * 64, g * a.heads_per_group + h,
+                      q_row0 + m0 + t * kBM, tb);
+      for (int j = j_begin; j < j_end; ++j) {
+        const int it = j - j_begin, st = it % kStages, use = it / kStages;
+        const int row = k_row0 + n_base + j * kBN;
+        if (use > 0 && !mbar_wait(&bar->k_empty[st], (use - 1) & 1, abort_flag)) {
+          atomicExch(a.status, 11);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&bar->k_full[st], L::kKV);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, kv_head, row, tb);
+        if (use > 0 && !mbar_wait(&bar->v_empty[st], (use - 1) & 1, abort_flag)) {
+          atomicExch(a.status, 12);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&bar->v_full[st], L::kKV);
+#pragma unroll
+        for (int hf = 0; hf < kHalves; ++hf)
+          tma_load_4d(smem + L::kV + st * L::kKV + hf * kHalfBytes, &a.tm_v, &bar->v_full[st], hf * 64, kv_head, row, tb);
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ============================================================== MMA issuer
+    constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
+    constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
+    bool ok = true;
+    int cnt[kTiles] = {0, 0};     // products issued per query tile (phase of p_full / pv_done)
+    bool o_init[kTiles] = {false, false};
+
+    auto issue_qk = [&](int t, int it) {
+      const uint32_t q_addr = smem_u32(smem + L::kQ + t * L::kQTile);
+      const uint32_t k_addr = smem_u32(smem + L::kK + (it % kStages) * L::kKV);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = (kk / 4) * kHalfBytes + (kk % 4) * 32;
+        umma_ss(tmem + t * 128, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+      }
+    };
+    auto issue_pv = [&](int t, int it) {
+      const uint32_t v_addr = smem_u32(smem + L::kV + (it % kStages) * L::kKV);
+#pragma unroll
+      for (int kk = 0; kk < kBN / 16; ++kk) {
+        const uint64_t vd = umma_desc_sw128(v_addr + kk * 16 * 128, kHalfBytes, 1024);
+        // A = P_t: packed 16-bit pairs, 8 columns of tensor memory per 16 keys
+        umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd, idesc_pv, (o_init[t] || kk > 0) ? 1u : 0u);
+      }
+      o_init[t] = true;
+    };
+
+    if (j_end > j_begin) {
+      ok = mbar_wait(&bar->q_full, 0, abort_flag) && mbar_wait(&bar->k_full[0], 0, abort_flag);
+      if (!ok && lane == 0) atomicExch(a.status, 21);
+      if (ok) {
+        tc_fence_after();
+        if (lane == 0) {
+#pragma unroll
+          for (int t = 0; t < kTiles; ++t)
+            if (j_begin >= jlo[t] && j_begin < jhi[t]) {
+              issue_qk(t, 0);
+              tc_commit(&bar->s_full[t]);
+            }
+          tc_commit(&bar->k_empty[0]);
+        }
+        __syncwarp();
+      }
+      for (int j = j_begin; ok && j < j_end; ++j) {
+        const int it = j - j_begin, st = it % kStages, use = it / kStages;
+        const bool has_next = j + 1 < j_end;
+        ok = mbar_wait(&bar->v_full[st], use & 1, abort_flag);
+        if (ok && has_next) ok = mbar_wait(&bar->k_full[(it + 1) % kStages], ((it + 1) / kStages) & 1, abort_flag);
+        if (!ok) {
+          if (lane == 0) atomicExch(a.status, 22);
+          break;
+        }
+        const int n0 = n_base + j * kBN;
+        if (n0 + kBN > klen) {
+          // V rows past the end of the sequence may hold anything; P is 0 there
+          const int first = max(klen - n0, 0);
+          uint8_t* vt = smem + L::kV + st * L::kKV;
+          for (int hf = 0; hf < kHalves; ++hf)
+            for (int i = first * 8 + lane; i < kBN * 8; i += 32) *reinterpret_cast<uint4*>(vt + hf * kHalfBytes + i * 16) = make_uint4(0, 0, 0, 0);
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+          const bool act = j >= jlo[t] && j < jhi[t];
+          const bool act_next = has_next && (j + 1) >= jlo[t] && (j + 1) < jhi[t];
+          if (act) {
+            ok = mbar_wait(&bar->p_full[t], cnt[t] & 1, abort_flag);
+            if (!ok) {
+              if (lane == 0) atomicExch(a.status, 23 + t);
+              break;
+            }
+            tc_fence_after();
+          }
+          if (lane == 0) {
+            if (act) {
+              issue_pv(t, it);
+              tc_commit(&bar->pv_done[t]);
+            }
+            if (act_next) {
+              issue_qk(t, it + 1);
+              tc_commit(&bar->s_full[t]);
+            }
+          }
+          if (act) cnt[t]++;
+          __syncwarp();
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          tc_commit(&bar->v_empty[st]);
+          if (has_next) tc_commit(&bar->k_empty[(it + 1) % kStages]);
+        }
+        __syncwarp();
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    // ================================================================ softmax
+    const int t = warp >> 2;                      // query tile of this warpgroup
+    const int row = (warp & 3) * 32 + lane;       // TMEM lane == row inside the tile
+    const uint32_t lane_sel = uint32_t((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem + t * 128 + lane_sel;
+    const uint32_t tmem_o = tmem + 256 + t * 128 + lane_sel;
+    const int mt0 = m0 + t * kBM;
+    const int i_loc = mt0 + row;
+    const int col_hi = causal ? min(klen, i_loc + shift + 1) : klen;
+    const int col_lo = a.window_left >= 0 ? i_loc + shift - a.window_left : 0;
+    const float sl2 = a.scale_log2;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    int cnt = 0;
+
+    for (int j = jlo[t]; j < jhi[t]; ++j, ++cnt) {
+      const int n0 = n_base + j * kBN;
+      ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag);
+      if (!ok) {
+        atomicExch(a.status, 31 + t);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sr[kBN];
+#pragma unroll
+      for (int cblk = 0; cblk < kBN / 32; ++cblk) {
+        uint32_t* dst = sr + cblk * 32;
+        XFB_TMEM_LD_32(tmem_s + cblk * 32, dst);
+      }
+      tc_wait_ld();
+      float* s = reinterpret_cast<float*>(sr);
+
+      const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift) ||
+                             (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) {
+          const int col = n0 + c;
+          s[c] = (col >= col_lo && col < col_hi) ? s[c] : -INFINITY;
+        }
+      }
+      // row maximum: four independent chains
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < kBN; c += 4) {
+        mx4[0] = fmaxf(mx4[0], s[c]);
+        mx4[1] = fmaxf(mx4[1], s[c + 1]);
+        mx4[2] = fmaxf(mx4[2], s[c + 2]);
+        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // scale > 0 (host guarantees)
+      const bool raise = mx > m_run + kRescaleThreshold;  // also true on the first visible key (m_run = -inf)
+      const float m_new = raise ? mx : m_run;
+      const float alpha = raise ? (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new)) : 1.f;
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+
+      // QK(t,j) completing implies PV(t,j-1) completed: O_t is quiescent here
+      if (cnt > 0 && __any_sync(0xffffffffu, raise)) {
+        const uint64_t al2 = f2_pack(alpha, alpha);
+#pragma unroll
+        for (int cblk = 0; cblk < D / 32; ++cblk) {
+          uint32_t orr[32];
+          XFB_TMEM_LD_32(tmem_o + cblk * 32, orr);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            f2_unpack(fmul2(f2_pack(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), al2), x0, x1);
+            orr[i] = __float_as_uint(x0);
+            orr[i + 1] = __float_as_uint(x1);
+          }
+          XFB_TMEM_ST_32(tmem_o + cblk * 32, orr);
+        }
+      }
+      l_run *= alpha;
+      m_run = m_new;
+
+      // P = exp2(s * scale - m), packed pairs, straight back into tensor memory
+      const uint64_t sc2 = f2_pack(sl2, sl2), nm2 = f2_pack(-m_use, -m_use);
+      uint64_t sum2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+      uint32_t pr[kBN / 2];
+#pragma unroll
+      for (int c = 0; c < kBN; c += 4) {
+        float a0, a1, b0, b1;
+        f2_unpack(ffma2(f2_pack(s[c], s[c + 1]), sc2, nm2), a0, a1);
+        f2_unpack(ffma2(f2_pack(s[c + 2], s[c + 3]), sc2, nm2), b0, b1);
+        a0 = fast_exp2(a0);
+        a1 = fast_exp2(a1);
+        b0 = fast_exp2(b0);
+        b1 = fast_exp2(b1);
+        sum2[0] = fadd2(sum2[0], f2_pack(a0, a1));
+        sum2[1] = fadd2(sum2[1], f2_pack(b0, b1));
+        pr[c / 2] = pack_pair<kBf16>(a0, a1);
+        pr[c / 2 + 1] = pack_pair<kBf16>(b0, b1);
+      }
+      {
+        float x0, x1, y0, y1;
+        f2_unpack(sum2[0], x0, x1);
+        f2_unpack(sum2[1], y0, y1);
+        l_run += (x0 + x1) + (y0 + y1);
+      }
+      {
+        uint32_t* p0 = pr;
+        uint32_t* p1 = pr + 32;
+        XFB_TMEM_ST_32(tmem_s, p0);
+        XFB_TMEM_ST_32(tmem_s + 32, p1);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[t]);
+    }
+
+    // ---- epilogue
+    const bool have = cnt > 0;
+    if (ok && have) {
+      ok = mbar_wait(&bar->pv_done[t], (cnt - 1) & 1, abort_flag);
+      if (!ok) atomicExch(a.status, 33 + t);
+      tc_fence_after();
+    }
+    const bool valid_row = i_loc < qlen;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const int64_t o_off = int64_t(tb) * a.os.b + int64_t(q_row0 + i_loc) * a.os.m + int64_t(g) * a.os.g + int64_t(h) * a.os.h;
+#pragma unroll
+    for (int cblk = 0; cblk < D / 32; ++cblk) {
+      uint32_t orr[32];
+      if (ok && have) {
+        XFB_TMEM_LD_32(tmem_o + cblk * 32, orr);
+        tc_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) orr[i] = 0;
+      }
+      if (valid_row) {
+        if (a.out_dtype == XFB200_F32) {
+          float* dst = reinterpret_cast<float*>(a.out) + o_off + cblk * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<float4*>(dst + i) = make_float4(__uint_as_float(orr[i]) * inv, __uint_as_float(orr[i + 1]) * inv,
+                                                              __uint_as_float(orr[i + 2]) * inv, __uint_as_float(orr[i + 3]) * inv);
+        } else {
+          uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + o_off + cblk * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float x0 = __uint_as_float(orr[i + 2 * e]) * inv, x1 = __uint_as_float(orr[i + 2 * e + 1]) * inv;
+              w[e] = a.out_dtype == XFB200_BF16 ? pack_pair<true>(x0, x1) : pack_pair<false>(x0, x1);
+            }
+            *reinterpret_cast<uint4*>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+    if (valid_row && a.lse != nullptr) {
+      const float lse = l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+      const int64_t lo = a.seqstart_q != nullptr ? int64_t(g) * a.lse_g + int64_t(h) * a.lse_h + q_row0 + i_loc
+                                                 : int64_t(b) * a.lse_b + int64_t(g) * a.lse_g + int64_t(h) * a.lse_h + i_loc;
+      a.lse[lo] = lse;
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+template <int D, bool kBf16>
+static int launch_t(const Sm100Args& a, cudaStream_t stream) {
+  auto kern = prefill_sm100_m256_kernel<D, kBf16>;
+  constexpr int smem = Smem<D>::kTotal;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_fail("prefill(sm100, 256 rows): cudaFuncSetAttribute", e);
+    configured = true;
+  }
+  dim3 grid(a.q_tiles, a.groups * a.heads_per_group, a.batch);
+  if (grid.y > 65535 || grid.z > 65535) return set_error(XFB200_E_UNSUPPORTED, "prefill: more than 65535 heads or sequences");
+  kern<<<grid, kThreads, smem, stream>>>(a);
+  return check_launch("prefill_sm100_m256_kernel");
+}
+
+}  // namespace m256
+
+int prefill_sm100_m256_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream) {
+  if (head_dim == 128) return bf16 ? m256::launch_t<128, true>(a, stream) : m256::launch_t<128, false>(a, stream);
+  return bf16 ? m256::launch_t<64, true>(a, stream) : m256::launch_t<64, false>(a, stream);
+}
+
+}  // namespace xfb
