@@ -89,6 +89,11 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
   if constexpr (kBf16) {
@@ -109,10 +114,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   Barriers* bar = reinterpret_cast<Barriers*>(smem + L::kBar);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = a.q_tiles - 1 - int(blockIdx.x);  // heaviest (latest) rows first
-  const int gh = blockIdx.y;
+  // CTAs are handed out with blockIdx.x fastest: all (batch, head) pairs of the
+  // heaviest (latest) row block first, the lightest row block last, so that the
+  // tail of the grid is made of short CTAs
+  const int qt = a.q_tiles - 1 - int(blockIdx.y);
+  const int n_heads = a.groups * a.heads_per_group;
+  const int gh = int(blockIdx.x) % n_heads;
   const int g = gh / a.heads_per_group, h = gh % a.heads_per_group;
-  const int b = blockIdx.z;
+  const int b = int(blockIdx.x) / n_heads;
 
   if (*reinterpret_cast<volatile int32_t*>(a.status) != 0) return;  // an earlier CTA gave up: drain the grid
 
@@ -158,7 +167,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     }
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(&bar->s_full[t], 1);
-      mbar_init(&bar->p_full[t], 128);
+      mbar_init(&bar->p_full[t], 4);  // one arrival per softmax warp
       mbar_init(&bar->pv_done[t], 1);
     }
     bar->abort_flag = 0;
@@ -357,11 +366,11 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       // row maximum: four independent chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < kBN; c += 4) {
-        mx4[0] = fmaxf(mx4[0], s[c]);
-        mx4[1] = fmaxf(mx4[1], s[c + 1]);
-        mx4[2] = fmaxf(mx4[2], s[c + 2]);
-        mx4[3] = fmaxf(mx4[3], s[c + 3]);
+      for (int c = 0; c < kBN; c += 8) {  // three-input max: two elements per instruction
+        mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
+        mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
+        mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
+        mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // scale > 0 (host guarantees)
       const bool raise = mx > m_run + kRescaleThreshold;  // also true on the first visible key (m_run = -inf)
@@ -422,7 +431,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&bar->p_full[t]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar->p_full[t]);
     }
 
     // ---- epilogue
@@ -493,8 +503,9 @@ static int launch_t(const Sm100Args& a, cudaStream_t stream) {
     if (e != cudaSuccess) return cuda_fail("prefill(sm100, 256 rows): cudaFuncSetAttribute", e);
     configured = true;
   }
-  dim3 grid(a.q_tiles, a.groups * a.heads_per_group, a.batch);
-  if (grid.y > 65535 || grid.z > 65535) return set_error(XFB200_E_UNSUPPORTED, "prefill: more than 65535 heads or sequences");
+  const int64_t bh = int64_t(a.groups) * a.heads_per_group * a.batch;
+  if (bh > 0x7fffffff || a.q_tiles > 65535) return set_error(XFB200_E_UNSUPPORTED, "prefill: grid too large");
+  dim3 grid(unsigned(bh), a.q_tiles, 1);
   kern<<<grid, kThreads, smem, stream>>>(a);
   return check_launch("prefill_sm100_m256_kernel");
 }
