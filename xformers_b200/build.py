@@ -56,18 +56,21 @@ def _stamp() -> str:
     return h.hexdigest()
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    stamp_file = CSRC / "build" / "stamp"
-    stamp = _stamp()
-    if not force and LIB.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
-        return LIB
-    objdir = CSRC / "build"
-    objdir.mkdir(exist_ok=True)
+def build(force: bool = False, verbose: bool = False, extra_flags=(), out: Path = LIB) -> Path:
+    """``extra_flags`` / ``out`` build an experimental variant beside the
+    default library (selected at run time with XFB200_LIBRARY)."""
+    variant = bool(extra_flags) or Path(out) != LIB
+    objdir = CSRC / "build" / (hashlib.sha256(" ".join(extra_flags).encode()).hexdigest()[:8] if variant else "")
+    stamp_file = objdir / "stamp"
+    stamp = _stamp() + " ".join(extra_flags)
+    if not force and Path(out).exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
+        return Path(out)
+    objdir.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
 
     def compile_one(src: str) -> Path:
         obj = objdir / (Path(src).stem + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-c", str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -79,13 +82,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs)]
+    cmd = [nvcc, "-shared", "-o", str(out), *map(str, objs)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     stamp_file.write_text(stamp)
-    return LIB
+    return Path(out)
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    defs = [a for a in sys.argv[1:] if a.startswith("-D")]
+    outs = [a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--out=")]
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, extra_flags=tuple(defs), out=Path(outs[0]) if outs else LIB))

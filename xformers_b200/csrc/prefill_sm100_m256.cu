@@ -39,16 +39,25 @@ namespace m256 {
 constexpr int kBM = 128;      // rows per query tile
 constexpr int kTiles = 2;     // query tiles per CTA
 constexpr int kBN = 128;      // keys per tile
-constexpr int kStages = 2;
-constexpr int kThreads = 384;  // warps 0-3 / 4-7: softmax of tile 0 / 1; warp 8: TMA; warp 9: MMA; 10-11 idle
-constexpr int kTmaWarp = 8, kMmaWarp = 9;
+// K tiles are requested 1.5 loop iterations ahead of their use, V tiles only one:
+// V gets the third stage (the TMA round trip is longer than one iteration)
+#ifndef XFB_KSTAGES
+#define XFB_KSTAGES 2
+#endif
+#ifndef XFB_VSTAGES
+#define XFB_VSTAGES 3
+#endif
+constexpr int kStagesK = XFB_KSTAGES, kStagesV = XFB_VSTAGES;
+constexpr int kThreads = 384;  // warps 0-3 / 4-7: softmax of tile 0 / 1; 8, 9: MMA of tile 0 / 1; 10: TMA; 11 idle
+constexpr int kMmaWarp0 = 8, kTmaWarp = 10;  // warps 8 and 9 issue the MMAs of query tile 0 and 1
 constexpr float kRescaleThreshold = 8.0f;
 constexpr uint32_t kHalfBytes = 128 * 128;  // one 64-column block of a 128-row tile
 
 struct __align__(8) Barriers {
   uint64_t q_full;
-  uint64_t k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
+  uint64_t k_full[kStagesK], v_full[kStagesV], k_empty[kStagesK], v_empty[kStagesV];
   uint64_t s_full[kTiles], p_full[kTiles], pv_done[kTiles];
+  uint64_t turn[kTiles];  // token of the tensor pipe: the two MMA warps issue their blocks alternately
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -59,8 +68,8 @@ struct Smem {
   static constexpr int kKV = kBN * D * 2;
   static constexpr int kQ = 0;
   static constexpr int kK = kQ + kTiles * kQTile;
-  static constexpr int kV = kK + kStages * kKV;
-  static constexpr int kBar = kV + kStages * kKV;
+  static constexpr int kV = kK + kStagesK * kKV;
+  static constexpr int kBar = kV + kStagesV * kKV;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
@@ -104,6 +113,29 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&t);
   }
 }
+
+// Probabilities to 16 bits.  The float-to-half conversions share the special-
+// function pipe with exp2, the busiest pipe of this kernel, so bf16 pairs are
+// instead cut out of the fp32 bit patterns with one byte permute (ALU pipe).
+// That truncates, i.e. P comes out low by 2^-9 on average; the row sum used for
+// the normalisation is scaled by the same factor at the end (kPTruncBias).
+#ifndef XFB_P_ROUND
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
+  if constexpr (kBf16) {
+    return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+  } else {
+    return pack_pair<false>(lo, hi);
+  }
+}
+template <bool kBf16>
+constexpr float kPTruncBias = kBf16 ? (1.f - 1.f / 512.f) : 1.f;
+#else
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack_p(float lo, float hi) { return pack_pair<kBf16>(lo, hi); }
+template <bool kBf16>
+constexpr float kPTruncBias = 1.f;
+#endif
 
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const __grid_constant__ Sm100Args a) {
@@ -159,21 +191,24 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
 
   if (threadIdx.x == 0) {
     mbar_init(&bar->q_full, 1);
-    for (int i = 0; i < kStages; ++i) {
+    for (int i = 0; i < kStagesK; ++i) {
       mbar_init(&bar->k_full[i], 1);
+      mbar_init(&bar->k_empty[i], kTiles);  // released by both MMA warps
+    }
+    for (int i = 0; i < kStagesV; ++i) {
       mbar_init(&bar->v_full[i], 1);
-      mbar_init(&bar->k_empty[i], 1);
-      mbar_init(&bar->v_empty[i], 1);
+      mbar_init(&bar->v_empty[i], kTiles);
     }
     for (int t = 0; t < kTiles; ++t) {
       mbar_init(&bar->s_full[t], 1);
-      mbar_init(&bar->p_full[t], 4);  // one arrival per softmax warp
+      mbar_init(&bar->p_full[t], 128);
       mbar_init(&bar->pv_done[t], 1);
+      mbar_init(&bar->turn[t], 1);
     }
     bar->abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp0) {
     tmem_alloc(&bar->tmem_base, 512);
     tmem_relinquish();
   }
@@ -199,122 +234,168 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
           tma_load_4d(smem + L::kQ + t * L::kQTile + hf * kHalfBytes, &a.tm_q, &bar->q_full, hf * 64, g * a.heads_per_group + h,
                       q_row0 + m0 + t * kBM, tb);
       for (int j = j_begin; j < j_end; ++j) {
-        const int it = j - j_begin, st = it % kStages, use = it / kStages;
+        const int it = j - j_begin, st = it % kStagesK, use = it / kStagesK;
+        const int sv = it % kStagesV, use_v = it / kStagesV;
         const int row = k_row0 + n_base + j * kBN;
         if (use > 0 && !mbar_wait(&bar->k_empty[st], (use - 1) & 1, abort_flag)) {
           atomicExch(a.status, 11);
           *abort_flag = 1;
           break;
         }
-        mbar_expect_tx(&bar->k_full[st], L::kKV);
+#ifdef XFB_X_NOLOAD
+        if (use > 0) {
+          mbar_arrive(&bar->k_full[st]);
+        } else
+#endif
+        {
+          mbar_expect_tx(&bar->k_full[st], L::kKV);
 #pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf)
-          tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, kv_head, row, tb);
-        if (use > 0 && !mbar_wait(&bar->v_empty[st], (use - 1) & 1, abort_flag)) {
+          for (int hf = 0; hf < kHalves; ++hf)
+            tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, kv_head, row, tb);
+        }
+        if (use_v > 0 && !mbar_wait(&bar->v_empty[sv], (use_v - 1) & 1, abort_flag)) {
           atomicExch(a.status, 12);
           *abort_flag = 1;
           break;
         }
-        mbar_expect_tx(&bar->v_full[st], L::kKV);
+#ifdef XFB_X_NOLOAD
+        if (use_v > 0) {
+          mbar_arrive(&bar->v_full[sv]);
+        } else
+#endif
+        {
+          mbar_expect_tx(&bar->v_full[sv], L::kKV);
 #pragma unroll
-        for (int hf = 0; hf < kHalves; ++hf)
-          tma_load_4d(smem + L::kV + st * L::kKV + hf * kHalfBytes, &a.tm_v, &bar->v_full[st], hf * 64, kv_head, row, tb);
+          for (int hf = 0; hf < kHalves; ++hf)
+            tma_load_4d(smem + L::kV + sv * L::kKV + hf * kHalfBytes, &a.tm_v, &bar->v_full[sv], hf * 64, kv_head, row, tb);
+        }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ============================================================== MMA issuer
+  } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
+    // ===================================================== MMA issuer of tile t
+    // tcgen05.mma is issued almost synchronously (the queue in front of the
+    // tensor pipe is about one instruction deep), so every clock this lane
+    // spends on anything else -- a satisfied mbarrier wait alone costs ~90 --
+    // is a clock the tensor pipe idles.  Hence one issuing warp per query tile:
+    // while one waits for its softmax, the other keeps the pipe fed.
+    const int t = warp - kMmaWarp0;
     constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
     constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
     bool ok = true;
-    int cnt[kTiles] = {0, 0};     // products issued per query tile (phase of p_full / pv_done)
-    bool o_init[kTiles] = {false, false};
-
-    auto issue_qk = [&](int t, int it) {
-      const uint32_t q_addr = smem_u32(smem + L::kQ + t * L::kQTile);
-      const uint32_t k_addr = smem_u32(smem + L::kK + (it % kStages) * L::kKV);
+    // Shared-memory descriptors: the upper word is constant (stride between
+    // 8-row groups = 1024 B, version 1, 128B swizzle); the lower word holds
+    // (address >> 4) and the leading-dimension offset, so stepping through a
+    // tile is one 32-bit add per operand.
+    constexpr uint32_t kDescHi = 64u | (1u << 14) | (2u << 29);
+    auto desc = [](uint32_t lo) -> uint64_t {
+      uint64_t d;
+      asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+      return d;
+    };
+    const uint32_t q_lo = (smem_u32(smem + L::kQ + t * L::kQTile) >> 4) | (1u << 16);
+    const uint32_t k_lo0 = (smem_u32(smem + L::kK) >> 4) | (1u << 16);
+    const uint32_t v_lo0 = (smem_u32(smem + L::kV) >> 4) | ((kHalfBytes >> 4) << 16);
+    const uint32_t tmem_s = tmem + t * 128, tmem_o = tmem + 256 + t * 128;
+    auto issue_qk_part = [&](int k_stage, int kk_lo, int kk_hi) {
+      const uint32_t kl = k_lo0 + k_stage * (L::kKV >> 4);
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
-        const uint32_t off = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-        umma_ss(tmem + t * 128, umma_desc_sw128(q_addr + off, 16, 1024), umma_desc_sw128(k_addr + off, 16, 1024), idesc_qk, kk > 0);
+        if (kk < kk_lo || kk >= kk_hi) continue;
+        const uint32_t off = ((kk / 4) * kHalfBytes + (kk % 4) * 32) >> 4;
+        umma_ss(tmem_s, desc(q_lo + off), desc(kl + off), idesc_qk, kk > 0);
       }
     };
-    auto issue_pv = [&](int t, int it) {
-      const uint32_t v_addr = smem_u32(smem + L::kV + (it % kStages) * L::kKV);
+    auto issue_qk = [&](int k_stage) { issue_qk_part(k_stage, 0, D / 16); };
+    auto issue_pv = [&](int v_stage, bool accumulate) {
+      const uint32_t vl = v_lo0 + v_stage * (L::kKV >> 4);
 #pragma unroll
       for (int kk = 0; kk < kBN / 16; ++kk) {
-        const uint64_t vd = umma_desc_sw128(v_addr + kk * 16 * 128, kHalfBytes, 1024);
         // A = P_t: packed 16-bit pairs, 8 columns of tensor memory per 16 keys
-        umma_ts(tmem + 256 + t * 128, tmem + t * 128 + kk * 8, vd, idesc_pv, (o_init[t] || kk > 0) ? 1u : 0u);
+        umma_ts(tmem_o, tmem_s + kk * 8, desc(vl + ((kk * 16 * 128) >> 4)), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
       }
-      o_init[t] = true;
     };
 
     if (j_end > j_begin) {
+      // ring positions advance by one per key tile (no divisions in the loop)
+      int ks = 0, kph = 0;  // K stage / phase of tile j
+      int vs = 0, vph = 0;  // V stage / phase of tile j
+      int cnt = 0;          // products of this query tile so far
       ok = mbar_wait(&bar->q_full, 0, abort_flag) && mbar_wait(&bar->k_full[0], 0, abort_flag);
       if (!ok && lane == 0) atomicExch(a.status, 21);
       if (ok) {
         tc_fence_after();
         if (lane == 0) {
-#pragma unroll
-          for (int t = 0; t < kTiles; ++t)
-            if (j_begin >= jlo[t] && j_begin < jhi[t]) {
-              issue_qk(t, 0);
-              tc_commit(&bar->s_full[t]);
-            }
+          if (j_begin >= jlo[t] && j_begin < jhi[t]) {
+            issue_qk(0);
+            tc_commit(&bar->s_full[t]);
+          }
           tc_commit(&bar->k_empty[0]);
+          if (t == 1) mbar_arrive(&bar->turn[0]);  // tile 0 opens every iteration
         }
-        __syncwarp();
       }
+      int turn_ph = 0;
       for (int j = j_begin; ok && j < j_end; ++j) {
-        const int it = j - j_begin, st = it % kStages, use = it / kStages;
         const bool has_next = j + 1 < j_end;
-        ok = mbar_wait(&bar->v_full[st], use & 1, abort_flag);
-        if (ok && has_next) ok = mbar_wait(&bar->k_full[(it + 1) % kStages], ((it + 1) / kStages) & 1, abort_flag);
+        const bool act = j >= jlo[t] && j < jhi[t];
+        const bool act_next = has_next && (j + 1) >= jlo[t] && (j + 1) < jhi[t];
+        int ks1 = ks + 1, kph1 = kph;
+        if (ks1 == kStagesK) ks1 = 0, kph1 ^= 1;
+        ok = mbar_wait(&bar->v_full[vs], vph, abort_flag);
+        if (ok && has_next) ok = mbar_wait(&bar->k_full[ks1], kph1, abort_flag);
         if (!ok) {
           if (lane == 0) atomicExch(a.status, 22);
           break;
         }
         const int n0 = n_base + j * kBN;
         if (n0 + kBN > klen) {
-          // V rows past the end of the sequence may hold anything; P is 0 there
+          // V rows past the end of the sequence may hold anything; P is 0 there.
+          // Both MMA warps write the same zeros: no ordering between them is needed.
           const int first = max(klen - n0, 0);
-          uint8_t* vt = smem + L::kV + st * L::kKV;
+          uint8_t* vt = smem + L::kV + vs * L::kKV;
           for (int hf = 0; hf < kHalves; ++hf)
             for (int i = first * 8 + lane; i < kBN * 8; i += 32) *reinterpret_cast<uint4*>(vt + hf * kHalfBytes + i * 16) = make_uint4(0, 0, 0, 0);
           fence_proxy_async_smem();
           __syncwarp();
         }
-#pragma unroll
-        for (int t = 0; t < kTiles; ++t) {
-          const bool act = j >= jlo[t] && j < jhi[t];
-          const bool act_next = has_next && (j + 1) >= jlo[t] && (j + 1) < jhi[t];
-          if (act) {
-            ok = mbar_wait(&bar->p_full[t], cnt[t] & 1, abort_flag);
-            if (!ok) {
-              if (lane == 0) atomicExch(a.status, 23 + t);
-              break;
-            }
-            tc_fence_after();
+        if (act) {
+          ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag);
+          if (!ok) {
+            if (lane == 0) atomicExch(a.status, 23 + t);
+            break;
           }
-          if (lane == 0) {
-            if (act) {
-              issue_pv(t, it);
-              tc_commit(&bar->pv_done[t]);
-            }
-            if (act_next) {
-              issue_qk(t, it + 1);
-              tc_commit(&bar->s_full[t]);
-            }
-          }
-          if (act) cnt[t]++;
-          __syncwarp();
+          tc_fence_after();
         }
-        if (!ok) break;
+        // If both warps issued at will, their MMAs would interleave one by one,
+        // both tiles would finish together and both softmaxes would run at the
+        // same time with the tensor pipe idle.  Blocks (PV, next QK) are
+        // therefore issued alternately, which keeps the two tiles half a period
+        // apart; the token is passed a few MMAs before the end of a block so
+        // that the hand-over latency is hidden.
+        ok = mbar_wait(&bar->turn[t], turn_ph, abort_flag);
+        turn_ph ^= 1;
+        if (!ok) {
+          if (lane == 0) atomicExch(a.status, 25 + t);
+          break;
+        }
         if (lane == 0) {
-          tc_commit(&bar->v_empty[st]);
-          if (has_next) tc_commit(&bar->k_empty[(it + 1) % kStages]);
+          if (act) {
+            issue_pv(vs, cnt > 0);
+            tc_commit(&bar->pv_done[t]);
+          }
+          tc_commit(&bar->v_empty[vs]);
+          if (act_next) {
+            issue_qk_part(ks1, 0, D / 32);
+            mbar_arrive(&bar->turn[1 - t]);
+            issue_qk_part(ks1, D / 32, D / 16);
+            tc_commit(&bar->s_full[t]);
+          } else {
+            mbar_arrive(&bar->turn[1 - t]);
+          }
+          if (has_next) tc_commit(&bar->k_empty[ks1]);
         }
-        __syncwarp();
+        if (act) ++cnt;
+        ks = ks1, kph = kph1;
+        if (++vs == kStagesV) vs = 0, vph ^= 1;
       }
       if (!ok) *abort_flag = 1;
     }
@@ -336,8 +417,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     bool ok = true;
     int cnt = 0;
 
+#ifdef XFB_TIMING
+    long long tm_wait = 0, tm_ld = 0, tm_math = 0, tm_st = 0, tm_n = 0, tm_max = 0, tm_tail = 0;
+#endif
     for (int j = jlo[t]; j < jhi[t]; ++j, ++cnt) {
       const int n0 = n_base + j * kBN;
+#ifdef XFB_TIMING
+      const long long c0 = clock64();
+#endif
       ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag);
       if (!ok) {
         atomicExch(a.status, 31 + t);
@@ -345,13 +432,25 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         break;
       }
       tc_fence_after();
+#ifdef XFB_X_TRIVIAL
+      tc_fence_before();
+      mbar_arrive(&bar->p_full[t]);
+      continue;
+#endif
       uint32_t sr[kBN];
 #pragma unroll
       for (int cblk = 0; cblk < kBN / 32; ++cblk) {
         uint32_t* dst = sr + cblk * 32;
         XFB_TMEM_LD_32(tmem_s + cblk * 32, dst);
       }
+#ifdef XFB_TIMING
+      const long long c1 = clock64();
+#endif
       tc_wait_ld();
+#ifdef XFB_TIMING
+      asm volatile("" ::"r"(sr[0]), "r"(sr[127]) : "memory");
+      const long long c2 = clock64();
+#endif
       float* s = reinterpret_cast<float*>(sr);
 
       const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift) ||
@@ -366,13 +465,22 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       // row maximum: four independent chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
+#ifdef XFB_X_NOMAX
+      for (int c = 0; c < 8; c += 8) {
+#else
       for (int c = 0; c < kBN; c += 8) {  // three-input max: two elements per instruction
+#endif
         mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
         mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
         mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
         mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // scale > 0 (host guarantees)
+#ifdef XFB_TIMING
+      asm volatile("" ::"f"(mx) : "memory");
+      const long long c2m = clock64();
+      tm_max += c2m - c2;
+#endif
       const bool raise = mx > m_run + kRescaleThreshold;  // also true on the first visible key (m_run = -inf)
       const float m_new = raise ? mx : m_run;
       const float alpha = raise ? (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new)) : 1.f;
@@ -399,6 +507,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       l_run *= alpha;
       m_run = m_new;
 
+#ifdef XFB_TIMING
+      long long c3 = 0;
+#endif
       // P = exp2(s * scale - m), packed pairs, straight back into tensor memory
       const uint64_t sc2 = f2_pack(sl2, sl2), nm2 = f2_pack(-m_use, -m_use);
       uint64_t sum2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
@@ -408,14 +519,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         float a0, a1, b0, b1;
         f2_unpack(ffma2(f2_pack(s[c], s[c + 1]), sc2, nm2), a0, a1);
         f2_unpack(ffma2(f2_pack(s[c + 2], s[c + 3]), sc2, nm2), b0, b1);
+#ifndef XFB_X_NOEXP
         a0 = fast_exp2(a0);
         a1 = fast_exp2(a1);
         b0 = fast_exp2(b0);
         b1 = fast_exp2(b1);
+#endif
         sum2[0] = fadd2(sum2[0], f2_pack(a0, a1));
         sum2[1] = fadd2(sum2[1], f2_pack(b0, b1));
-        pr[c / 2] = pack_pair<kBf16>(a0, a1);
-        pr[c / 2 + 1] = pack_pair<kBf16>(b0, b1);
+        pr[c / 2] = pack_p<kBf16>(a0, a1);
+        pr[c / 2 + 1] = pack_p<kBf16>(b0, b1);
       }
       {
         float x0, x1, y0, y1;
@@ -426,14 +539,34 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       {
         uint32_t* p0 = pr;
         uint32_t* p1 = pr + 32;
+#ifdef XFB_TIMING
+        asm volatile("" ::"r"(pr[0]), "r"(pr[63]) : "memory");
+        c3 = clock64();
+        tm_wait += c1 - c0, tm_ld += c2 - c1, tm_math += c3 - c2;
+#endif
         XFB_TMEM_ST_32(tmem_s, p0);
         XFB_TMEM_ST_32(tmem_s + 32, p1);
       }
       tc_wait_st();
       tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bar->p_full[t]);
+      mbar_arrive(&bar->p_full[t]);
+#ifdef XFB_TIMING
+      const long long c4 = clock64();
+      tm_st += c4 - c0, tm_n += 1, tm_tail += c4 - c3;
+#endif
     }
+#ifdef XFB_TIMING
+    if (row == 0 && tm_n > 0) {
+      unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.status) + 8;
+      atomicAdd(dbg + 0, (unsigned long long)tm_wait);
+      atomicAdd(dbg + 1, (unsigned long long)tm_ld);
+      atomicAdd(dbg + 2, (unsigned long long)tm_math);
+      atomicAdd(dbg + 3, (unsigned long long)tm_st);
+      atomicAdd(dbg + 4, (unsigned long long)tm_n);
+      atomicAdd(dbg + 5, (unsigned long long)tm_max);
+      atomicAdd(dbg + 6, (unsigned long long)tm_tail);
+    }
+#endif
 
     // ---- epilogue
     const bool have = cnt > 0;
@@ -443,7 +576,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       tc_fence_after();
     }
     const bool valid_row = i_loc < qlen;
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const float inv = l_run > 0.f ? 1.f / (l_run * kPTruncBias<kBf16>) : 0.f;
     const int64_t o_off = int64_t(tb) * a.os.b + int64_t(q_row0 + i_loc) * a.os.m + int64_t(g) * a.os.g + int64_t(h) * a.os.h;
 #pragma unroll
     for (int cblk = 0; cblk < D / 32; ++cblk) {
@@ -487,7 +620,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   }
 
   __syncthreads();
-  if (warp == kMmaWarp) {
+  if (warp == kMmaWarp0) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
