@@ -558,14 +558,3 @@ extern "C" int xfb200_prefill_device_status(void* stream, int32_t* status_out) {
   return XFB200_OK;
 }
 
-// Testing aid: raw 64-bit counters kept behind the status word (only written by
-// builds with XFB_TIMING).  Copies 8 counters to the host and clears them.
-extern "C" __attribute__((visibility("default"))) int xfb200_debug_read_counters(unsigned long long* out8) {  // 16 counters
-  using namespace xfb;
-  int32_t* w = prefill_status_word();
-  if (w == nullptr || out8 == nullptr) return XFB200_E_INVALID;
-  cudaError_t e = cudaDeviceSynchronize();
-  if (e == cudaSuccess) e = cudaMemcpy(out8, reinterpret_cast<unsigned long long*>(w) + 8, 128, cudaMemcpyDeviceToHost);
-  if (e == cudaSuccess) e = cudaMemset(reinterpret_cast<unsigned long long*>(w) + 8, 0, 128);
-  return e == cudaSuccess ? XFB200_OK : cuda_fail("debug_read_counters", e);
-}

@@ -39,13 +39,12 @@ namespace m256 {
 constexpr int kBM = 128;      // rows per query tile
 constexpr int kTiles = 2;     // query tiles per CTA
 constexpr int kBN = 128;      // keys per tile
-// K tiles are requested 1.5 loop iterations ahead of their use, V tiles only one:
-// V gets the third stage (the TMA round trip is longer than one iteration)
+// depth of the K and V rings (a third V stage measured no gain)
 #ifndef XFB_KSTAGES
 #define XFB_KSTAGES 2
 #endif
 #ifndef XFB_VSTAGES
-#define XFB_VSTAGES 3
+#define XFB_VSTAGES 2
 #endif
 constexpr int kStagesK = XFB_KSTAGES, kStagesV = XFB_VSTAGES;
 constexpr int kThreads = 384;  // warps 0-3 / 4-7: softmax of tile 0 / 1; 8, 9: MMA of tile 0 / 1; 10: TMA; 11 idle
@@ -113,29 +112,6 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&t);
   }
 }
-
-// Probabilities to 16 bits.  The float-to-half conversions share the special-
-// function pipe with exp2, the busiest pipe of this kernel, so bf16 pairs are
-// instead cut out of the fp32 bit patterns with one byte permute (ALU pipe).
-// That truncates, i.e. P comes out low by 2^-9 on average; the row sum used for
-// the normalisation is scaled by the same factor at the end (kPTruncBias).
-#ifndef XFB_P_ROUND
-template <bool kBf16>
-__device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
-  if constexpr (kBf16) {
-    return __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
-  } else {
-    return pack_pair<false>(lo, hi);
-  }
-}
-template <bool kBf16>
-constexpr float kPTruncBias = kBf16 ? (1.f - 1.f / 512.f) : 1.f;
-#else
-template <bool kBf16>
-__device__ __forceinline__ uint32_t pack_p(float lo, float hi) { return pack_pair<kBf16>(lo, hi); }
-template <bool kBf16>
-constexpr float kPTruncBias = 1.f;
-#endif
 
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const __grid_constant__ Sm100Args a) {
@@ -242,11 +218,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
           *abort_flag = 1;
           break;
         }
-#ifdef XFB_X_NOLOAD
-        if (use > 0) {
-          mbar_arrive(&bar->k_full[st]);
-        } else
-#endif
         {
           mbar_expect_tx(&bar->k_full[st], L::kKV);
 #pragma unroll
@@ -258,11 +229,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
           *abort_flag = 1;
           break;
         }
-#ifdef XFB_X_NOLOAD
-        if (use_v > 0) {
-          mbar_arrive(&bar->v_full[sv]);
-        } else
-#endif
         {
           mbar_expect_tx(&bar->v_full[sv], L::kKV);
 #pragma unroll
@@ -417,14 +383,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     bool ok = true;
     int cnt = 0;
 
-#ifdef XFB_TIMING
-    long long tm_wait = 0, tm_ld = 0, tm_math = 0, tm_st = 0, tm_n = 0, tm_max = 0, tm_tail = 0;
-#endif
     for (int j = jlo[t]; j < jhi[t]; ++j, ++cnt) {
       const int n0 = n_base + j * kBN;
-#ifdef XFB_TIMING
-      const long long c0 = clock64();
-#endif
       ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag);
       if (!ok) {
         atomicExch(a.status, 31 + t);
@@ -432,25 +392,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         break;
       }
       tc_fence_after();
-#ifdef XFB_X_TRIVIAL
-      tc_fence_before();
-      mbar_arrive(&bar->p_full[t]);
-      continue;
-#endif
       uint32_t sr[kBN];
 #pragma unroll
       for (int cblk = 0; cblk < kBN / 32; ++cblk) {
         uint32_t* dst = sr + cblk * 32;
         XFB_TMEM_LD_32(tmem_s + cblk * 32, dst);
       }
-#ifdef XFB_TIMING
-      const long long c1 = clock64();
-#endif
       tc_wait_ld();
-#ifdef XFB_TIMING
-      asm volatile("" ::"r"(sr[0]), "r"(sr[127]) : "memory");
-      const long long c2 = clock64();
-#endif
       float* s = reinterpret_cast<float*>(sr);
 
       const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift) ||
@@ -465,22 +413,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       // row maximum: four independent chains
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-#ifdef XFB_X_NOMAX
-      for (int c = 0; c < 8; c += 8) {
-#else
       for (int c = 0; c < kBN; c += 8) {  // three-input max: two elements per instruction
-#endif
         mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
         mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
         mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
         mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
       }
       const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // scale > 0 (host guarantees)
-#ifdef XFB_TIMING
-      asm volatile("" ::"f"(mx) : "memory");
-      const long long c2m = clock64();
-      tm_max += c2m - c2;
-#endif
       const bool raise = mx > m_run + kRescaleThreshold;  // also true on the first visible key (m_run = -inf)
       const float m_new = raise ? mx : m_run;
       const float alpha = raise ? (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new)) : 1.f;
@@ -507,66 +446,46 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       l_run *= alpha;
       m_run = m_new;
 
-#ifdef XFB_TIMING
-      long long c3 = 0;
-#endif
       // P = exp2(s * scale - m), packed pairs, straight back into tensor memory
       const uint64_t sc2 = f2_pack(sl2, sl2), nm2 = f2_pack(-m_use, -m_use);
-      uint64_t sum2[2] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
       uint32_t pr[kBN / 2];
-#pragma unroll
-      for (int c = 0; c < kBN; c += 4) {
-        float a0, a1, b0, b1;
-        f2_unpack(ffma2(f2_pack(s[c], s[c + 1]), sc2, nm2), a0, a1);
-        f2_unpack(ffma2(f2_pack(s[c + 2], s[c + 3]), sc2, nm2), b0, b1);
-#ifndef XFB_X_NOEXP
-        a0 = fast_exp2(a0);
-        a1 = fast_exp2(a1);
-        b0 = fast_exp2(b0);
-        b1 = fast_exp2(b1);
+      // A lone warp per scheduler hides no latency by itself: the loop is written
+      // in blocks of XFB_EXP_BLOCK independent elements (all FMAs, then all exp2,
+      // then the sums and packs) with four independent sum chains.
+#ifndef XFB_EXP_BLOCK
+#define XFB_EXP_BLOCK 16
 #endif
-        sum2[0] = fadd2(sum2[0], f2_pack(a0, a1));
-        sum2[1] = fadd2(sum2[1], f2_pack(b0, b1));
-        pr[c / 2] = pack_p<kBf16>(a0, a1);
-        pr[c / 2 + 1] = pack_p<kBf16>(b0, b1);
+      constexpr int kEB = XFB_EXP_BLOCK;
+      uint64_t sum2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+#pragma unroll
+      for (int c = 0; c < kBN; c += kEB) {
+        float e[kEB];
+#pragma unroll
+        for (int i = 0; i < kEB; i += 2) f2_unpack(ffma2(f2_pack(s[c + i], s[c + i + 1]), sc2, nm2), e[i], e[i + 1]);
+#pragma unroll
+        for (int i = 0; i < kEB; ++i) e[i] = fast_exp2(e[i]);
+#pragma unroll
+        for (int i = 0; i < kEB; i += 2) {
+          sum2[(i / 2) & 3] = fadd2(sum2[(i / 2) & 3], f2_pack(e[i], e[i + 1]));
+          pr[(c + i) / 2] = pack_pair<kBf16>(e[i], e[i + 1]);
+        }
       }
       {
         float x0, x1, y0, y1;
-        f2_unpack(sum2[0], x0, x1);
-        f2_unpack(sum2[1], y0, y1);
+        f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
+        f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
         l_run += (x0 + x1) + (y0 + y1);
       }
       {
         uint32_t* p0 = pr;
         uint32_t* p1 = pr + 32;
-#ifdef XFB_TIMING
-        asm volatile("" ::"r"(pr[0]), "r"(pr[63]) : "memory");
-        c3 = clock64();
-        tm_wait += c1 - c0, tm_ld += c2 - c1, tm_math += c3 - c2;
-#endif
         XFB_TMEM_ST_32(tmem_s, p0);
         XFB_TMEM_ST_32(tmem_s + 32, p1);
       }
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&bar->p_full[t]);
-#ifdef XFB_TIMING
-      const long long c4 = clock64();
-      tm_st += c4 - c0, tm_n += 1, tm_tail += c4 - c3;
-#endif
     }
-#ifdef XFB_TIMING
-    if (row == 0 && tm_n > 0) {
-      unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.status) + 8;
-      atomicAdd(dbg + 0, (unsigned long long)tm_wait);
-      atomicAdd(dbg + 1, (unsigned long long)tm_ld);
-      atomicAdd(dbg + 2, (unsigned long long)tm_math);
-      atomicAdd(dbg + 3, (unsigned long long)tm_st);
-      atomicAdd(dbg + 4, (unsigned long long)tm_n);
-      atomicAdd(dbg + 5, (unsigned long long)tm_max);
-      atomicAdd(dbg + 6, (unsigned long long)tm_tail);
-    }
-#endif
 
     // ---- epilogue
     const bool have = cnt > 0;
@@ -576,7 +495,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       tc_fence_after();
     }
     const bool valid_row = i_loc < qlen;
-    const float inv = l_run > 0.f ? 1.f / (l_run * kPTruncBias<kBf16>) : 0.f;
+    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     const int64_t o_off = int64_t(tb) * a.os.b + int64_t(q_row0 + i_loc) * a.os.m + int64_t(g) * a.os.g + int64_t(h) * a.os.h;
 #pragma unroll
     for (int cblk = 0; cblk < D / 32; ++cblk) {
