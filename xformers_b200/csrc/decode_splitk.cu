@@ -113,13 +113,474 @@ struct DecStage {
 constexpr int kDecMaxStages = 12;
 constexpr int kDecRingBudget = 212 * 1024;  // bytes of cache in flight per SM
 
+// What a consumer warp needs to know about its CTA.
+struct DecWarp {
+  const uint8_t* qs;          // this warp's staged Q rows (ROWS x D, 16-bit)
+  const uint8_t* stage_base;  // the ring
+  uint64_t* full_bar;
+  uint64_t* empty_bar;
+  uint64_t* q_done_bar;
+  float* mine;  // this warp's slot of the combine area: [ROWS][D + 2]
+  int lane, hw, sub, wph, row0;
+  int chunk_lo, chunk_hi, kv_len, n_tiles;
+  int tok_per_stage, kv_bytes, row_bytes, stages;
+};
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+  uint32_t y;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------
+// 16-bit cache.  Query rows (heads of the GQA group x queries) are the M rows
+// of the MMAs, tokens the N columns of QK^T and the K dimension of PV.
+// Leaves the un-normalised partial (acc, running max, row sum) in w.mine.
+// ---------------------------------------------------------------------------
+template <int D, int MT, bool kBf16>
+__device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp& w) {
+  constexpr int KS = D / 16;  // k-steps of the QK^T product
+  constexpr int NT = D / 8;   // n-tiles of the PV product
+  constexpr int kQRowBytes = D * 2;
+  constexpr int kCmbRow = D + 2;
+  constexpr int kSps = DecStage<D, false>::kSubTiles;
+  const int lane = w.lane, r = lane >> 2, c = lane & 3;
+  const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
+
+  uint32_t qf[MT][KS][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int rr = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int cc = ks * 16 + (lane >> 4) * 8;
+      ldmatrix_x4(qf[mt][ks], smem_u32(w.qs + rr * kQRowBytes + cc * 2));
+    }
+  // Q now lives in registers: release the staging area to the producer
+  __syncwarp();
+  if (lane == 0) mbar_arrive(w.q_done_bar);
+
+  // per-row visibility limit: token t visible iff t < lim
+  int lim[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+      const int row = w.row0 + mt * 16 + r + hlf * 8;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[mt][hlf] = l;
+    }
+
+  float acc[MT][NT][4];
+  float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+  }
+
+  for (int tile = 0; tile < w.n_tiles; ++tile) {
+    const int st = tile % w.stages;
+    if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
+      if (lane == 0) atomicExch(a.status, 2);
+      break;
+    }
+    for (int sp = 0; sp < kSps; ++sp) {
+      const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
+      const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;  // its first token
+      if (t_sub >= w.chunk_hi) continue;
+      const uint8_t* ks_ = w.stage_base + st * 2 * w.kv_bytes;
+      const uint8_t* vs_ = ks_ + w.kv_bytes;
+      const bool ragged = t_sub + 16 > w.chunk_hi;
+
+      // ------------------------------------------------ S = Q K^T (16*MT x 16)
+      float s[MT][2][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
+      {
+        const int tok = usub * 16 + (lane & 7) + (lane >> 4) * 8;
+        const uint32_t kaddr = smem_u32(ks_ + tok * row_bytes + hw * D * 2 + ((lane >> 3) & 1) * 16);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, kaddr + ks * 32);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816<kBf16>(s[mt][0], qf[mt][ks], kf[0], kf[1]);
+            mma_16816<kBf16>(s[mt][1], qf[mt][ks], kf[2], kf[3]);
+          }
+        }
+      }
+
+      // -------------------------------- scale, mask, online softmax (log2 domain)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int t = t_sub + j * 8 + 2 * c + e;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            s[mt][j][e] = t < lim[mt][0] ? s[mt][j][e] * a.scale_log2 : -INFINITY;
+            s[mt][j][2 + e] = t < lim[mt][1] ? s[mt][j][2 + e] * a.scale_log2 : -INFINITY;
+          }
+        }
+
+      uint32_t pa[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        float alpha[2];
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          float mx = fmaxf(fmaxf(s[mt][0][2 * hlf], s[mt][0][2 * hlf + 1]), fmaxf(s[mt][1][2 * hlf], s[mt][1][2 * hlf + 1]));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+          const float m_new = fmaxf(m_run[mt][hlf], mx);
+          const float m_use = m_new == -INFINITY ? 0.f : m_new;
+          alpha[hlf] = fast_exp2(m_run[mt][hlf] - m_use);  // exp2(-inf) = 0 on the first tile
+          m_run[mt][hlf] = m_new;
+          const float p00 = fast_exp2(s[mt][0][2 * hlf] - m_use), p01 = fast_exp2(s[mt][0][2 * hlf + 1] - m_use);
+          const float p10 = fast_exp2(s[mt][1][2 * hlf] - m_use), p11 = fast_exp2(s[mt][1][2 * hlf + 1] - m_use);
+          l_run[mt][hlf] = l_run[mt][hlf] * alpha[hlf] + ((p00 + p01) + (p10 + p11));
+          pa[mt][hlf] = pack2<kBf16>(p00, p01);      // k = 2c, 2c+1   (rows r / r+8)
+          pa[mt][2 + hlf] = pack2<kBf16>(p10, p11);  // k = 2c+8, 2c+9
+        }
+        // rescale the running output only when some row's maximum moved
+        const bool moved = alpha[0] != 1.f || alpha[1] != 1.f;
+        if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            acc[mt][j][0] *= alpha[0];
+            acc[mt][j][1] *= alpha[0];
+            acc[mt][j][2] *= alpha[1];
+            acc[mt][j][3] *= alpha[1];
+          }
+        }
+      }
+
+      // ------------------------------------------------------- O += P V
+      if (ragged) {
+        // rows of tokens past the end were not copied: zero them so that
+        // 0 * garbage cannot produce NaN
+        for (int i = lane; i < 16 * (D / 8); i += 32) {
+          const int tt = i / (D / 8), ch = i % (D / 8);
+          if (t_sub + tt >= w.chunk_hi)
+            *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + (usub * 16 + tt) * row_bytes + hw * D * 2 + ch * 16) = make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+      const int tok = usub * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+      const uint32_t vaddr = smem_u32(vs_ + tok * row_bytes + hw * D * 2 + (lane >> 4) * 16);
+#pragma unroll
+      for (int j = 0; j < NT; j += 2) {
+        uint32_t vf[4];
+        ldmatrix_x4_trans(vf, vaddr + j * 16);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_16816<kBf16>(acc[mt][j], pa[mt], vf[0], vf[1]);
+          mma_16816<kBf16>(acc[mt][j + 1], pa[mt], vf[2], vf[3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&w.empty_bar[st]);
+  }
+
+  // full row sums (each thread of a quad saw 4 of the 16 tokens of a tile)
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+      float l = l_run[mt][hlf];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      l_run[mt][hlf] = l;
+    }
+
+  // the ring is no longer in use once every consumer warp got here
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int rr = mt * 16 + r + (e >> 1) * 8;
+        w.mine[rr * kCmbRow + j * 8 + 2 * c + (e & 1)] = acc[mt][j][e];
+      }
+    if (c == 0) {
+      w.mine[(mt * 16 + r) * kCmbRow + D] = m_run[mt][0];
+      w.mine[(mt * 16 + r) * kCmbRow + D + 1] = l_run[mt][0];
+      w.mine[(mt * 16 + r + 8) * kCmbRow + D] = m_run[mt][1];
+      w.mine[(mt * 16 + r + 8) * kCmbRow + D + 1] = l_run[mt][1];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// int4 row-wise cache.  The products are taken transposed: tokens are the M
+// rows of S^T = K Q^T and the K dimension of O^T = V^T P^T, the query rows
+// (8 per n-tile) are the N columns, so that one 16-token sub-tile costs
+// D/16 + D/16 MMAs per n-tile and no MMA row is padding when the GQA group has
+// 8 query heads.  Nibbles are unpacked in registers straight into A fragments:
+//   K: thread (r, c) reads word 4i + c of tokens r and r + 8; its nibble pairs
+//      (e, e + 4) are the k-slots (2c, 2c+1) / (2c+8, 2c+9) of k-steps 2i and
+//      2i + 1.  Q^T is loaded in the same permuted order of d.
+//   V: thread (r, c) reads words WPT*r + wi of tokens 2c, 2c+1, 2c+8, 2c+9;
+//      two byte permutes pair the same element of neighbouring tokens, so
+//      m-tile wi*4 + e holds d = 8*(WPT*r + wi) + e in row r and d + 4 in row
+//      r + 8.
+// Scale and shift never touch the elements: K's are applied to the scores
+// (with the row sum of q), V's scale is folded into P and its shift, together
+// with the offset 16 of the unpacked nibbles, becomes a per-row correction.
+// P^T reaches the B operand of the second product through movmatrix.
+// ---------------------------------------------------------------------------
+template <int D, int NTQ, bool kBf16>
+__device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp& w) {
+  using T = typename Half2Type<kBf16>::T;
+  constexpr int W = 1 + D / 8;  // words per row (scale/shift word + nibbles)
+  constexpr int KS = D / 16;    // k-steps of K Q^T
+  constexpr int MTV = D / 16;   // m-tiles of V^T P^T
+  constexpr int WPT = D / 64;   // V words per thread and token
+  constexpr int kQRowBytes = D * 2;
+  constexpr int kCmbRow = D + 2;
+  constexpr int kSps = DecStage<D, true>::kSubTiles;
+  const int lane = w.lane, r = lane >> 2, c = lane & 3;
+  const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
+
+  // A nibble n dropped into the top four mantissa bits of 16.0 reads as 16 + n
+  // exactly (bf16: mantissa bits [3,7); f16: bits [6,10)).  The offset is of the
+  // size of the values themselves, so removing it later costs no precision.
+  constexpr uint32_t kMagic = kBf16 ? 0x41804180u : 0x4C004C00u;
+  constexpr uint32_t kNibMask = kBf16 ? 0x00780078u : 0x03C003C0u;
+  constexpr int kNibPos = kBf16 ? 3 : 6;
+  constexpr float kMagicF = 16.f;
+  // nibble pair (e, e+4) of a packed word, e = 0..3, as two 16-bit floats 16+n
+  auto unpack_pair = [](uint32_t x, int e) -> uint32_t {
+    const int sh = 4 * e - kNibPos;  // compile-time after unrolling
+    const uint32_t t = sh >= 0 ? (x >> sh) : (x << (-sh));
+    return (t & kNibMask) | kMagic;
+  };
+
+  // B fragments of Q^T (n = query row nt*8 + r) in the permuted order of d
+  uint32_t qf[NTQ][KS][2];
+  float qsum[NTQ][2];  // sum over d of q[row][d] for the rows 2c, 2c+1 of each n-tile
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+    const T* qrow = reinterpret_cast<const T*>(w.qs + (nt * 8 + r) * kQRowBytes);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const T* q0 = qrow + (4 * (ks >> 1) + c) * 8;
+      const int e0 = (ks & 1) * 2;
+      auto pk = [](const T* p, int i0, int i1) {
+        const uint32_t lo = *reinterpret_cast<const unsigned short*>(p + i0);
+        const uint32_t hi = *reinterpret_cast<const unsigned short*>(p + i1);
+        return lo | (hi << 16);
+      };
+      qf[nt][ks][0] = pk(q0, e0, e0 + 4);
+      qf[nt][ks][1] = pk(q0, e0 + 1, e0 + 5);
+    }
+    float sr = 0.f;  // the quad of row r adds up that row, then rows 2c, 2c+1 are fetched
+    for (int d = c; d < D; d += 4) sr += float(qrow[d]);
+    sr += __shfl_xor_sync(0xffffffffu, sr, 1);
+    sr += __shfl_xor_sync(0xffffffffu, sr, 2);
+    qsum[nt][0] = __shfl_sync(0xffffffffu, sr, 8 * c);
+    qsum[nt][1] = __shfl_sync(0xffffffffu, sr, 8 * c + 4);
+  }
+  // Q now lives in registers: release the staging area to the producer
+  __syncwarp();
+  if (lane == 0) mbar_arrive(w.q_done_bar);
+
+  // per-query-row visibility limit: token t visible iff t < lim
+  int lim[NTQ][2];
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = w.row0 + nt * 8 + 2 * c + e;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
+    }
+
+  float acc[MTV][NTQ][4];
+  float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+    corr[nt][0] = corr[nt][1] = 0.f;
+  }
+
+  for (int tile = 0; tile < w.n_tiles; ++tile) {
+    const int st = tile % w.stages;
+    if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
+      if (lane == 0) atomicExch(a.status, 2);
+      break;
+    }
+    const uint8_t* ks_ = w.stage_base + st * 2 * w.kv_bytes;
+    const uint8_t* vs_ = ks_ + w.kv_bytes;
+#pragma unroll 1
+    for (int sp = 0; sp < kSps; ++sp) {
+      const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
+      const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;  // its first token
+      if (t_sub >= w.chunk_hi) continue;
+      const uint32_t* k0 = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + r) * row_bytes + hw * W * 4);
+      const uint32_t* k1 = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + r + 8) * row_bytes + hw * W * 4);
+      const uint32_t* v0 = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + r) * row_bytes + hw * W * 4);
+      const uint32_t* v1 = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + r + 8) * row_bytes + hw * W * 4);
+
+      // ------------------------------------------- S^T = K Q^T (16 tokens x 8*NTQ)
+      float s[NTQ][4];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < KS / 2; ++i) {
+        const uint32_t w0 = k0[1 + 4 * i + c], w1 = k1[1 + 4 * i + c];
+        const uint32_t ka[4] = {unpack_pair(w0, 0), unpack_pair(w1, 0), unpack_pair(w0, 1), unpack_pair(w1, 1)};
+        const uint32_t kb[4] = {unpack_pair(w0, 2), unpack_pair(w1, 2), unpack_pair(w0, 3), unpack_pair(w1, 3)};
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt) {
+          mma_16816<kBf16>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
+          mma_16816<kBf16>(s[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+        }
+      }
+
+      // ------------------ scale/shift of tokens r, r+8; mask; online softmax
+      const uint32_t kw0 = k0[0], kw1 = k1[0], vw0 = v0[0], vw1 = v1[0];
+      const int t0 = t_sub + r, t1 = t_sub + r + 8;
+      const float ksc0 = half_bits_to_float(kw0 & 0xFFFFu) * a.scale_log2;
+      const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu) * a.scale_log2;
+      const float kof0 = half_bits_to_float(kw0 >> 16) * a.scale_log2 - kMagicF * ksc0;
+      const float kof1 = half_bits_to_float(kw1 >> 16) * a.scale_log2 - kMagicF * ksc1;
+      // tokens past the end were not copied: their scale words are garbage
+      const float vsc0 = t0 < w.chunk_hi ? half_bits_to_float(vw0 & 0xFFFFu) : 0.f;
+      const float vsc1 = t1 < w.chunk_hi ? half_bits_to_float(vw1 & 0xFFFFu) : 0.f;
+      const float vsh0 = t0 < w.chunk_hi ? half_bits_to_float(vw0 >> 16) : 0.f;
+      const float vsh1 = t1 < w.chunk_hi ? half_bits_to_float(vw1 >> 16) : 0.f;
+
+      uint32_t pb[NTQ][2];
+      bool moved = false;
+      float alpha[NTQ][2];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+        float pw0[2], pw1[2], p0[2], p1[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float s0 = t0 < lim[nt][e] ? fmaf(ksc0, s[nt][e], kof0 * qsum[nt][e]) : -INFINITY;
+          const float s1 = t1 < lim[nt][e] ? fmaf(ksc1, s[nt][2 + e], kof1 * qsum[nt][e]) : -INFINITY;
+          float mx = fmaxf(s0, s1);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m_run[nt][e], mx);
+          const float m_use = m_new == -INFINITY ? 0.f : m_new;
+          alpha[nt][e] = fast_exp2(m_run[nt][e] - m_use);  // exp2(-inf) = 0 on the first tile
+          m_run[nt][e] = m_new;
+          p0[e] = fast_exp2(s0 - m_use);
+          p1[e] = fast_exp2(s1 - m_use);
+          pw0[e] = p0[e] * vsc0;
+          pw1[e] = p1[e] * vsc1;
+          moved |= alpha[nt][e] != 1.f;
+        }
+        // fold the V scale into P; the shift and the offset of the unpacked
+        // nibbles become a per-row correction that uses the ROUNDED weights so
+        // that the offset cancels exactly
+        const uint32_t pt0 = pack2<kBf16>(pw0[0], pw0[1]);  // token r,   rows 2c, 2c+1
+        const uint32_t pt1 = pack2<kBf16>(pw1[0], pw1[1]);  // token r+8
+        const float2 r0 = unpack2<kBf16>(pt0), r1 = unpack2<kBf16>(pt1);
+        l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + (p0[0] + p1[0]);
+        l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + (p0[1] + p1[1]);
+        corr[nt][0] = corr[nt][0] * alpha[nt][0] + (fmaf(p0[0], vsh0, p1[0] * vsh1) - kMagicF * (r0.x + r1.x));
+        corr[nt][1] = corr[nt][1] * alpha[nt][1] + (fmaf(p0[1], vsh0, p1[1] * vsh1) - kMagicF * (r0.y + r1.y));
+        pb[nt][0] = movmatrix_trans(pt0);  // tokens 2c, 2c+1   of row r
+        pb[nt][1] = movmatrix_trans(pt1);  // tokens 2c+8, 2c+9 of row r
+      }
+      // rescale the running output only when some row's maximum moved
+      if (__any_sync(0xffffffffu, moved)) {
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+          for (int mt = 0; mt < MTV; ++mt) {
+            acc[mt][nt][0] *= alpha[nt][0];
+            acc[mt][nt][1] *= alpha[nt][1];
+            acc[mt][nt][2] *= alpha[nt][0];
+            acc[mt][nt][3] *= alpha[nt][1];
+          }
+      }
+
+      // ------------------------------------------------- O^T += V^T P^T
+      const uint32_t* va = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + 2 * c) * row_bytes + hw * W * 4) + 1 + WPT * r;
+      const int rw = row_bytes / 4;
+#pragma unroll
+      for (int wi = 0; wi < WPT; ++wi) {
+        const uint32_t x0 = va[wi], x1 = va[rw + wi], x2 = va[8 * rw + wi], x3 = va[9 * rw + wi];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t u0 = unpack_pair(x0, e), u1 = unpack_pair(x1, e);
+          const uint32_t u2 = unpack_pair(x2, e), u3 = unpack_pair(x3, e);
+          const uint32_t vf[4] = {__byte_perm(u0, u1, 0x5410), __byte_perm(u0, u1, 0x7632),
+                                  __byte_perm(u2, u3, 0x5410), __byte_perm(u2, u3, 0x7632)};
+#pragma unroll
+          for (int nt = 0; nt < NTQ; ++nt) mma_16816<kBf16>(acc[wi * 4 + e][nt], vf, pb[nt][0], pb[nt][1]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&w.empty_bar[st]);
+  }
+
+  // full row sums (each thread saw tokens r and r+8 of every sub-tile)
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float l = l_run[nt][e], cs = corr[nt][e];
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, o);
+        cs += __shfl_xor_sync(0xffffffffu, cs, o);
+      }
+      l_run[nt][e] = l;
+      corr[nt][e] = cs;
+    }
+
+  // the ring is no longer in use once every consumer warp got here
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int d = 8 * (WPT * r + (mt >> 2)) + (mt & 3) + (q >> 1) * 4;
+        const int rr = nt * 8 + 2 * c + (q & 1);
+        w.mine[rr * kCmbRow + d] = acc[mt][nt][q] + corr[nt][q & 1];
+      }
+    if (r == 0) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D] = m_run[nt][e];
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D + 1] = l_run[nt][e];
+      }
+    }
+  }
+}
+
 template <int D, int MT, bool kInt4, bool kBf16>
 __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
   using Stage = DecStage<D, kInt4>;
   using T = typename Half2Type<kBf16>::T;
   constexpr int W = 1 + D / 8;  // int4 words per row (one quantisation group)
-  constexpr int KS = D / 16;    // k-steps of the QK^T product
-  constexpr int NT = D / 8;     // n-tiles of the PV product
+  // query rows of one kv head per CTA: MT m-tiles of 16 (16-bit cache) or MT
+  // n-tiles of 8 (int4 cache, transposed products)
+  constexpr int ROWS = kInt4 ? 8 * MT : 16 * MT;
 
   // bytes in flight per SM are what hide HBM latency: the ring takes ~200 KB,
   // i.e. 3 stages of 64 KB (bf16, D = 128) up to 12 stages of 17 KB (int4)
@@ -148,10 +609,10 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
     // pass the rows of an empty sequence still have to be defined: out = 0,
     // lse = -inf.
     if (a.split_k == 1 && split == 0) {
-      const int nrows = min(16 * MT, a.rows - rblk * 16 * MT);
+      const int nrows = min(ROWS, a.rows - rblk * ROWS);
       for (int i = threadIdx.x; i < hb * nrows * D; i += blockDim.x) {
         const int d = i % D, rr = (i / D) % nrows, hh = i / (D * nrows);
-        const int row = rblk * 16 * MT + rr, head = hblk * hb + hh;
+        const int row = rblk * ROWS + rr, head = hblk * hb + hh;
         const int qi = row / a.q_per_kv, h = row % a.q_per_kv;
         const int64_t off = (int64_t(b) * a.mq + qi) * a.o_sm + int64_t(head) * a.o_sg + int64_t(h) * a.o_sh + d;
         if (a.out_dtype == XFB200_F32)
@@ -253,15 +714,14 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
   const int hw = warp % hb;   // kv head of this warp inside the block
   const int sub = warp / hb;  // 16-token sub-tile of each stage
   const int head = hblk * hb + hw;
-  const int r = lane >> 2, c = lane & 3;
-  const int row0 = rblk * 16 * MT;  // first query row (of this kv head) handled here
+  const int row0 = rblk * ROWS;  // first query row (of this kv head) handled here
   const int R = a.rows;
 
   // ---- stage Q (this warp's head) in shared memory, zero rows beyond R
   {
-    uint8_t* qs = q_smem + warp * (16 * MT) * kQRowBytes;
+    uint8_t* qs = q_smem + warp * ROWS * kQRowBytes;
     const T* qg = reinterpret_cast<const T*>(a.q);
-    for (int i = lane; i < 16 * MT * (D / 8); i += 32) {
+    for (int i = lane; i < ROWS * (D / 8); i += 32) {
       const int rr = i / (D / 8), ch = i % (D / 8);
       const int row = row0 + rr;
       uint4 val = make_uint4(0, 0, 0, 0);
@@ -274,359 +734,36 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __g
     }
     __syncwarp();
   }
-  const uint8_t* qs = q_smem + warp * (16 * MT) * kQRowBytes;
-
-  // A fragments of Q.  Plain cache: natural k order.  int4 cache: k-slot
-  // (ks, 2c+e [+8]) of thread c <-> d = 8*(4*(ks/2)... see kperm() below.
-  uint32_t qf[MT][KS][4];
-  float qsum[MT][2];  // int4: sum over d of q[row][d] (rows r, r+8)
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) qsum[mt][0] = qsum[mt][1] = 0.f;
-  if constexpr (!kInt4) {
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int rr = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const int cc = ks * 16 + (lane >> 4) * 8;
-        ldmatrix_x4(qf[mt][ks], smem_u32(qs + rr * kQRowBytes + cc * 2));
-      }
-  } else {
-    // Thread c unpacks words c, c+4, c+8, ... of a K row; word i (= 4*j + c)
-    // feeds k-steps 2j and 2j+1: k-step 2j holds elements (0,4 | 1,5), k-step
-    // 2j+1 holds (2,6 | 3,7) of that word.  Q must use the same order.
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int word = 4 * (ks >> 1) + c;
-        const int e0 = (ks & 1) * 2;
-        const T* q0 = reinterpret_cast<const T*>(qs + (mt * 16 + r) * kQRowBytes) + word * 8;
-        const T* q1 = reinterpret_cast<const T*>(qs + (mt * 16 + r + 8) * kQRowBytes) + word * 8;
-        auto pk = [](const T* p, int i0, int i1) {
-          uint32_t lo = *reinterpret_cast<const unsigned short*>(p + i0);
-          uint32_t hi = *reinterpret_cast<const unsigned short*>(p + i1);
-          return lo | (hi << 16);
-        };
-        qf[mt][ks][0] = pk(q0, e0, e0 + 4);
-        qf[mt][ks][1] = pk(q1, e0, e0 + 4);
-        qf[mt][ks][2] = pk(q0, e0 + 1, e0 + 5);
-        qf[mt][ks][3] = pk(q1, e0 + 1, e0 + 5);
-      }
-    // row sums over all d (every thread of a quad needs them for its rows)
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-      const T* q0 = reinterpret_cast<const T*>(qs + (mt * 16 + r) * kQRowBytes);
-      const T* q1 = reinterpret_cast<const T*>(qs + (mt * 16 + r + 8) * kQRowBytes);
-      float s0 = 0.f, s1 = 0.f;
-      for (int d = c; d < D; d += 4) {
-        s0 += float(q0[d]);
-        s1 += float(q1[d]);
-      }
-      s0 += __shfl_xor_sync(0xffffffffu, s0, 1);
-      s0 += __shfl_xor_sync(0xffffffffu, s0, 2);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, 2);
-      qsum[mt][0] = s0;
-      qsum[mt][1] = s1;
-    }
-  }
-
-  // Q now lives in registers: release the staging area to the producer
-  __syncwarp();
-  if (lane == 0) mbar_arrive(&q_done_bar);
-
-  // per-row visibility limit: token t visible iff t < lim
-  int lim[MT][2];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int hlf = 0; hlf < 2; ++hlf) {
-      const int row = row0 + mt * 16 + r + hlf * 8;
-      int l = chunk_hi;
-      if (a.causal && row < R) l = min(l, kv_len - a.mq + row / a.q_per_kv + 1);
-      lim[mt][hlf] = l;
-    }
-
-  float acc[MT][NT][4];
-  float m_run[MT][2], l_run[MT][2], corr[MT][2];
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-    for (int j = 0; j < NT; ++j) acc[mt][j][0] = acc[mt][j][1] = acc[mt][j][2] = acc[mt][j][3] = 0.f;
-    m_run[mt][0] = m_run[mt][1] = -INFINITY;
-    l_run[mt][0] = l_run[mt][1] = 0.f;
-    corr[mt][0] = corr[mt][1] = 0.f;
-  }
-  // A nibble n dropped into the top four mantissa bits of 16.0 reads as 16 + n
-  // exactly (bf16: mantissa bits [3,7); f16: bits [6,10)).  The offset is of the
-  // size of the values themselves, so removing it later costs no precision.
-  constexpr uint32_t kMagic = kBf16 ? 0x41804180u : 0x4C004C00u;
-  constexpr uint32_t kNibMask = kBf16 ? 0x00780078u : 0x03C003C0u;
-  constexpr int kNibPos = kBf16 ? 3 : 6;
-  constexpr float kMagicF = 16.f;
-  // nibble pair (e, e+4) of a packed word, e = 0..3, as two 16-bit floats 16+n
-  auto unpack_pair = [](uint32_t w, int e) -> uint32_t {
-    const int sh = 4 * e - kNibPos;  // compile-time after unrolling
-    const uint32_t t = sh >= 0 ? (w >> sh) : (w << (-sh));
-    return (t & kNibMask) | kMagic;
-  };
-
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const int st = tile % kDecStages;
-    if (!mbar_wait(&full_bar[st], (tile / kDecStages) & 1)) {
-      if (lane == 0) atomicExch(a.status, 2);
-      break;
-    }
-    for (int sp = 0; sp < kSps; ++sp) {
-    const int usub = sub + wph * sp;                      // this warp's sub-tile of the stage
-    const int t_sub = chunk_lo + tile * TOK + usub * 16;  // its first token
-    if (t_sub < chunk_hi) {
-      const uint8_t* ks_ = stage_base + st * 2 * kv_bytes;
-      const uint8_t* vs_ = ks_ + kv_bytes;
-      const bool ragged = t_sub + 16 > chunk_hi;
-
-      // ------------------------------------------------ S = Q K^T (16*MT x 16)
-      float s[MT][2][4];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
-
-      if constexpr (!kInt4) {
-        const int tok = usub * 16 + (lane & 7) + (lane >> 4) * 8;
-        const uint32_t kaddr = smem_u32(ks_ + tok * row_bytes + hw * D * 2 + ((lane >> 3) & 1) * 16);
-#pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-          uint32_t kf[4];
-          ldmatrix_x4(kf, kaddr + ks * 32);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            mma_16816<kBf16>(s[mt][0], qf[mt][ks], kf[0], kf[1]);
-            mma_16816<kBf16>(s[mt][1], qf[mt][ks], kf[2], kf[3]);
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const uint32_t* krow = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + j * 8 + r) * row_bytes + hw * W * 4) + 1;
-#pragma unroll
-          for (int i = 0; i < KS / 2; ++i) {
-            const uint32_t w = krow[4 * i + c];
-            const uint32_t b00 = unpack_pair(w, 0);  // elements 0,4
-            const uint32_t b01 = unpack_pair(w, 1);  // elements 1,5
-            const uint32_t b10 = unpack_pair(w, 2);  // elements 2,6
-            const uint32_t b11 = unpack_pair(w, 3);  // elements 3,7
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              mma_16816<kBf16>(s[mt][j], qf[mt][2 * i], b00, b01);
-              mma_16816<kBf16>(s[mt][j], qf[mt][2 * i + 1], b10, b11);
-            }
-          }
-        }
-      }
-
-      // -------------------------------- scale, mask, online softmax (log2 domain)
-      float vsc[2][2] = {{1.f, 1.f}, {1.f, 1.f}}, vsh[2][2] = {{0.f, 0.f}, {0.f, 0.f}};  // V scale/shift of tokens (j, 2c+e)
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int tl = usub * 16 + j * 8 + 2 * c + e;
-          const int t = t_sub + j * 8 + 2 * c + e;
-          if constexpr (kInt4) {
-            const uint32_t kw = *reinterpret_cast<const uint32_t*>(ks_ + tl * row_bytes + hw * W * 4);
-            const uint32_t vw = *reinterpret_cast<const uint32_t*>(vs_ + tl * row_bytes + hw * W * 4);
-            const float ksc = half_bits_to_float(kw & 0xFFFFu), ksh = half_bits_to_float(kw >> 16);
-            const bool tv = t < chunk_hi;
-            vsc[j][e] = tv ? half_bits_to_float(vw & 0xFFFFu) : 0.f;
-            vsh[j][e] = tv ? half_bits_to_float(vw >> 16) : 0.f;
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              s[mt][j][e] = ksc * s[mt][j][e] + (ksh - kMagicF * ksc) * qsum[mt][0];
-              s[mt][j][2 + e] = ksc * s[mt][j][2 + e] + (ksh - kMagicF * ksc) * qsum[mt][1];
-            }
-          }
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            s[mt][j][e] = t < lim[mt][0] ? s[mt][j][e] * a.scale_log2 : -INFINITY;
-            s[mt][j][2 + e] = t < lim[mt][1] ? s[mt][j][2 + e] * a.scale_log2 : -INFINITY;
-          }
-        }
-
-      uint32_t pa[MT][4];
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        float alpha[2];
-#pragma unroll
-        for (int hlf = 0; hlf < 2; ++hlf) {
-          float mx = fmaxf(fmaxf(s[mt][0][2 * hlf], s[mt][0][2 * hlf + 1]), fmaxf(s[mt][1][2 * hlf], s[mt][1][2 * hlf + 1]));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-          const float m_new = fmaxf(m_run[mt][hlf], mx);
-          const float m_use = m_new == -INFINITY ? 0.f : m_new;
-          alpha[hlf] = fast_exp2(m_run[mt][hlf] - m_use);  // exp2(-inf) = 0 on the first tile
-          m_run[mt][hlf] = m_new;
-          float psum = 0.f, csum = 0.f;
-          float p[2][2];
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float pv = fast_exp2(s[mt][j][2 * hlf + e] - m_use);
-              psum += pv;
-              if constexpr (kInt4) {
-                // fold the V scale into P; the shift (and the 2^k offset of the
-                // unpacked nibbles) becomes a per-row correction that uses the
-                // ROUNDED weight so that the offset cancels exactly
-                const float pw = pv * vsc[j][e];
-                const uint32_t one = pack2<kBf16>(pw, 0.f);
-                const float pw_r = unpack2<kBf16>(one).x;
-                csum += pv * vsh[j][e] - kMagicF * pw_r;
-                p[j][e] = pw;
-              } else {
-                p[j][e] = pv;
-              }
-            }
-          l_run[mt][hlf] = l_run[mt][hlf] * alpha[hlf] + psum;
-          corr[mt][hlf] = corr[mt][hlf] * alpha[hlf] + csum;
-          pa[mt][hlf] = pack2<kBf16>(p[0][0], p[0][1]);      // k = 2c, 2c+1   (rows r / r+8)
-          pa[mt][2 + hlf] = pack2<kBf16>(p[1][0], p[1][1]);  // k = 2c+8, 2c+9
-        }
-        // rescale the running output only when some row's maximum moved
-        const bool moved = alpha[0] != 1.f || alpha[1] != 1.f;
-        if (__any_sync(0xffffffffu, moved)) {
-#pragma unroll
-          for (int j = 0; j < NT; ++j) {
-            acc[mt][j][0] *= alpha[0];
-            acc[mt][j][1] *= alpha[0];
-            acc[mt][j][2] *= alpha[1];
-            acc[mt][j][3] *= alpha[1];
-          }
-        }
-      }
-
-      // ------------------------------------------------------- O += P V
-      if constexpr (!kInt4) {
-        if (ragged) {
-          // rows of tokens past the end were not copied: zero them so that
-          // 0 * garbage cannot produce NaN
-          for (int i = lane; i < 16 * (D / 8); i += 32) {
-            const int tt = i / (D / 8), ch = i % (D / 8);
-            if (t_sub + tt >= chunk_hi)
-              *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + (usub * 16 + tt) * row_bytes + hw * D * 2 + ch * 16) = make_uint4(0, 0, 0, 0);
-          }
-          __syncwarp();
-        }
-        const int tok = usub * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        const uint32_t vaddr = smem_u32(vs_ + tok * row_bytes + hw * D * 2 + (lane >> 4) * 16);
-#pragma unroll
-        for (int j = 0; j < NT; j += 2) {
-          uint32_t vf[4];
-          ldmatrix_x4_trans(vf, vaddr + j * 16);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            mma_16816<kBf16>(acc[mt][j], pa[mt], vf[0], vf[1]);
-            mma_16816<kBf16>(acc[mt][j + 1], pa[mt], vf[2], vf[3]);
-          }
-        }
-      } else {
-        // Thread (r, c) unpacks words 2r', 2r'+1 ... of tokens 2c, 2c+1, 2c+8,
-        // 2c+9: virtual output column (n-tile j, col r) <-> d = (D/8)*r + j.
-        constexpr int WPT = D / 64;  // words per thread and token (2 for D = 128)
-#pragma unroll
-        for (int wi = 0; wi < WPT; ++wi) {
-          uint32_t x[4][4];  // [token 2c,2c+1,2c+8,2c+9][element pair i,(i+4)]
-#pragma unroll
-          for (int tk = 0; tk < 4; ++tk) {
-            const int tl = usub * 16 + 2 * c + (tk & 1) + (tk >> 1) * 8;
-            const uint32_t w = *(reinterpret_cast<const uint32_t*>(vs_ + tl * row_bytes + hw * W * 4) + 1 + WPT * r + wi);
-            x[tk][0] = unpack_pair(w, 0);
-            x[tk][1] = unpack_pair(w, 1);
-            x[tk][2] = unpack_pair(w, 2);
-            x[tk][3] = unpack_pair(w, 3);
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            // element i (low halves) and element i+4 (high halves) of this word
-            const uint32_t b0_lo = __byte_perm(x[0][i], x[1][i], 0x5410);
-            const uint32_t b1_lo = __byte_perm(x[2][i], x[3][i], 0x5410);
-            const uint32_t b0_hi = __byte_perm(x[0][i], x[1][i], 0x7632);
-            const uint32_t b1_hi = __byte_perm(x[2][i], x[3][i], 0x7632);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-              mma_16816<kBf16>(acc[mt][wi * 8 + i], pa[mt], b0_lo, b1_lo);
-              mma_16816<kBf16>(acc[mt][wi * 8 + i + 4], pa[mt], b0_hi, b1_hi);
-            }
-          }
-        }
-      }
-    }
-    }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[st]);
-  }
-
-  // ------------------------------------------------------------- epilogue
-  // full row sums (each thread of a quad saw 4 of the 16 tokens of a tile)
-#pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int hlf = 0; hlf < 2; ++hlf) {
-      float l = l_run[mt][hlf], cs = corr[mt][hlf];
-      l += __shfl_xor_sync(0xffffffffu, l, 1);
-      l += __shfl_xor_sync(0xffffffffu, l, 2);
-      cs += __shfl_xor_sync(0xffffffffu, cs, 1);
-      cs += __shfl_xor_sync(0xffffffffu, cs, 2);
-      l_run[mt][hlf] = l;
-      corr[mt][hlf] = cs;
-    }
-
-  // Combine the warps that share a kv head through shared memory (the ring is
-  // no longer in use once every consumer warp got here).
-  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
-  float* cmb = reinterpret_cast<float*>(smem_raw);  // [warp][16*MT][D + 2]  (acc, m, l)
+  // Partial results of the warps meet in shared memory once the ring is drained.
+  float* cmb = reinterpret_cast<float*>(smem_raw);  // [warp][ROWS][D + 2]  (acc, m, l)
   constexpr int kCmbRow = D + 2;
-  {
-    float* mine = cmb + size_t(warp) * (16 * MT) * kCmbRow;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
-#pragma unroll
-      for (int j = 0; j < NT; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int rr = mt * 16 + r + (e >> 1) * 8;
-          const int col = 2 * c + (e & 1);
-          const int d = kInt4 ? (D / 8) * col + j : j * 8 + col;
-          float val = acc[mt][j][e];
-          if constexpr (kInt4) val += corr[mt][e >> 1];
-          mine[rr * kCmbRow + d] = val;
-        }
-      }
-      if (c == 0) {
-        mine[(mt * 16 + r) * kCmbRow + D] = m_run[mt][0];
-        mine[(mt * 16 + r) * kCmbRow + D + 1] = l_run[mt][0];
-        mine[(mt * 16 + r + 8) * kCmbRow + D] = m_run[mt][1];
-        mine[(mt * 16 + r + 8) * kCmbRow + D + 1] = l_run[mt][1];
-      }
-    }
-  }
+  DecWarp w;
+  w.qs = q_smem + warp * ROWS * kQRowBytes;
+  w.stage_base = stage_base;
+  w.full_bar = full_bar, w.empty_bar = empty_bar, w.q_done_bar = &q_done_bar;
+  w.mine = cmb + size_t(warp) * ROWS * kCmbRow;
+  w.lane = lane, w.hw = hw, w.sub = sub, w.wph = wph, w.row0 = row0;
+  w.chunk_lo = chunk_lo, w.chunk_hi = chunk_hi, w.kv_len = kv_len, w.n_tiles = n_tiles;
+  w.tok_per_stage = TOK, w.kv_bytes = kv_bytes, w.row_bytes = row_bytes, w.stages = kDecStages;
+  if constexpr (kInt4)
+    consume_int4<D, MT, kBf16>(a, w);
+  else
+    consume_plain<D, MT, kBf16>(a, w);
   asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
-
   // warps of head hw share the rows: warp `sub` finalises rows sub, sub+wph, ...
   const bool direct = a.split_k == 1;
-  for (int rr = sub; rr < 16 * MT; rr += wph) {
+  for (int rr = sub; rr < ROWS; rr += wph) {
     const int row = row0 + rr;
     if (row >= R) break;
     float mx = -INFINITY;
-    for (int w2 = 0; w2 < wph; ++w2) mx = fmaxf(mx, cmb[size_t(w2 * hb + hw) * (16 * MT) * kCmbRow + rr * kCmbRow + D]);
+    for (int w2 = 0; w2 < wph; ++w2) mx = fmaxf(mx, cmb[size_t(w2 * hb + hw) * ROWS * kCmbRow + rr * kCmbRow + D]);
     const float m_use = mx == -INFINITY ? 0.f : mx;
     float den = 0.f;
     float o[D / 32];
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) o[i] = 0.f;
     for (int w2 = 0; w2 < wph; ++w2) {
-      const float* src = cmb + size_t(w2 * hb + hw) * (16 * MT) * kCmbRow + rr * kCmbRow;
+      const float* src = cmb + size_t(w2 * hb + hw) * ROWS * kCmbRow + rr * kCmbRow;
       const float mw = src[D];
       if (mw == -INFINITY) continue;
       const float wgt = fast_exp2(mw - m_use);
@@ -756,9 +893,10 @@ int decode_chunk_tokens(int kv_bound, int split_k) {
 template <int D, int MT, bool kInt4, bool kBf16>
 static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
   using Stage = DecStage<D, kInt4>;
+  constexpr int ROWS = kInt4 ? 8 * MT : 16 * MT;
   const size_t stage_bytes = 2 * size_t(Stage::kv_bytes(a_in.hb));
-  const size_t qbytes = size_t(kDecConsumerWarps) * 16 * MT * (D * 2);
-  const size_t cmb = size_t(kDecConsumerWarps) * 16 * MT * (D + 2) * 4;
+  const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
+  const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
   int stages = int(kDecRingBudget / stage_bytes);
   stages = stages > kDecMaxStages ? kDecMaxStages : stages;
   const int q_stages = int((qbytes + stage_bytes - 1) / stage_bytes);
@@ -827,8 +965,10 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (p->mask_type != XFB200_MASK_NONE && p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT)
     return set_error(XFB200_E_UNSUPPORTED, "decode: mask_type %d", p->mask_type);
   const int R = p->mq * p->q_per_kv;
-  const int mt = R <= 16 ? 1 : 2;
-  const int row_blocks = (R + 16 * mt - 1) / (16 * mt);
+  // query rows of one kv head per CTA: 16 or 32 (16-bit cache), 8 or 16 (int4 cache)
+  const int tile_rows = int4 ? 8 : 16;
+  const int mt = R <= tile_rows ? 1 : 2;
+  const int row_blocks = (R + tile_rows * mt - 1) / (tile_rows * mt);
   if (p->split_k > 1 && p->scratch == nullptr) return set_error(XFB200_E_INVALID, "decode: split_k > 1 needs scratch");
   if (p->split_k > 1 && (reinterpret_cast<uintptr_t>(p->scratch) & 255)) return set_error(XFB200_E_INVALID, "decode: scratch must be 256-B aligned");
 
@@ -874,6 +1014,16 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   } else if (heads_contig && al16(p->k_stride_m) && al16(p->v_stride_m) && al16(int64_t(hb) * head_elems) &&
              al16(a.k_sg * hb) && al16(a.v_sg * hb)) {
     a.copy_mode = 0;
+    // The copy engine's throughput is set by the number of copies, not by
+    // their bytes, and a packed token stripe is only hb * 68 B: when the
+    // tokens of a page (or of the padded row) follow one another in memory,
+    // copy runs of up to 64 tokens at once.
+    if (int4 && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
+      const int span = p->block_tables ? p->page_size : p->kv_padding;
+      int g = 64;
+      while (g > 1 && span % g) g >>= 1;
+      a.copy_group = g;
+    }
   } else if (al16(p->k_stride_m) && al16(p->v_stride_m) && al16(a.k_sg) && al16(a.v_sg) && al16(head_elems)) {
     a.copy_mode = 1;
   } else if (int4 && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
