@@ -202,6 +202,44 @@ def test_paged_invariances(B, max_t, page, quant):
 
 @gpu
 @pytest.mark.parametrize("quant", [False, True])
+@pytest.mark.parametrize("split_k", [None, 1, 3])
+@pytest.mark.parametrize("page", [32, 64, 256])
+@pytest.mark.parametrize("kv_heads,group", [(8, 8), (4, 4), (2, 16), (3, 8)])
+def test_paged_gqa_several_kv_heads(kv_heads, group, page, split_k, quant):
+    """Serving layout of benchmarks/benchmark_attn_decoding.py:241-306: several
+    kv heads interleaved in every token row (so runs of tokens are contiguous
+    in memory), query heads of a group broadcast with stride 0, paged cache."""
+    require_cuda()
+    dtype, D, B, max_t = torch.bfloat16, 128, 3, 1536
+    g = torch.Generator().manual_seed(77)
+    lens = [max_t, 1, 700]
+    q = torch.randn(1, B, kv_heads, group, D, generator=g).to(dtype).cuda()
+    kf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
+    vf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
+    if quant:
+        k_pad, v_pad = oracle.quantize_kv_int4(kf), oracle.quantize_kv_int4(vf)
+        k_ref, v_ref = oracle.dequantize_kv_int4(k_pad), oracle.dequantize_kv_int4(v_pad)
+    else:
+        k_pad, v_pad = kf.to(dtype), vf.to(dtype)
+        k_ref, v_ref = k_pad.float(), v_pad.float()
+    expand = lambda t: t.expand(-1, -1, -1, group, -1)
+    pad_bias = ab.BlockDiagonalPaddedKeysMask.from_seqlens([1] * B, max_t, lens, device="cuda")
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), expand(k_ref), expand(v_ref), pad_bias.to("cpu"))
+    pages_per_seq = max_t // page
+    n_pages = B * pages_per_seq
+    perm = torch.randperm(n_pages, generator=g).int().view(B, pages_per_seq)
+    k_pg = oracle.scatter_to_pages(k_pad, perm, page, [max_t] * B, max_t, n_pages)
+    v_pg = oracle.scatter_to_pages(v_pad, perm, page, [max_t] * B, max_t, n_pages)
+    bias = pad_bias.make_paged(perm.cuda(), page, ab.PagedBlockDiagonalPaddedKeysMask)
+    op = S.FwOp if split_k is None else type("Op", (S.FwOp,), {"SPLIT_K": split_k})
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, expand(k_pg.cuda()), expand(v_pg.cuda()), bias, op=op)
+    assert_o_lse(out, lse, ro, rl, dtype, f"paged kv_heads={kv_heads}")
+    out_pad, lse_pad = fmha.memory_efficient_attention_forward_requires_grad(q, expand(k_pad.cuda()), expand(v_pad.cuda()), pad_bias, op=op)
+    assert torch.equal(out, out_pad) and torch.equal(lse, lse_pad), "page placement must not change a single bit"
+
+
+@gpu
+@pytest.mark.parametrize("quant", [False, True])
 def test_nans_in_padding_do_not_leak(quant):
     # tests/test_mem_eff_attention.py:3036-3163
     require_cuda()

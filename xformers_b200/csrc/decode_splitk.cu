@@ -101,9 +101,9 @@ struct DecStage {
   // int4 : one row per token = hb heads * (1 + D/8) words, unpadded
   __host__ __device__ static int row_bytes(int hb) { return kInt4 ? hb * (1 + D / 8) * 4 : hb * D * 2 + 16; }
   // sub-tiles of 16 tokens each warp takes from one stage: the packed cache is 4x
-  // denser, so its stages hold 4x the tokens to keep the per-stage overhead
+  // denser, so its stages hold more tokens to keep the per-stage overhead
   // (barrier round trip, page-table look-ups of the producer) off the critical path
-  static constexpr int kSubTiles = kInt4 ? 4 : 1;
+  static constexpr int kSubTiles = kInt4 ? 2 : 1;
   __host__ __device__ static int tokens(int hb) { return 16 * kSubTiles * (kDecConsumerWarps / hb); }
   __host__ __device__ static int kv_bytes(int hb) {  // K or V part of a stage, rounded to 128 B
     return (row_bytes(hb) * tokens(hb) + 127) & ~127;
@@ -111,7 +111,15 @@ struct DecStage {
 };
 
 constexpr int kDecMaxStages = 12;
-constexpr int kDecRingBudget = 212 * 1024;  // bytes of cache in flight per SM
+// Bytes of cache in flight per SM are what hide the HBM latency.  The 16-bit
+// kernel runs one CTA per SM with a ~212 KB ring.  The int4 kernel does 4x the
+// arithmetic per byte and each warp's sub-tile is one long dependency chain, so
+// it runs two CTAs per SM (twice the warps to interleave) with half the ring each.
+template <bool kInt4>
+struct DecOccupancy {
+  static constexpr int kCtasPerSm = kInt4 ? 2 : 1;
+  static constexpr int kRingBudget = kInt4 ? 106 * 1024 : 212 * 1024;
+};
 
 // What a consumer warp needs to know about its CTA.
 struct DecWarp {
@@ -322,22 +330,36 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
 }
 
 // ---------------------------------------------------------------------------
-// int4 row-wise cache.  The products are taken transposed: tokens are the M
-// rows of S^T = K Q^T and the K dimension of O^T = V^T P^T, the query rows
-// (8 per n-tile) are the N columns, so that one 16-token sub-tile costs
-// D/16 + D/16 MMAs per n-tile and no MMA row is padding when the GQA group has
-// 8 query heads.  Nibbles are unpacked in registers straight into A fragments:
-//   K: thread (r, c) reads word 4i + c of tokens r and r + 8; its nibble pairs
-//      (e, e + 4) are the k-slots (2c, 2c+1) / (2c+8, 2c+9) of k-steps 2i and
-//      2i + 1.  Q^T is loaded in the same permuted order of d.
-//   V: thread (r, c) reads words WPT*r + wi of tokens 2c, 2c+1, 2c+8, 2c+9;
-//      two byte permutes pair the same element of neighbouring tokens, so
-//      m-tile wi*4 + e holds d = 8*(WPT*r + wi) + e in row r and d + 4 in row
-//      r + 8.
-// Scale and shift never touch the elements: K's are applied to the scores
-// (with the row sum of q), V's scale is folded into P and its shift, together
-// with the offset 16 of the unpacked nibbles, becomes a per-row correction.
-// P^T reaches the B operand of the second product through movmatrix.
+// int4 row-wise cache.  The integer pipe that unpacks the nibbles is what
+// bounds this path, so everything is arranged to spend as few logic
+// operations per nibble as possible:
+//  * The products are taken transposed: tokens are the M rows of S^T = K Q^T
+//    and the K dimension of O^T = V^T P^T, the query rows (8 per n-tile) are
+//    the N columns.  One 16-token sub-tile costs D/16 + D/16 MMAs per n-tile
+//    and no MMA row is padding when the GQA group has 8 query heads.
+//  * Both products run in f16 whatever the type of Q.  With 10 mantissa bits a
+//    nibble can be read where it already sits: (w & 0x000F000F) | 0x64006400
+//    is the pair (1024 + n_e, 1024 + n_{e+4}) and (w & 0x00F000F0) | 0x64006400
+//    the pair (1024 + 16 n), so a word costs one shift (w >> 8, for the upper
+//    byte of each half) and four logic operations.  One half2 subtraction or
+//    fused multiply-add per pair, on the otherwise idle FMA pipe, brings the
+//    values back to exactly n, so the accumulators never see the offset.
+//    bf16 queries are converted to f16 after scaling each row by a power of
+//    two that keeps it below 2^15; the factor returns with the softmax scale.
+//  * K: thread (r, c) reads word 4i + c of tokens r and r + 8; its nibble pairs
+//    (e, e + 4) are the k-slots (2c, 2c+1) / (2c+8, 2c+9) of k-steps 2i and
+//    2i + 1.  Q^T is loaded in the same permuted order of d.
+//  * V: thread (r, c) reads words WPT*r + wi of tokens 2c, 2c+1, 2c+8, 2c+9;
+//    a byte permute first puts the same half-word of two neighbouring tokens
+//    side by side, so that unpacking yields A-fragment registers directly:
+//    m-tile wi*4 + e holds d = 8*(WPT*r + wi) + e in row r, d + 4 in row r + 8.
+//  * K's scale and shift are applied to the scores (shift times the row sum
+//    of q), V's scale is folded into P and its shift is a per-row term
+//    sum_t p_t * shift_t added at the end.  P^T reaches the B operand of the
+//    second product through movmatrix.
+//  * The running maximum is refreshed (cross-lane reduction, rescaling) only
+//    when some score exceeds it by more than 2^8; otherwise probabilities are
+//    taken against the stale maximum, which is exact in floating point.
 // ---------------------------------------------------------------------------
 template <int D, int NTQ, bool kBf16>
 __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp& w) {
@@ -349,47 +371,66 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   constexpr int kQRowBytes = D * 2;
   constexpr int kCmbRow = D + 2;
   constexpr int kSps = DecStage<D, true>::kSubTiles;
+  // log2 of the largest probability taken against a stale maximum; P * scale(V)
+  // is an f16 value, so 2^kLazy * scale must stay below 65504
+  constexpr float kLazy = 4.f;
   const int lane = w.lane, r = lane >> 2, c = lane & 3;
   const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
 
-  // A nibble n dropped into the top four mantissa bits of 16.0 reads as 16 + n
-  // exactly (bf16: mantissa bits [3,7); f16: bits [6,10)).  The offset is of the
-  // size of the values themselves, so removing it later costs no precision.
-  constexpr uint32_t kMagic = kBf16 ? 0x41804180u : 0x4C004C00u;
-  constexpr uint32_t kNibMask = kBf16 ? 0x00780078u : 0x03C003C0u;
-  constexpr int kNibPos = kBf16 ? 3 : 6;
-  constexpr float kMagicF = 16.f;
-  // nibble pair (e, e+4) of a packed word, e = 0..3, as two 16-bit floats 16+n
-  auto unpack_pair = [](uint32_t x, int e) -> uint32_t {
-    const int sh = 4 * e - kNibPos;  // compile-time after unrolling
-    const uint32_t t = sh >= 0 ? (x >> sh) : (x << (-sh));
-    return (t & kNibMask) | kMagic;
+  // nibble pairs (e, e+4), e = 0..3, of a packed word as two f16 values n
+  auto unpack4 = [](uint32_t x, uint32_t (&out)[4]) {
+    constexpr uint32_t kMagic = 0x64006400u;                   // 1024.0 | 1024.0
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 k64 = __half2half2(__ushort_as_half(0x5400));   // 64.0
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));  // 1/16
+    const uint32_t hi = x >> 8;
+    uint32_t v0 = (x & 0x000F000Fu) | kMagic, v1 = (x & 0x00F000F0u) | kMagic;
+    uint32_t v2 = (hi & 0x000F000Fu) | kMagic, v3 = (hi & 0x00F000F0u) | kMagic;
+    __half2 h0 = __hsub2(*reinterpret_cast<__half2*>(&v0), k1024);
+    __half2 h1 = __hfma2(*reinterpret_cast<__half2*>(&v1), k16th, __hneg2(k64));
+    __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&v2), k1024);
+    __half2 h3 = __hfma2(*reinterpret_cast<__half2*>(&v3), k16th, __hneg2(k64));
+    out[0] = *reinterpret_cast<uint32_t*>(&h0);
+    out[1] = *reinterpret_cast<uint32_t*>(&h1);
+    out[2] = *reinterpret_cast<uint32_t*>(&h2);
+    out[3] = *reinterpret_cast<uint32_t*>(&h3);
   };
 
-  // B fragments of Q^T (n = query row nt*8 + r) in the permuted order of d
+  // B fragments of Q^T (n = query row nt*8 + r) in the permuted order of d, as
+  // f16 of q * 2^-k with k chosen per row so that nothing overflows
   uint32_t qf[NTQ][KS][2];
-  float qsum[NTQ][2];  // sum over d of q[row][d] for the rows 2c, 2c+1 of each n-tile
+  float qsum[NTQ][2];  // sum over d of the scaled q, for the rows 2c, 2c+1 of each n-tile
+  float qfac[NTQ][2];  // 2^k * softmax scale * log2(e) of those rows
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt) {
     const T* qrow = reinterpret_cast<const T*>(w.qs + (nt * 8 + r) * kQRowBytes);
+    float amax = 0.f;
+    for (int d = c; d < D; d += 4) amax = fmaxf(amax, fabsf(float(qrow[d])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int kexp = 0;
+    if (amax >= 32768.f && amax < INFINITY) kexp = int(__float_as_uint(amax) >> 23) - 127 - 14;
+    const float qmul = __uint_as_float(uint32_t(127 - kexp) << 23);  // 2^-k
+    float sr = 0.f;  // the quad of row r adds up that row, then rows 2c, 2c+1 are fetched
+    for (int d = c; d < D; d += 4) sr += __half2float(__float2half_rn(float(qrow[d]) * qmul));
+    sr += __shfl_xor_sync(0xffffffffu, sr, 1);
+    sr += __shfl_xor_sync(0xffffffffu, sr, 2);
+    const float fac = __uint_as_float(uint32_t(127 + kexp) << 23) * a.scale_log2;
+    qsum[nt][0] = __shfl_sync(0xffffffffu, sr, 8 * c);
+    qsum[nt][1] = __shfl_sync(0xffffffffu, sr, 8 * c + 4);
+    qfac[nt][0] = __shfl_sync(0xffffffffu, fac, 8 * c);
+    qfac[nt][1] = __shfl_sync(0xffffffffu, fac, 8 * c + 4);
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
       const T* q0 = qrow + (4 * (ks >> 1) + c) * 8;
       const int e0 = (ks & 1) * 2;
-      auto pk = [](const T* p, int i0, int i1) {
-        const uint32_t lo = *reinterpret_cast<const unsigned short*>(p + i0);
-        const uint32_t hi = *reinterpret_cast<const unsigned short*>(p + i1);
-        return lo | (hi << 16);
+      auto pk = [qmul](const T* p, int i0, int i1) {
+        const __half2 h = __floats2half2_rn(float(p[i0]) * qmul, float(p[i1]) * qmul);
+        return *reinterpret_cast<const uint32_t*>(&h);
       };
       qf[nt][ks][0] = pk(q0, e0, e0 + 4);
       qf[nt][ks][1] = pk(q0, e0 + 1, e0 + 5);
     }
-    float sr = 0.f;  // the quad of row r adds up that row, then rows 2c, 2c+1 are fetched
-    for (int d = c; d < D; d += 4) sr += float(qrow[d]);
-    sr += __shfl_xor_sync(0xffffffffu, sr, 1);
-    sr += __shfl_xor_sync(0xffffffffu, sr, 2);
-    qsum[nt][0] = __shfl_sync(0xffffffffu, sr, 8 * c);
-    qsum[nt][1] = __shfl_sync(0xffffffffu, sr, 8 * c + 4);
   }
   // Q now lives in registers: release the staging area to the producer
   __syncwarp();
@@ -397,6 +438,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
 
   // per-query-row visibility limit: token t visible iff t < lim
   int lim[NTQ][2];
+  int lim_min = w.chunk_hi;  // below it nothing is masked for any row of this warp
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
@@ -405,7 +447,10 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
       int l = w.chunk_hi;
       if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
       lim[nt][e] = l;
+      lim_min = min(lim_min, l);
     }
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
@@ -418,117 +463,139 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
     corr[nt][0] = corr[nt][1] = 0.f;
   }
 
+  const int rw = row_bytes / 4;  // words per token row of the stage
   for (int tile = 0; tile < w.n_tiles; ++tile) {
     const int st = tile % w.stages;
     if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
       if (lane == 0) atomicExch(a.status, 2);
       break;
     }
-    const uint8_t* ks_ = w.stage_base + st * 2 * w.kv_bytes;
-    const uint8_t* vs_ = ks_ + w.kv_bytes;
+    const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * 2 * w.kv_bytes) + hw * W;
+    const uint32_t* vst = kst + w.kv_bytes / 4;
 #pragma unroll 1
     for (int sp = 0; sp < kSps; ++sp) {
       const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
       const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;  // its first token
       if (t_sub >= w.chunk_hi) continue;
-      const uint32_t* k0 = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + r) * row_bytes + hw * W * 4);
-      const uint32_t* k1 = reinterpret_cast<const uint32_t*>(ks_ + (usub * 16 + r + 8) * row_bytes + hw * W * 4);
-      const uint32_t* v0 = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + r) * row_bytes + hw * W * 4);
-      const uint32_t* v1 = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + r + 8) * row_bytes + hw * W * 4);
+      const uint32_t* k0 = kst + (usub * 16 + r) * rw;  // token r; token r + 8 is 8 rows on
+      const uint32_t* v0 = vst + (usub * 16 + r) * rw;
 
       // ------------------------------------------- S^T = K Q^T (16 tokens x 8*NTQ)
-      float s[NTQ][4];
+      float s[NTQ][4], s2[NTQ][4];  // two chains of dependent MMAs instead of one
 #pragma unroll
-      for (int nt = 0; nt < NTQ; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+      for (int nt = 0; nt < NTQ; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+      }
 #pragma unroll
       for (int i = 0; i < KS / 2; ++i) {
-        const uint32_t w0 = k0[1 + 4 * i + c], w1 = k1[1 + 4 * i + c];
-        const uint32_t ka[4] = {unpack_pair(w0, 0), unpack_pair(w1, 0), unpack_pair(w0, 1), unpack_pair(w1, 1)};
-        const uint32_t kb[4] = {unpack_pair(w0, 2), unpack_pair(w1, 2), unpack_pair(w0, 3), unpack_pair(w1, 3)};
+        uint32_t u0[4], u1[4];
+        unpack4(k0[1 + 4 * i + c], u0);
+        unpack4(k0[8 * rw + 1 + 4 * i + c], u1);
+        const uint32_t ka[4] = {u0[0], u1[0], u0[1], u1[1]};
+        const uint32_t kb[4] = {u0[2], u1[2], u0[3], u1[3]};
 #pragma unroll
         for (int nt = 0; nt < NTQ; ++nt) {
-          mma_16816<kBf16>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
-          mma_16816<kBf16>(s[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+          mma_16816<false>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
+          mma_16816<false>(s2[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
         }
       }
 
       // ------------------ scale/shift of tokens r, r+8; mask; online softmax
-      const uint32_t kw0 = k0[0], kw1 = k1[0], vw0 = v0[0], vw1 = v1[0];
-      const int t0 = t_sub + r, t1 = t_sub + r + 8;
-      const float ksc0 = half_bits_to_float(kw0 & 0xFFFFu) * a.scale_log2;
-      const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu) * a.scale_log2;
-      const float kof0 = half_bits_to_float(kw0 >> 16) * a.scale_log2 - kMagicF * ksc0;
-      const float kof1 = half_bits_to_float(kw1 >> 16) * a.scale_log2 - kMagicF * ksc1;
-      // tokens past the end were not copied: their scale words are garbage
-      const float vsc0 = t0 < w.chunk_hi ? half_bits_to_float(vw0 & 0xFFFFu) : 0.f;
-      const float vsc1 = t1 < w.chunk_hi ? half_bits_to_float(vw1 & 0xFFFFu) : 0.f;
-      const float vsh0 = t0 < w.chunk_hi ? half_bits_to_float(vw0 >> 16) : 0.f;
-      const float vsh1 = t1 < w.chunk_hi ? half_bits_to_float(vw1 >> 16) : 0.f;
-
-      uint32_t pb[NTQ][2];
-      bool moved = false;
-      float alpha[NTQ][2];
+      const uint32_t kw0 = k0[0], kw1 = k0[8 * rw], vw0 = v0[0], vw1 = v0[8 * rw];
+      const float ksc0 = half_bits_to_float(kw0 & 0xFFFFu), ksh0 = half_bits_to_float(kw0 >> 16);
+      const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
+      float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
+      float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
+      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
+      float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
+      bool need = false;
 #pragma unroll
-      for (int nt = 0; nt < NTQ; ++nt) {
-        float pw0[2], pw1[2], p0[2], p1[2];
+      for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const float s0 = t0 < lim[nt][e] ? fmaf(ksc0, s[nt][e], kof0 * qsum[nt][e]) : -INFINITY;
-          const float s1 = t1 < lim[nt][e] ? fmaf(ksc1, s[nt][2 + e], kof1 * qsum[nt][e]) : -INFINITY;
-          float mx = fmaxf(s0, s1);
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
-          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
-          const float m_new = fmaxf(m_run[nt][e], mx);
-          const float m_use = m_new == -INFINITY ? 0.f : m_new;
-          alpha[nt][e] = fast_exp2(m_run[nt][e] - m_use);  // exp2(-inf) = 0 on the first tile
-          m_run[nt][e] = m_new;
-          p0[e] = fast_exp2(s0 - m_use);
-          p1[e] = fast_exp2(s1 - m_use);
-          pw0[e] = p0[e] * vsc0;
-          pw1[e] = p1[e] * vsc1;
-          moved |= alpha[nt][e] != 1.f;
+          sc0[nt][e] = fmaf(ksc0, s[nt][e] + s2[nt][e], ksh0 * qsum[nt][e]) * qfac[nt][e];
+          sc1[nt][e] = fmaf(ksc1, s[nt][2 + e] + s2[nt][2 + e], ksh1 * qsum[nt][e]) * qfac[nt][e];
         }
-        // fold the V scale into P; the shift and the offset of the unpacked
-        // nibbles become a per-row correction that uses the ROUNDED weights so
-        // that the offset cancels exactly
-        const uint32_t pt0 = pack2<kBf16>(pw0[0], pw0[1]);  // token r,   rows 2c, 2c+1
-        const uint32_t pt1 = pack2<kBf16>(pw1[0], pw1[1]);  // token r+8
-        const float2 r0 = unpack2<kBf16>(pt0), r1 = unpack2<kBf16>(pt1);
-        l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + (p0[0] + p1[0]);
-        l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + (p0[1] + p1[1]);
-        corr[nt][0] = corr[nt][0] * alpha[nt][0] + (fmaf(p0[0], vsh0, p1[0] * vsh1) - kMagicF * (r0.x + r1.x));
-        corr[nt][1] = corr[nt][1] * alpha[nt][1] + (fmaf(p0[1], vsh0, p1[1] * vsh1) - kMagicF * (r0.y + r1.y));
-        pb[nt][0] = movmatrix_trans(pt0);  // tokens 2c, 2c+1   of row r
-        pb[nt][1] = movmatrix_trans(pt1);  // tokens 2c+8, 2c+9 of row r
-      }
-      // rescale the running output only when some row's maximum moved
-      if (__any_sync(0xffffffffu, moved)) {
+      if (!all_visible) {
+        const int t0 = t_sub + r, t1 = t_sub + r + 8;
+        // tokens past the end were not copied: their scale words are garbage
+        if (t0 >= w.chunk_hi) vsc0 = 0.f, vsh0 = 0.f;
+        if (t1 >= w.chunk_hi) vsc1 = 0.f, vsh1 = 0.f;
 #pragma unroll
         for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
-          for (int mt = 0; mt < MTV; ++mt) {
-            acc[mt][nt][0] *= alpha[nt][0];
-            acc[mt][nt][1] *= alpha[nt][1];
-            acc[mt][nt][2] *= alpha[nt][0];
-            acc[mt][nt][3] *= alpha[nt][1];
+          for (int e = 0; e < 2; ++e) {
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
           }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) need |= fmaxf(sc0[nt][e], sc1[nt][e]) > m_run[nt][e] + kLazy;
+      if (__any_sync(0xffffffffu, need)) {
+        // some row's maximum grew by more than the slack: refresh all of them
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt) {
+          float alpha[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float mx = fmaxf(sc0[nt][e], sc1[nt][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[nt][e], mx);
+            alpha[e] = fast_exp2(m_run[nt][e] - (m_new == -INFINITY ? 0.f : m_new));  // exp2(-inf) = 0 at first
+            m_run[nt][e] = m_new;
+            l_run[nt][e] *= alpha[e];
+            corr[nt][e] *= alpha[e];
+          }
+#pragma unroll
+          for (int mt = 0; mt < MTV; ++mt) {
+            acc[mt][nt][0] *= alpha[0];
+            acc[mt][nt][1] *= alpha[1];
+            acc[mt][nt][2] *= alpha[0];
+            acc[mt][nt][3] *= alpha[1];
+          }
+        }
+      }
+      uint32_t pb[NTQ][2];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+        float p0[2], p1[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_use = m_run[nt][e] == -INFINITY ? 0.f : m_run[nt][e];
+          p0[e] = fast_exp2(sc0[nt][e] - m_use);
+          p1[e] = fast_exp2(sc1[nt][e] - m_use);
+          l_run[nt][e] += p0[e] + p1[e];
+          corr[nt][e] = fmaf(p0[e], vsh0, fmaf(p1[e], vsh1, corr[nt][e]));
+        }
+        // V's scale rides on the probabilities
+        pb[nt][0] = movmatrix_trans(pack2<false>(p0[0] * vsc0, p0[1] * vsc0));  // tokens 2c, 2c+1   of row r
+        pb[nt][1] = movmatrix_trans(pack2<false>(p1[0] * vsc1, p1[1] * vsc1));  // tokens 2c+8, 2c+9 of row r
       }
 
       // ------------------------------------------------- O^T += V^T P^T
-      const uint32_t* va = reinterpret_cast<const uint32_t*>(vs_ + (usub * 16 + 2 * c) * row_bytes + hw * W * 4) + 1 + WPT * r;
-      const int rw = row_bytes / 4;
+      const uint32_t* va = vst + (usub * 16 + 2 * c) * rw + 1 + WPT * r;
 #pragma unroll
       for (int wi = 0; wi < WPT; ++wi) {
         const uint32_t x0 = va[wi], x1 = va[rw + wi], x2 = va[8 * rw + wi], x3 = va[9 * rw + wi];
+        // low / high half-words of two neighbouring tokens side by side
+        uint32_t ylo[4], yhi[4], zlo[4], zhi[4];
+        unpack4(__byte_perm(x0, x1, 0x5410), ylo);  // nibbles e   of tokens 2c,   2c+1 -> rows r
+        unpack4(__byte_perm(x0, x1, 0x7632), yhi);  // nibbles e+4 of tokens 2c,   2c+1 -> rows r+8
+        unpack4(__byte_perm(x2, x3, 0x5410), zlo);  // nibbles e   of tokens 2c+8, 2c+9
+        unpack4(__byte_perm(x2, x3, 0x7632), zhi);
+        // unpack4 pairs nibble e of the low half with nibble e of the high half
+        // (its "e + 4"), i.e. the same element of the two tokens: out[0..3] are
+        // elements 0, 1, 2, 3 of the half-word
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const uint32_t u0 = unpack_pair(x0, e), u1 = unpack_pair(x1, e);
-          const uint32_t u2 = unpack_pair(x2, e), u3 = unpack_pair(x3, e);
-          const uint32_t vf[4] = {__byte_perm(u0, u1, 0x5410), __byte_perm(u0, u1, 0x7632),
-                                  __byte_perm(u2, u3, 0x5410), __byte_perm(u2, u3, 0x7632)};
+          const uint32_t vf[4] = {ylo[e], yhi[e], zlo[e], zhi[e]};
 #pragma unroll
-          for (int nt = 0; nt < NTQ; ++nt) mma_16816<kBf16>(acc[wi * 4 + e][nt], vf, pb[nt][0], pb[nt][1]);
+          for (int nt = 0; nt < NTQ; ++nt) mma_16816<false>(acc[wi * 4 + e][nt], vf, pb[nt][0], pb[nt][1]);
         }
       }
     }
@@ -574,7 +641,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
 }
 
 template <int D, int MT, bool kInt4, bool kBf16>
-__global__ void __launch_bounds__(kDecThreads, 1) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
+__global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
   using Stage = DecStage<D, kInt4>;
   using T = typename Half2Type<kBf16>::T;
   constexpr int W = 1 + D / 8;  // int4 words per row (one quantisation group)
@@ -897,7 +964,7 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   const size_t stage_bytes = 2 * size_t(Stage::kv_bytes(a_in.hb));
   const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
-  int stages = int(kDecRingBudget / stage_bytes);
+  int stages = int(DecOccupancy<kInt4>::kRingBudget / stage_bytes);
   stages = stages > kDecMaxStages ? kDecMaxStages : stages;
   const int q_stages = int((qbytes + stage_bytes - 1) / stage_bytes);
   if (stages < 2 || q_stages > stages) return set_error(XFB200_E_UNSUPPORTED, "decode: shared-memory ring too small for this shape");
@@ -908,7 +975,7 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   const size_t smem = ring > cmb ? ring : cmb;
   auto kern = decode_splitk_kernel<D, MT, kInt4, kBf16>;
   // 227 KB per CTA includes the static part (the mbarriers)
-  if (smem + 1024 > 227 * 1024) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
+  if (smem + 1024 > size_t(227 * 1024) / DecOccupancy<kInt4>::kCtasPerSm) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
   static size_t configured = 0;  // per instantiation: largest size opted into so far
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -1020,7 +1087,9 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     // copy runs of up to 64 tokens at once.
     if (int4 && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
       const int span = p->block_tables ? p->page_size : p->kv_padding;
-      int g = 64;
+      // a run must fit the stage it is copied into (a power of two of tokens)
+      const int stage_tokens = p->head_dim == 128 ? DecStage<128, true>::tokens(hb) : DecStage<64, true>::tokens(hb);
+      int g = stage_tokens < 64 ? stage_tokens : 64;
       while (g > 1 && span % g) g >>= 1;
       a.copy_group = g;
     }
