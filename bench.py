@@ -53,6 +53,12 @@ CFG2 = dict(B=4, M=4096, H=32, D=128)
 CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from the ncu captures summarised
+# under profiles/: bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
+# byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
+NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (979.70e6 + 14.65e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6}
+
+
 def causal_flops(B, M, H, D):
     return 4.0 * M * M * D * B * H / 2.0
 
@@ -124,6 +130,17 @@ def cpu_sample_inputs():
     return q, k, v
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to every rank; the CPU arm runs on
+    rank 0 alone and may use every core the process is allowed on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_step(q, k, v):
     import oracle
     from xformers_b200.ops.fmha.attn_bias import LowerTriangularMask
@@ -132,6 +149,7 @@ def cpu_step(q, k, v):
 
 
 def time_cpu(budget_s: float, max_reps: int, warmup: int = 1):
+    use_all_host_threads()
     q, k, v = cpu_sample_inputs()
     for _ in range(warmup):
         cpu_step(q, k, v)
@@ -149,6 +167,7 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    use_all_host_threads()
     q, k, v = cpu_sample_inputs()
     for _ in range(max(args.warmup, 1)):
         cpu_step(q, k, v)
@@ -324,26 +343,68 @@ def main():
         launches = args.steps
         out_line.update({"value": tfs * world, "ms_per_step": per_step, "gpu_launches": launches})
         out_line["roofline"] = {"bound": "tensor", "achieved": tfs, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                "frac": tfs / peaks["bf16_tflops"], "traffic": None, "kernel": "prefill_sm100_kernel<128,bf16>",
+                                "frac": tfs / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill"] * (B / 1), "traffic_unit": "bytes per launch (ncu, B=1 case scaled by B)", "kernel": "prefill_sm100_m256_kernel<128, bf16>",
                                 "of": peaks["source"], "frac_of_nominal_2250": tfs / 2250.0, "device_status": status}
     # ------------------------------------------------------------------ e2e
     if "e2e" in legs:
         hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
         ho = torch.empty((B, M, H, D), dtype=torch.bfloat16).pin_memory()
 
+        # Three streams, two sets of device buffers: the upload of step i+1 and
+        # the read-back of step i-1 overlap the kernel of step i, as a serving
+        # loop would run it.  Every step still moves its own inputs and result.
+        s_in, s_out, s_cmp = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.current_stream()
+        slots = [tuple(torch.empty_like(q) for _ in range(3)) for _ in range(2)]
+        ev_in = [torch.cuda.Event() for _ in range(2)]
+        ev_cmp = [torch.cuda.Event() for _ in range(2)]
+        ev_out = torch.cuda.Event()
+        counter = [0]
+
         def e2e_step():
-            dq, dk, dv = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-            o = xops.memory_efficient_attention_forward(dq, dk, dv, causal)
-            ho.copy_(o, non_blocking=True)
+            i = counter[0] % 2
+            counter[0] += 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(ev_cmp[i])  # the kernel that last read this slot is done
+                for dst, src in zip(slots[i], (hq, hk, hv)):
+                    dst.copy_(src, non_blocking=True)
+                ev_in[i].record(s_in)
+            s_cmp.wait_event(ev_in[i])
+            o = xops.memory_efficient_attention_forward(*slots[i], causal)
+            ev_cmp[i].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[i])
+                ho.copy_(o, non_blocking=True)
+                o.record_stream(s_out)
+                ev_out.record(s_out)
+
+        def e2e_drain():
+            s_cmp.wait_event(ev_out)  # the timed region ends when the last result is on the host
 
         e_steps = max(3, min(args.steps, 20))
-        ms, win = event_time_ms(e2e_step, e_steps, 3, barrier)
+        s_in.wait_stream(s_cmp)
+        for _ in range(3):
+            e2e_step()
+        e2e_drain()
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        e0.record()
+        s_in.wait_event(e0)
+        for _ in range(e_steps):
+            e2e_step()
+        e2e_drain()
+        e1.record()
+        torch.cuda.synchronize()
+        win = (t0, time.time())
+        barrier()
+        ms = e0.elapsed_time(e1)
         windows.append(win)
         ms = max_over_ranks(ms)
         nbytes = q.numel() * 2
         out_line["e2e"] = {"value": world * flops / (ms / e_steps * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes,
                            "d2h_bytes_per_step": nbytes, "ms_per_step": ms / e_steps, "steps": e_steps}
-        del hq, hk, hv, ho
+        del hq, hk, hv, ho, slots
     del q, k, v
     torch.cuda.empty_cache()
 
@@ -359,7 +420,8 @@ def main():
             split = fmha.b200_splitk.FwOp.get_split_k(16 if args.small else 64, 32768, 8, 68 if quant else 256)
             out_line[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes, "split_k": split,
                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                           "frac": gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"]},
+                                           "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name] * nbytes, "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 16-sequence case)",
+                                           "of": peaks["source"]},
                               "workload": "64 seqs, kv len U[1024,32768], paged 256, Hq=64 Hkv=8 D=128, 1 query each; cache far larger than L2"}
             del dq, dk, dv, dbias
             torch.cuda.empty_cache()
