@@ -273,6 +273,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="headline only (no decode / varlen / long-context / CPU legs)")
+    ap.add_argument("--e2e-mode", default="pipelined", choices=["pipelined", "serial"],
+                    help="e2e leg: overlap upload / kernel / read-back of neighbouring steps, or run them back to back")
     ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,varlen,long,cpu")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: one batch of the headline configuration (128 MB of tensors, still larger than L2) and 16 decode sequences; not a bench value")
@@ -360,7 +362,15 @@ def main():
         ev_out = torch.cuda.Event()
         counter = [0]
 
+        def e2e_step_serial():
+            for dst, src in zip(slots[0], (hq, hk, hv)):
+                dst.copy_(src, non_blocking=True)
+            o = xops.memory_efficient_attention_forward(*slots[0], causal)
+            ho.copy_(o, non_blocking=True)
+
         def e2e_step():
+            if args.e2e_mode == "serial":
+                return e2e_step_serial()
             i = counter[0] % 2
             counter[0] += 1
             with torch.cuda.stream(s_in):
@@ -378,7 +388,8 @@ def main():
                 ev_out.record(s_out)
 
         def e2e_drain():
-            s_cmp.wait_event(ev_out)  # the timed region ends when the last result is on the host
+            if args.e2e_mode != "serial":
+                s_cmp.wait_event(ev_out)  # the timed region ends when the last result is on the host
 
         e_steps = max(3, min(args.steps, 20))
         s_in.wait_stream(s_cmp)
@@ -403,7 +414,7 @@ def main():
         ms = max_over_ranks(ms)
         nbytes = q.numel() * 2
         out_line["e2e"] = {"value": world * flops / (ms / e_steps * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": 3 * nbytes,
-                           "d2h_bytes_per_step": nbytes, "ms_per_step": ms / e_steps, "steps": e_steps}
+                           "d2h_bytes_per_step": nbytes, "ms_per_step": ms / e_steps, "steps": e_steps, "mode": args.e2e_mode}
         del hq, hk, hv, ho, slots
     del q, k, v
     torch.cuda.empty_cache()

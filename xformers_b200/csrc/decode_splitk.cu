@@ -17,6 +17,7 @@
 // exist for each sequence in a fixed order, so results are bit-reproducible.
 // Lengths and page tables are read from device memory at run time; the grid
 // depends on static bounds only.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -30,6 +31,8 @@ constexpr int kDecThreads = (kDecConsumerWarps + 1) * 32;
 constexpr int kDecChunkAlign = 128;  // chunk size granularity in tokens (= largest stage)
 
 struct DecodeArgs {
+  // copy_mode 3 only: the K and V caches as 3-D tensors {64 elements, token rows, 128-byte column groups}
+  CUtensorMap tm_k, tm_v;
   const void* q;
   const void* k;
   const void* v;
@@ -46,7 +49,10 @@ struct DecodeArgs {
   int32_t hb;          // kv heads per CTA (1, 2, 4 or 8)
   int32_t rows;        // R = mq * q_per_kv
   int32_t row_blocks;  // ceil(R / (16*MT))
-  int32_t copy_mode;   // 0: one bulk copy per token stripe of hb heads; 1: per (token, head); 2: word copies (no TMA)
+  int32_t copy_mode;   // 0: one bulk copy per token stripe of hb heads; 1: per (token, head); 2: word copies (no TMA);
+                       // 3: tiled TMA, a whole run of tokens per copy, 128-byte swizzled in shared memory (16-bit cache)
+  int32_t box_tok;     // mode 3: tokens per tiled copy (power of two, 8..256, divides the stage)
+  int32_t kv_bytes;    // bytes of the K (or V) part of a stage
   int32_t copy_group;  // tokens per bulk copy (int4 only, mode 0)
   int32_t stages;         // depth of the shared-memory ring
   int32_t q_first_stage;  // stages >= this one hold the staged Q until q_done
@@ -130,6 +136,7 @@ struct DecWarp {
   uint64_t* q_done_bar;
   float* mine;  // this warp's slot of the combine area: [ROWS][D + 2]
   int lane, hw, sub, wph, row0;
+  int b, head;  // sequence and kv head of this warp
   int chunk_lo, chunk_hi, kv_len, n_tiles;
   int tok_per_stage, kv_bytes, row_bytes, stages;
 };
@@ -149,24 +156,40 @@ template <int D, int MT, bool kBf16>
 __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp& w) {
   constexpr int KS = D / 16;  // k-steps of the QK^T product
   constexpr int NT = D / 8;   // n-tiles of the PV product
-  constexpr int kQRowBytes = D * 2;
   constexpr int kCmbRow = D + 2;
   constexpr int kSps = DecStage<D, false>::kSubTiles;
   const int lane = w.lane, r = lane >> 2, c = lane & 3;
   const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
+  // Tiled copies leave a stage as boxes of [column group][token][128 B] with the
+  // 16-byte chunks of every row XOR-ed by (token & 7); bulk copies leave padded
+  // token rows.  Either way ldmatrix sees no bank conflicts.
+  const bool swz = a.copy_mode == 3;
+  const int box_shift = __ffs(a.box_tok) - 1;
+  const int cg_stride = a.box_tok * 128;
+  const int box_bytes = cg_stride * (a.hb * (D / 64));
 
+  // A fragments of Q straight from global memory (rows r and r + 8 of each
+  // m-tile, element pairs 2c and 2c + 8 of each k-step); rows beyond R are zero.
   uint32_t qf[MT][KS][4];
+  {
+    using T = typename Half2Type<kBf16>::T;
+    const T* qg = reinterpret_cast<const T*>(a.q);
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int rr = mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      const int cc = ks * 16 + (lane >> 4) * 8;
-      ldmatrix_x4(qf[mt][ks], smem_u32(w.qs + rr * kQRowBytes + cc * 2));
-    }
-  // Q now lives in registers: release the staging area to the producer
-  __syncwarp();
-  if (lane == 0) mbar_arrive(w.q_done_bar);
+      for (int hlf = 0; hlf < 2; ++hlf) {
+        const int row = w.row0 + mt * 16 + r + hlf * 8;
+        const bool live = row < R;
+        const int qi = live ? row / a.q_per_kv : 0, h = live ? row % a.q_per_kv : 0;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(
+            qg + (int64_t(w.b) * a.mq + qi) * a.q_sm + int64_t(w.head) * a.q_sg + int64_t(h) * a.q_sh + 2 * c);
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          qf[mt][ks][hlf] = live ? __ldg(src + ks * 8) : 0u;
+          qf[mt][ks][2 + hlf] = live ? __ldg(src + ks * 8 + 4) : 0u;
+        }
+      }
+  }
 
   // per-row visibility limit: token t visible iff t < lim
   int lim[MT][2];
@@ -212,11 +235,15 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
         for (int j = 0; j < 2; ++j) s[mt][j][0] = s[mt][j][1] = s[mt][j][2] = s[mt][j][3] = 0.f;
       {
         const int tok = usub * 16 + (lane & 7) + (lane >> 4) * 8;
-        const uint32_t kaddr = smem_u32(ks_ + tok * row_bytes + hw * D * 2 + ((lane >> 3) & 1) * 16);
+        const int ti = tok & (a.box_tok - 1);
+        const uint32_t kaddr = swz ? smem_u32(ks_) + (tok >> box_shift) * box_bytes + hw * (D / 64) * cg_stride + ti * 128
+                                   : smem_u32(ks_ + tok * row_bytes + hw * D * 2 + ((lane >> 3) & 1) * 16);
+        const int xh = (ti & 7) ^ ((lane >> 3) & 1);
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
           uint32_t kf[4];
-          ldmatrix_x4(kf, kaddr + ks * 32);
+          // byte column ks*32 + half*16 of this head: column group ks/4, chunk (2 ks + half) & 7
+          ldmatrix_x4(kf, swz ? kaddr + (ks >> 2) * cg_stride + ((((2 * ks) & 7) ^ xh) << 4) : kaddr + ks * 32);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             mma_16816<kBf16>(s[mt][0], qf[mt][ks], kf[0], kf[1]);
@@ -276,17 +303,26 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
         // 0 * garbage cannot produce NaN
         for (int i = lane; i < 16 * (D / 8); i += 32) {
           const int tt = i / (D / 8), ch = i % (D / 8);
-          if (t_sub + tt >= w.chunk_hi)
-            *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + (usub * 16 + tt) * row_bytes + hw * D * 2 + ch * 16) = make_uint4(0, 0, 0, 0);
+          if (t_sub + tt >= w.chunk_hi) {
+            const int tk = usub * 16 + tt;
+            // (all eight chunks of a 128-byte row are cleared, so the swizzle does not matter)
+            const int off = swz ? (tk >> box_shift) * box_bytes + (hw * (D / 64) + (ch >> 3)) * cg_stride + (tk & (a.box_tok - 1)) * 128 + (ch & 7) * 16
+                                : tk * row_bytes + hw * D * 2 + ch * 16;
+            *reinterpret_cast<uint4*>(const_cast<uint8_t*>(vs_) + off) = make_uint4(0, 0, 0, 0);
+          }
         }
         __syncwarp();
       }
       const int tok = usub * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-      const uint32_t vaddr = smem_u32(vs_ + tok * row_bytes + hw * D * 2 + (lane >> 4) * 16);
+      const int tiv = tok & (a.box_tok - 1);
+      const uint32_t vaddr = swz ? smem_u32(vs_) + (tok >> box_shift) * box_bytes + hw * (D / 64) * cg_stride + tiv * 128
+                                 : smem_u32(vs_ + tok * row_bytes + hw * D * 2 + (lane >> 4) * 16);
+      const int xv = (tiv & 7) ^ (lane >> 4);
 #pragma unroll
       for (int j = 0; j < NT; j += 2) {
         uint32_t vf[4];
-        ldmatrix_x4_trans(vf, vaddr + j * 16);
+        // byte column (j + hi)*16 of this head: column group j/8, chunk (j & 7) | hi
+        ldmatrix_x4_trans(vf, swz ? vaddr + (j >> 3) * cg_stride + (((j & 7) ^ xv) << 4) : vaddr + j * 16);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           mma_16816<kBf16>(acc[mt][j], pa[mt], vf[0], vf[1]);
@@ -693,12 +729,13 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   }
   const int n_tiles = (chunk_hi - chunk_lo + TOK - 1) / TOK;
 
-  const int kv_bytes = Stage::kv_bytes(hb);
+  const int kv_bytes = a.kv_bytes;
   const int row_bytes = Stage::row_bytes(hb);
-  uint8_t* stage_base = smem_raw;                                  // kDecStages * 2 * kv_bytes
+  // swizzled tiles want 1024-byte aligned stages; the static barriers precede the dynamic part
+  uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // Q is staged once in the region of the LAST stages; the producer does not
   // fill those before every consumer warp has taken its Q fragments
-  uint8_t* q_smem = smem_raw + a.q_first_stage * 2 * kv_bytes;     // 8 warps * 16*MT rows * D*2 B
+  uint8_t* q_smem = stage_base + a.q_first_stage * 2 * kv_bytes;     // 8 warps * 16*MT rows * D*2 B
   constexpr int kQRowBytes = D * 2;
 
   if (threadIdx.x == 0) {
@@ -725,7 +762,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
           if (lane == 0) atomicExch(a.status, 1);
           return;
         }
-      } else if (tile == a.q_first_stage) {
+      } else if (kInt4 && tile == a.q_first_stage) {
         if (!mbar_wait(&q_done_bar, 0)) {
           if (lane == 0) atomicExch(a.status, 3);
           return;
@@ -735,6 +772,23 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
       const int nvalid = min(TOK, chunk_hi - t0);
       uint8_t* ks = stage_base + st * 2 * kv_bytes;
       uint8_t* vs = ks + kv_bytes;
+      if (a.copy_mode == 3) {
+        // one tiled copy per run of box_tok tokens: {64 elements} x {box_tok rows} x {hb*D/64 column groups}
+        if (lane == 0) {
+          const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
+          const uint32_t box_bytes = uint32_t(a.box_tok) * hb * kHeadBytes;
+          mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
+          for (int bx = 0; bx < nbox; ++bx) {
+            const int t = t0 + bx * a.box_tok;
+            const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
+                                               : int64_t(b) * a.kv_padding + t;
+            tma_load_3d(ks + bx * box_bytes, &a.tm_k, &full_bar[st], 0, int(row), head0 * (D / 64));
+            tma_load_3d(vs + bx * box_bytes, &a.tm_v, &full_bar[st], 0, int(row), head0 * (D / 64));
+          }
+        }
+        __syncwarp();
+        continue;
+      }
       if (a.copy_mode == 2) {
         // no TMA: 32-bit loads (rows that are not 16-B aligned)
         const int words_per_head = kHeadBytes / 4;
@@ -784,8 +838,12 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   const int row0 = rblk * ROWS;  // first query row (of this kv head) handled here
   const int R = a.rows;
 
-  // ---- stage Q (this warp's head) in shared memory, zero rows beyond R
-  {
+  // ---- int4 path: stage Q (this warp's head) in shared memory, zero rows beyond R.
+  // (The 16-bit path reads its fragments from global memory: a fragment load that
+  // nothing consumes yet could still be in flight when the staging area is handed
+  // back to the copy engine.  The int4 path converts what it loads before it
+  // arrives on q_done, so its loads have returned by then.)
+  if constexpr (kInt4) {
     uint8_t* qs = q_smem + warp * ROWS * kQRowBytes;
     const T* qg = reinterpret_cast<const T*>(a.q);
     for (int i = lane; i < ROWS * (D / 8); i += 32) {
@@ -810,6 +868,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   w.full_bar = full_bar, w.empty_bar = empty_bar, w.q_done_bar = &q_done_bar;
   w.mine = cmb + size_t(warp) * ROWS * kCmbRow;
   w.lane = lane, w.hw = hw, w.sub = sub, w.wph = wph, w.row0 = row0;
+  w.b = b, w.head = head;
   w.chunk_lo = chunk_lo, w.chunk_hi = chunk_hi, w.kv_len = kv_len, w.n_tiles = n_tiles;
   w.tok_per_stage = TOK, w.kv_bytes = kv_bytes, w.row_bytes = row_bytes, w.stages = kDecStages;
   if constexpr (kInt4)
@@ -961,17 +1020,20 @@ template <int D, int MT, bool kInt4, bool kBf16>
 static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
   using Stage = DecStage<D, kInt4>;
   constexpr int ROWS = kInt4 ? 8 * MT : 16 * MT;
-  const size_t stage_bytes = 2 * size_t(Stage::kv_bytes(a_in.hb));
+  // tiled copies need no row padding
+  const int kv_bytes = a_in.copy_mode == 3 ? Stage::tokens(a_in.hb) * a_in.hb * D * 2 : Stage::kv_bytes(a_in.hb);
+  const size_t stage_bytes = 2 * size_t(kv_bytes);
   const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
   int stages = int(DecOccupancy<kInt4>::kRingBudget / stage_bytes);
   stages = stages > kDecMaxStages ? kDecMaxStages : stages;
-  const int q_stages = int((qbytes + stage_bytes - 1) / stage_bytes);
+  const int q_stages = kInt4 ? int((qbytes + stage_bytes - 1) / stage_bytes) : 0;  // only the int4 path stages Q
   if (stages < 2 || q_stages > stages) return set_error(XFB200_E_UNSUPPORTED, "decode: shared-memory ring too small for this shape");
   DecodeArgs a = a_in;
   a.stages = stages;
   a.q_first_stage = stages - q_stages;
-  const size_t ring = stages * stage_bytes;
+  a.kv_bytes = kv_bytes;
+  const size_t ring = stages * stage_bytes + 1024;  // the kernel aligns the ring to 1024 B
   const size_t smem = ring > cmb ? ring : cmb;
   auto kern = decode_splitk_kernel<D, MT, kInt4, kBf16>;
   // 227 KB per CTA includes the static part (the mbarriers)
@@ -1111,6 +1173,35 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     a.copy_mode = 2;
   }
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
+  a.box_tok = 16;
+  if (!int4 && a.copy_mode == 0 && (p->kv_heads == 1 || (a.k_sg == p->head_dim && a.v_sg == p->head_dim))) {
+    // The copy engine's throughput is set by the number of copies: one tiled
+    // copy per run of tokens that is contiguous in the cache (a whole stage, or
+    // what a page allows) instead of one bulk copy per token.
+    const int stage_tokens = 16 * (kDecConsumerWarps / hb);
+    int box = stage_tokens;
+    if (p->block_tables != nullptr)
+      while (box > 1 && p->page_size % box) box >>= 1;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (box >= 8 && enc != nullptr) {
+      // token rows: all of a padded cache (rows past the end read as zero); a paged
+      // pool's size is not part of the call, and a copy never leaves its page
+      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t dims[3] = {64, rows, cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
+      const cuuint32_t bx[3] = {64, cuuint32_t(box), cuuint32_t(hb * (p->head_dim / 64))};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const CUtensorMapDataType dt = p->dtype == XFB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      const cuuint64_t ks[2] = {cuuint64_t(p->k_stride_m) * 2, 128}, vs[2] = {cuuint64_t(p->v_stride_m) * 2, 128};
+      const CUresult rk = enc(&a.tm_k, dt, 3, const_cast<void*>(p->k), dims, ks, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      const CUresult rv = enc(&a.tm_v, dt, 3, const_cast<void*>(p->v), dims, vs, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (rk == CUDA_SUCCESS && rv == CUDA_SUCCESS) {  // otherwise stay with the per-token bulk copies
+        a.copy_mode = 3;
+        a.box_tok = box;
+      }
+    }
+  }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = p->dtype == XFB200_BF16;

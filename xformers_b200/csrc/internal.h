@@ -1,6 +1,7 @@
 // Host-side helpers shared by the translation units of libxfb200.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdint.h>
@@ -35,6 +36,13 @@ inline int cuda_fail(const char* what, cudaError_t e) {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+
+// cuTensorMapEncodeTiled, looked up through the runtime so that the library does
+// not link against libcuda; nullptr if the driver does not provide it.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
 
 // Entry points implemented in other translation units.
 int prefill_sm100_supported(const xfb200_prefill_params* p);

@@ -410,22 +410,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_kernel(const __grid
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
 // Tensor map over [D, heads, rows, batch] (innermost first); box = 64 x 1 x 128 x 1, 128B swizzle.
 static int make_map(CUtensorMap* tm, const void* base, int dtype, int D, int64_t heads, int64_t head_stride, int64_t rows,
                     int64_t row_stride, int64_t batch, int64_t batch_stride, const char* what) {
