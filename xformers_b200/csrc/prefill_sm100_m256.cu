@@ -6,11 +6,16 @@
 //
 //   warps 0-3   softmax of query tile 0   (thread <-> row <-> TMEM lane)
 //   warps 4-7   softmax of query tile 1
-//   warp 8      TMA producer: Q (both tiles) once, then K_j / V_j into 2-deep rings
-//   warp 9      MMA issuer  : ... PV(t,j), QK(t,j+1) for t = 0,1 ...   (one lane issues)
+//   warp 8      MMA issuer of tile 0: ... PV(0,j), QK(0,j+1) ...   (one lane issues)
+//   warp 9      MMA issuer of tile 1; the two pass a token so that their blocks
+//               of MMAs alternate on the tensor pipe (an issuing thread stalls on
+//               every barrier it waits for, two of them hide each other's stalls)
+//   warp 10     TMA producer: Q (both tiles) once, then K_j / V_j into 2-deep rings
+//   warp 11     idle
 // The third warpgroup (warps 8-11) hands most of its registers to the two
 // softmax warpgroups with setmaxnreg, so that a whole score row (128 fp32)
-// stays in registers.
+// stays in registers.  setmaxnreg only moves registers inside what the CTA was
+// launched with; a request beyond that never returns (see kRegs* below).
 //
 // Tensor memory (all 512 columns): S0 | S1 | O0 | O1, fp32.  The probabilities
 // P_t overwrite the first 64 columns of S_t as packed bf16/f16 pairs and feed
@@ -49,6 +54,10 @@ constexpr int kBN = 128;      // keys per tile
 constexpr int kStagesK = XFB_KSTAGES, kStagesV = XFB_VSTAGES;
 constexpr int kThreads = 384;  // warps 0-3 / 4-7: softmax of tile 0 / 1; 8, 9: MMA of tile 0 / 1; 10: TMA; 11 idle
 constexpr int kMmaWarp0 = 8, kTmaWarp = 10;  // warps 8 and 9 issue the MMAs of query tile 0 and 1
+// registers per thread after setmaxnreg: 8 softmax warps grow, 4 other warps shrink;
+// the sum must fit what 384 threads were launched with (168 each)
+constexpr int kRegsLaunch = 168, kRegsSoftmax = 208, kRegsAux = 88;
+static_assert(8 * kRegsSoftmax + 4 * kRegsAux <= 12 * kRegsLaunch, "setmaxnreg would ask for more registers than the CTA owns");
 constexpr float kRescaleThreshold = 8.0f;
 constexpr uint32_t kHalfBytes = 128 * 128;  // one 64-column block of a 128-row tile
 
@@ -195,7 +204,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   volatile uint32_t* abort_flag = &bar->abort_flag;
 
   if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsAux));
   if (warp == kTmaWarp) {
     // ============================================================ TMA producer
     if (lane == 0 && j_end > j_begin) {
@@ -367,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsSoftmax));
     // ================================================================ softmax
     const int t = warp >> 2;                      // query tile of this warpgroup
     const int row = (warp & 3) * 32 + lane;       // TMEM lane == row inside the tile
