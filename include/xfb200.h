@@ -229,7 +229,9 @@ XFB200_API const char* xfb200_last_error(void);
  * (0 = no timed-out wait).  Synchronises the given stream. */
 XFB200_API int xfb200_prefill_device_status(void* stream, int32_t* status_out);
 /* Testing knob: 0 = choose automatically, 1 = always the mma.sync kernel,
- * 2 = fail unless the tcgen05 kernel covers the input. */
+ * 2 = fail unless a tcgen05 kernel covers the input; 3, 4, 5 = likewise and pick
+ * the tcgen05 variant (128 rows per CTA; 256 rows with 128-key steps; 256 rows
+ * with 64-key steps). */
 XFB200_API int xfb200_debug_set_prefill_path(int path);
 
 #ifdef __cplusplus

@@ -11,7 +11,7 @@ from xformers_b200.ops import fmha
 from xformers_b200.ops.fmha import attn_bias as ab
 
 P = fmha.b200
-KERNELS = [P.FwOp_Tcgen05, P.FwOp_Generic]
+KERNELS = [P.FwOp_Tcgen05, P.FwOp_Tcgen05_S64, P.FwOp_Generic]
 
 
 def _status_ok():

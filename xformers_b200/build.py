@@ -24,6 +24,7 @@ SOURCES = [
     "prefill_generic.cu",
     "prefill_sm100.cu",
     "prefill_sm100_m256.cu",
+    "prefill_sm100_s64.cu",
     "prefill_api.cu",
 ]
 HEADERS = ["internal.h", "ptx.cuh", "prefill_sm100.h", "../../include/xfb200.h"]

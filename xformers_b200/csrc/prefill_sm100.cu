@@ -410,16 +410,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_kernel(const __grid
 }
 
 // ------------------------------------------------------------------ host side
-// Tensor map over [D, heads, rows, batch] (innermost first); box = 64 x 1 x 128 x 1, 128B swizzle.
+// Tensor map over [D, heads, rows, batch] (innermost first); box = 64 x 1 x box_rows x 1, 128B swizzle.
 static int make_map(CUtensorMap* tm, const void* base, int dtype, int D, int64_t heads, int64_t head_stride, int64_t rows,
-                    int64_t row_stride, int64_t batch, int64_t batch_stride, const char* what) {
+                    int64_t row_stride, int64_t batch, int64_t batch_stride, const char* what, int box_rows = 128) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return set_error(XFB200_E_CUDA, "prefill: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[4] = {cuuint64_t(D), cuuint64_t(heads), cuuint64_t(rows), cuuint64_t(batch)};
   // a dimension of extent 1 never contributes to an address; give it a legal stride
   auto st = [&](int64_t s, int64_t extent) { return cuuint64_t((extent > 1 ? s : int64_t(D)) * 2); };
   const cuuint64_t strides[3] = {st(head_stride, heads), st(row_stride, rows), st(batch_stride, batch)};
-  const cuuint32_t box[4] = {64, 1, 128, 1};
+  const cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, dtype == XFB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -505,9 +505,11 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
     heads_flatten(p->k_strides, G, H, &khs, &khc);
     heads_flatten(p->v_strides, G, H, &vhs, &khc);
   }
-  rc = make_map(&a.tm_k, p->k, p->dtype, D, khc, khs, k_rows, p->k_strides.m, nb, p->k_strides.b, "k");
+  // keys per K/V copy: 128 (a tile of the 128-key kernels) or 64 (a stage of the 64-key-step kernel)
+  const int kv_box = prefill_path_override() == 5 ? 64 : 128;
+  rc = make_map(&a.tm_k, p->k, p->dtype, D, khc, khs, k_rows, p->k_strides.m, nb, p->k_strides.b, "k", kv_box);
   if (rc) return rc;
-  rc = make_map(&a.tm_v, p->v, p->dtype, D, khc, vhs, k_rows, p->v_strides.m, nb, p->v_strides.b, "v");
+  rc = make_map(&a.tm_v, p->v, p->dtype, D, khc, vhs, k_rows, p->v_strides.m, nb, p->v_strides.b, "v", kv_box);
   if (rc) return rc;
   a.out = p->out, a.lse = p->lse;
   a.seqstart_q = p->seqstart_q, a.seqstart_k = p->seqstart_k, a.seqlen_k = p->seqlen_k;
@@ -523,6 +525,7 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   const bool bf16 = p->dtype == XFB200_BF16;
   if (prefill_path_override() != 3) {
     a.q_tiles = (p->mq + 255) / 256;
+    if (prefill_path_override() == 5) return prefill_sm100_s64_launch(a, D, bf16, stream);
     return prefill_sm100_m256_launch(a, D, bf16, stream);
   }
   if (D == 128) return bf16 ? launch_sm100_t<128, true>(a, stream) : launch_sm100_t<128, false>(a, stream);

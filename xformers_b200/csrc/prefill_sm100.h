@@ -24,10 +24,12 @@ struct Sm100Args {
   int32_t q_tiles;
 };
 
-// 256 query rows per CTA (two 128-row tiles sharing every K/V tile).
+// 256 query rows per CTA (two 128-row tiles sharing every K/V tile), 128-key steps, one score buffer per tile.
 int prefill_sm100_m256_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream);
+// The same CTA shape with 64-key steps and two score buffers per tile.
+int prefill_sm100_s64_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream);
 
-// 0 = default kernel choice; 3 = the 128-rows-per-CTA kernel (testing knob).
+// 0 = default kernel choice; 3 = the 128-rows-per-CTA kernel, 4 = 256 rows with 128-key steps, 5 = 256 rows with 64-key steps (testing knobs).
 int prefill_path_override();
 
 }  // namespace xfb

@@ -37,7 +37,7 @@ MemoryEfficientAttentionB200SplitKOp = (b200_splitk.FwOp, None)
 
 ALL_FW_OPS: List[Type[AttentionFwOpBase]] = [b200.FwOp, b200_splitk.FwOp]
 ALL_BW_OPS: List[Type[AttentionBwOpBase]] = []
-_OPS_LOOKUP = {op.NAME: op for op in ALL_FW_OPS + [b200.FwOp_Generic, b200.FwOp_Tcgen05] + list(b200_splitk.FwOp_Map.values())}
+_OPS_LOOKUP = {op.NAME: op for op in ALL_FW_OPS + [b200.FwOp_Generic, b200.FwOp_Tcgen05, b200.FwOp_Tcgen05_M256, b200.FwOp_Tcgen05_S64] + list(b200_splitk.FwOp_Map.values())}
 
 
 def _serialize_op(op):

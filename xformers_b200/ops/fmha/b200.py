@@ -204,6 +204,20 @@ class FwOp_Tcgen05(FwOp):
     _TEST_K = [64, 128]
 
 
+class FwOp_Tcgen05_M256(FwOp_Tcgen05):
+    """tcgen05 kernel with 128-key steps and one score buffer per query tile."""
+
+    NAME = "b200F-tc5-m256"
+    KERNEL_PATH = 4
+
+
+class FwOp_Tcgen05_S64(FwOp_Tcgen05):
+    """tcgen05 kernel with 64-key steps and two score buffers per query tile."""
+
+    NAME = "b200F-tc5-s64"
+    KERNEL_PATH = 5
+
+
 def prefill_device_status(device=None) -> int:
     """Status word of the tcgen05 kernel on ``device`` (0 = every wait was
     satisfied).  Synchronises the current stream; meant for tests."""
