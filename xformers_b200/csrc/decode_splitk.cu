@@ -732,7 +732,8 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   const int kv_bytes = a.kv_bytes;
   const int row_bytes = Stage::row_bytes(hb);
   // swizzled tiles want 1024-byte aligned stages; the static barriers precede the dynamic part
-  uint8_t* stage_base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // (an offset from the array, not a cast of a rounded integer: the compiler must keep seeing shared memory)
+  uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   // Q is staged once in the region of the LAST stages; the producer does not
   // fill those before every consumer warp has taken its Q fragments
   uint8_t* q_smem = stage_base + a.q_first_stage * 2 * kv_bytes;     // 8 warps * 16*MT rows * D*2 B

@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_kernel(const __grid
   constexpr int kHalves = D / 64;          // 64-element (128-byte) column blocks of Q/K/V
   constexpr uint32_t kHalfBytes = 128 * 128;  // 128 rows x 128 B
   extern __shared__ uint8_t smem_dyn[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);  // an offset, so that the compiler keeps seeing shared memory
   Sm100Barriers* bar = reinterpret_cast<Sm100Barriers*>(smem + L::kBar);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

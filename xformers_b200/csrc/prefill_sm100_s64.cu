@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_s64_kernel(const __
   using L = Smem<D>;
   constexpr int kHalves = D / 64;
   extern __shared__ uint8_t smem_dyn[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);  // an offset, so that the compiler keeps seeing shared memory
   Barriers* bar = reinterpret_cast<Barriers*>(smem + L::kBar);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
