@@ -56,7 +56,7 @@ CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from the ncu captures summarised
 # under profiles/: bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
-NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (979.70e6 + 14.65e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6}
+NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6}
 
 
 def causal_flops(B, M, H, D):
