@@ -226,7 +226,20 @@ def gpu_quantize_int4(x):
     return torch.cat([ss, packed], dim=-1).contiguous().view(torch.int32)
 
 
-def decode_workload(dev, quant: bool, seed: int = 0, B: int = 64):
+def gpu_quantize_fp8(x):
+    """Device-side restatement of the row-wise fp8 quantiser of the reference's
+    tests (tests/utils.py:311-333), used only to prepare synthetic caches:
+    returns (int32 words of four e4m3 values, int32 [scale | shift << 16])."""
+    xf = x.float()
+    shift = xf.mean(-1, keepdim=True)
+    c = xf - shift
+    scale = torch.nan_to_num(448.0 / c.abs().amax(-1, keepdim=True), posinf=1.0)
+    q8 = (c / scale).to(torch.float8_e4m3fn)
+    ss = torch.cat([scale.half().view(torch.uint8), shift.half().view(torch.uint8)], dim=-1).contiguous().view(torch.int32)
+    return q8.contiguous().view(torch.int32), ss.squeeze(-1)
+
+
+def decode_workload(dev, quant, seed: int = 0, B: int = 64):
     from xformers_b200.ops.fmha import attn_bias as ab
 
     g = torch.Generator().manual_seed(seed)
@@ -247,7 +260,20 @@ def decode_workload(dev, quant: bool, seed: int = 0, B: int = 64):
     shape = (1, pool * page, Hkv, 1, D)
     k = torch.randn(shape, generator=gd, device=dev, dtype=torch.bfloat16)
     v = torch.randn(shape, generator=gd, device=dev, dtype=torch.bfloat16)
-    if quant:
+    kss = vss = None
+    if quant == "fp8":
+        kq = torch.empty(shape[:-1] + (D // 4,), dtype=torch.int32, device=dev)
+        vq = torch.empty_like(kq)
+        kss = torch.empty(shape[:-1], dtype=torch.int32, device=dev)
+        vss = torch.empty_like(kss)
+        step = 64 * page
+        for lo in range(0, pool * page, step):
+            kq[:, lo : lo + step], kss[:, lo : lo + step] = gpu_quantize_fp8(k[:, lo : lo + step])
+            vq[:, lo : lo + step], vss[:, lo : lo + step] = gpu_quantize_fp8(v[:, lo : lo + step])
+        k, v = kq, vq
+        row_bytes = D + 4
+        kss, vss = kss.expand(-1, -1, -1, G).contiguous(), vss.expand(-1, -1, -1, G).contiguous()
+    elif quant:
         kq = torch.empty(shape[:-1] + (D // 8 + 1,), dtype=torch.int32, device=dev)
         vq = torch.empty_like(kq)
         step = 64 * page
@@ -263,6 +289,8 @@ def decode_workload(dev, quant: bool, seed: int = 0, B: int = 64):
     bias = ab.PagedBlockDiagonalPaddedKeysMask.from_seqlens([1] * B, lens.tolist(), table.to(dev), page)
     kv_bytes = float(lens.sum()) * Hkv * 2 * row_bytes
     qo_bytes = 2.0 * B * Hkv * G * D * 2
+    if quant == "fp8":
+        return q, k, v, bias, kv_bytes + qo_bytes + table.numel() * 4, kss, vss
     return q, k, v, bias, kv_bytes + qo_bytes + table.numel() * 4
 
 
@@ -275,7 +303,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="headline only (no decode / varlen / long-context / CPU legs)")
     ap.add_argument("--e2e-mode", default="pipelined", choices=["pipelined", "serial"],
                     help="e2e leg: overlap upload / kernel / read-back of neighbouring steps, or run them back to back")
-    ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,varlen,long,cpu")
+    ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,decode_fp8,varlen,long,cpu")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: one batch of the headline configuration (128 MB of tensors, still larger than L2) and 16 decode sequences; not a bench value")
     args = ap.parse_args()
@@ -300,7 +328,7 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "varlen", "long", "cpu"}
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "decode_fp8", "varlen", "long", "cpu"}
     if args.skip_extras:
         legs &= {"prefill", "e2e"}
     peaks = load_peaks()
@@ -437,6 +465,22 @@ def main():
             del dq, dk, dv, dbias
             torch.cuda.empty_cache()
         barrier()
+
+    if "decode_fp8" in legs and rank == 0:
+        dq, dk, dv, dbias, nbytes, kss, vss = decode_workload(dev, "fp8", B=16 if args.small else 64)
+        inp = fmha.triton_splitk.InputsFp8(query=dq, key=dk, value=dv, attn_bias=dbias, k_fp8_scale_shift=kss, v_fp8_scale_shift=vss)
+        fn = lambda: fmha._memory_efficient_attention_forward(inp, op=fmha.b200_splitk.FwOp)
+        d_steps = max(5, min(args.steps, 30))
+        ms, win = event_time_ms(fn, d_steps, 3)
+        windows.append(win)
+        gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
+        out_line["decode_fp8"] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes,
+                                  "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                               "frac": gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"]},
+                                  "workload": "as decode_bf16 with a row-wise fp8 cache (128 B + one scale/shift word per token and head)"}
+        del dq, dk, dv, dbias, kss, vss, inp
+        torch.cuda.empty_cache()
+    barrier()
 
     # ------------------------------------------- packed varlen GQA (rank 0)
     if "varlen" in legs and rank == 0:

@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define XFB200_ABI_VERSION 1
+#define XFB200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define XFB200_API __attribute__((visibility("default")))
@@ -54,7 +54,7 @@ enum { XFB200_BF16 = 0, XFB200_F16 = 1, XFB200_F32 = 2 };
  * 0 none, 1 causal aligned top-left, 2 causal aligned bottom-right. */
 enum { XFB200_MASK_NONE = 0, XFB200_MASK_CAUSAL_TOP_LEFT = 1, XFB200_MASK_CAUSAL_BOTTOM_RIGHT = 2 };
 
-enum { XFB200_KV_PLAIN = 0, XFB200_KV_INT4_ROWWISE = 1 };
+enum { XFB200_KV_PLAIN = 0, XFB200_KV_INT4_ROWWISE = 1, XFB200_KV_FP8_ROWWISE = 2 };
 
 /* [B, M, G, H, D] view of a tensor; a 4-D BMHK tensor has G = 1.  The head
  * stride of K/V may be 0 (MQA/GQA: one KV head broadcast over H query heads);
@@ -135,7 +135,7 @@ typedef struct {
   const int32_t* seqlen_k;     /* [batch]; NULL: every sequence has kv_padding keys */
   const int32_t* block_tables; /* NULL: padded cache */
   int32_t dtype;     /* of q and out (and of k/v when kv_format == PLAIN) */
-  int32_t kv_format; /* XFB200_KV_PLAIN | XFB200_KV_INT4_ROWWISE */
+  int32_t kv_format; /* XFB200_KV_PLAIN | XFB200_KV_INT4_ROWWISE | XFB200_KV_FP8_ROWWISE */
   int32_t num_quant_groups;
   int32_t batch;
   int32_t mq; /* queries per sequence (uniform) */
@@ -155,6 +155,13 @@ typedef struct {
   float scale;
   int32_t out_dtype;
   int32_t reserved;
+  /* XFB200_KV_FP8_ROWWISE only (xformers/ops/fmha/triton_splitk.py:28, InputsFp8; tests/utils.py:311-340):
+   * k/v are int32 words of four e4m3 values, x = fp8 * scale + shift with one
+   * (fp16 scale | fp16 shift << 16) word per token and kv head; strides in words. */
+  const int32_t* k_scale_shift;
+  const int32_t* v_scale_shift;
+  int64_t ks_stride_m, ks_stride_g;
+  int64_t vs_stride_m, vs_stride_g;
 } xfb200_decode_params;
 
 XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t kv_heads, int32_t q_per_kv, int32_t head_dim,

@@ -27,6 +27,14 @@ from .masks import (  # noqa: F401
     local_mask,
 )
 from .int4 import quantize_kv_int4, dequantize_kv_int4  # noqa: F401
+from .fp8 import (  # noqa: F401
+    quantize_fp8_asymmetric,
+    dequantize_fp8_asymmetric,
+    combine_scale_shift,
+    split_scale_shift,
+    pack_fp8_words,
+    unpack_fp8_words,
+)
 from .paged import gather_paged, scatter_to_pages, physical_rows  # noqa: F401
 from .merge import merge_attentions_ref  # noqa: F401
 from .splitk import ref_attention_splitk  # noqa: F401

@@ -289,3 +289,24 @@ def test_nan_in_hidden_keys_does_not_leak():
         v[0, b * 8 + n : (b + 1) * 8] = float("nan")
     got = oracle.ref_attention(q, k, v, bias)
     assert not got.isnan().any() and torch.equal(ref, got)
+
+
+def test_fp8_rowwise_format():
+    """tests/utils.py:311-340: one int32 per row carries fp16 scale (low half)
+    and fp16 shift (high half); four e4m3 values per int32 word, element e in
+    byte e; x = fp8 * scale + shift."""
+    import struct
+
+    w = oracle.combine_scale_shift(torch.tensor([1.0, 0.5]), torch.tensor([2.0, -1.0]))
+    assert w.dtype == torch.int32 and [int(x) & 0xFFFFFFFF for x in w] == [0x40003C00, 0xBC003800]
+    sc, sh = oracle.split_scale_shift(w)
+    assert sc.tolist() == [1.0, 0.5] and sh.tolist() == [2.0, -1.0]
+    vals = torch.tensor([[1.0, -2.0, 0.5, 448.0]]).to(oracle.fp8.FP8)
+    words = oracle.pack_fp8_words(vals)
+    assert words.shape == (1, 1) and (int(words[0, 0]) & 0xFFFFFFFF) == struct.unpack("<I", bytes([0x38, 0xC0, 0x30, 0x7E]))[0]
+    assert torch.equal(oracle.unpack_fp8_words(words).float(), vals.float())
+    x = torch.randn(7, 128, generator=torch.Generator().manual_seed(0))
+    q, scale, shift = oracle.quantize_fp8_asymmetric(x)
+    assert torch.allclose(shift, x.mean(dim=1)) and torch.allclose(scale, 448.0 / (x - shift[:, None]).abs().max(dim=1)[0])
+    back = oracle.dequantize_fp8_asymmetric(q, scale, shift)
+    assert (back - x).abs().max() < 0.5  # the reference's scale choice uses little of the e4m3 range

@@ -12,7 +12,7 @@ import os
 from pathlib import Path
 from typing import Optional
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 XFB200_OK = 0
 XFB200_E_INVALID = -1
@@ -22,7 +22,7 @@ XFB200_E_DEVICE = -4
 
 BF16, F16, F32 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL_TOP_LEFT, MASK_CAUSAL_BOTTOM_RIGHT = 0, 1, 2
-KV_PLAIN, KV_INT4_ROWWISE = 0, 1
+KV_PLAIN, KV_INT4_ROWWISE, KV_FP8_ROWWISE = 0, 1, 2
 MERGE_MAX_PTRS = 32
 DECODE_STATIC_SCRATCH_BYTES = 16 << 20
 
@@ -115,6 +115,12 @@ class DecodeParams(C.Structure):
         ("scale", C.c_float),
         ("out_dtype", C.c_int32),
         ("reserved", C.c_int32),
+        ("k_scale_shift", C.c_void_p),
+        ("v_scale_shift", C.c_void_p),
+        ("ks_stride_m", C.c_int64),
+        ("ks_stride_g", C.c_int64),
+        ("vs_stride_m", C.c_int64),
+        ("vs_stride_g", C.c_int64),
     ]
 
 

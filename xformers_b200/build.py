@@ -39,6 +39,11 @@ NVCC_FLAGS = [
     "-fPIC",
     "-Xcompiler",
     "-fvisibility=hidden",
+    # a function that can fall off its end without a return value is an error, not a warning
+    "-Xcompiler",
+    "-Werror=return-type",
+    "-Werror",
+    "cross-execution-space-call",
 ]
 
 

@@ -53,6 +53,10 @@ struct DecodeArgs {
                        // 3: tiled TMA, a whole run of tokens per copy, 128-byte swizzled in shared memory (16-bit cache)
   int32_t box_tok;     // mode 3: tokens per tiled copy (power of two, 8..256, divides the stage)
   int32_t kv_bytes;    // bytes of the K (or V) part of a stage
+  int32_t stage_bytes; // bytes of a whole stage (K part, V part, fp8: the scale/shift words of both)
+  const int32_t* k_ss; // fp8: scale/shift words of K and V, strides in words
+  const int32_t* v_ss;
+  int64_t kss_m, kss_g, vss_m, vss_g;
   int32_t copy_group;  // tokens per bulk copy (int4 only, mode 0)
   int32_t stages;         // depth of the shared-memory ring
   int32_t q_first_stage;  // stages >= this one hold the staged Q until q_done
@@ -101,30 +105,40 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
 }
 
 // Shared-memory geometry of one stage.
-template <int D, bool kInt4>
+// cache formats (the template parameter kFmt of what follows)
+constexpr int kFmtPlain = 0, kFmtInt4 = 1, kFmtFp8 = 2;
+
+template <int D, int kFmt>
 struct DecStage {
-  // plain: one row per token = hb heads * D elements (+16 B pad against bank conflicts)
+  // plain: one row per token = hb heads * D elements (+16 B pad against bank conflicts; unpadded and
+  //        swizzled when the stage is filled by a tiled copy)
   // int4 : one row per token = hb heads * (1 + D/8) words, unpadded
-  __host__ __device__ static int row_bytes(int hb) { return kInt4 ? hb * (1 + D / 8) * 4 : hb * D * 2 + 16; }
-  // sub-tiles of 16 tokens each warp takes from one stage: the packed cache is 4x
+  // fp8  : [head][token][D bytes] boxes (tiled copy, 128-byte swizzle), then the scale/shift words
+  __host__ __device__ static int row_bytes(int hb) {
+    return kFmt == kFmtInt4 ? hb * (1 + D / 8) * 4 : kFmt == kFmtFp8 ? hb * D : hb * D * 2 + 16;
+  }
+  // sub-tiles of 16 tokens each warp takes from one stage: the int4 cache is 4x
   // denser, so its stages hold more tokens to keep the per-stage overhead
   // (barrier round trip, page-table look-ups of the producer) off the critical path
-  static constexpr int kSubTiles = kInt4 ? 2 : 1;
+  static constexpr int kSubTiles = kFmt == kFmtInt4 ? 2 : 1;
   __host__ __device__ static int tokens(int hb) { return 16 * kSubTiles * (kDecConsumerWarps / hb); }
   __host__ __device__ static int kv_bytes(int hb) {  // K or V part of a stage, rounded to 128 B
     return (row_bytes(hb) * tokens(hb) + 127) & ~127;
   }
+  // fp8: scale/shift words of the K (or V) rows of a stage, one per token and head
+  __host__ __device__ static int ss_bytes(int hb) { return kFmt == kFmtFp8 ? tokens(hb) * hb * 4 : 0; }
 };
 
 constexpr int kDecMaxStages = 12;
 // Bytes of cache in flight per SM are what hide the HBM latency.  The 16-bit
 // kernel runs one CTA per SM with a ~212 KB ring.  The int4 kernel does 4x the
 // arithmetic per byte and each warp's sub-tile is one long dependency chain, so
-// it runs two CTAs per SM (twice the warps to interleave) with half the ring each.
-template <bool kInt4>
+// it runs two CTAs per SM (twice the warps to interleave) with half the ring each;
+// so does the fp8 kernel, which shares its structure.
+template <int kFmt>
 struct DecOccupancy {
-  static constexpr int kCtasPerSm = kInt4 ? 2 : 1;
-  static constexpr int kRingBudget = kInt4 ? 106 * 1024 : 212 * 1024;
+  static constexpr int kCtasPerSm = kFmt != kFmtPlain ? 2 : 1;
+  static constexpr int kRingBudget = kFmt != kFmtPlain ? 106 * 1024 : 212 * 1024;
 };
 
 // What a consumer warp needs to know about its CTA.
@@ -138,7 +152,7 @@ struct DecWarp {
   int lane, hw, sub, wph, row0;
   int b, head;  // sequence and kv head of this warp
   int chunk_lo, chunk_hi, kv_len, n_tiles;
-  int tok_per_stage, kv_bytes, row_bytes, stages;
+  int tok_per_stage, kv_bytes, stage_bytes, row_bytes, stages;
 };
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
@@ -157,7 +171,7 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
   constexpr int KS = D / 16;  // k-steps of the QK^T product
   constexpr int NT = D / 8;   // n-tiles of the PV product
   constexpr int kCmbRow = D + 2;
-  constexpr int kSps = DecStage<D, false>::kSubTiles;
+  constexpr int kSps = DecStage<D, kFmtPlain>::kSubTiles;
   const int lane = w.lane, r = lane >> 2, c = lane & 3;
   const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
   // Tiled copies leave a stage as boxes of [column group][token][128 B] with the
@@ -223,7 +237,7 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
       const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
       const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;  // its first token
       if (t_sub >= w.chunk_hi) continue;
-      const uint8_t* ks_ = w.stage_base + st * 2 * w.kv_bytes;
+      const uint8_t* ks_ = w.stage_base + st * w.stage_bytes;
       const uint8_t* vs_ = ks_ + w.kv_bytes;
       const bool ragged = t_sub + 16 > w.chunk_hi;
 
@@ -406,7 +420,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   constexpr int WPT = D / 64;   // V words per thread and token
   constexpr int kQRowBytes = D * 2;
   constexpr int kCmbRow = D + 2;
-  constexpr int kSps = DecStage<D, true>::kSubTiles;
+  constexpr int kSps = DecStage<D, kFmtInt4>::kSubTiles;
   // log2 of the largest probability taken against a stale maximum; P * scale(V)
   // is an f16 value, so 2^kLazy * scale must stay below 65504
   constexpr float kLazy = 4.f;
@@ -506,7 +520,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
       if (lane == 0) atomicExch(a.status, 2);
       break;
     }
-    const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * 2 * w.kv_bytes) + hw * W;
+    const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * w.stage_bytes) + hw * W;
     const uint32_t* vst = kst + w.kv_bytes / 4;
 #pragma unroll 1
     for (int sp = 0; sp < kSps; ++sp) {
@@ -676,14 +690,295 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   }
 }
 
-template <int D, int MT, bool kInt4, bool kBf16>
-__global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
-  using Stage = DecStage<D, kInt4>;
+// ---------------------------------------------------------------------------
+// fp8 row-wise cache (four e4m3 values per int32 word, one fp16 scale / shift
+// pair per token and kv head in a tensor of its own; tests/utils.py:311-340 of
+// the reference).  Same structure as the int4 consumer: transposed products in
+// f16, tokens = M rows of S^T = K Q^T and K dimension of O^T = V^T P^T, K's
+// scale/shift applied to the scores, V's scale folded into P, its shift a
+// per-row term.  A stage is [head][token][128 B] as the tiled copy left it
+// (16-byte chunks XOR-ed with token & 7).
+//   K: thread (r, c) reads word c of chunk ks of tokens r and r + 8: elements
+//      d = 16 ks + 4 c + {0, 1 | 2, 3} are the k-slots (2c, 2c+1 | 2c+8, 2c+9)
+//      of k-step ks; one cvt.f16x2.e4m3x2 per pair.
+//   V: thread (r, c) reads word r + 8 wj of tokens 2c, 2c+1, 2c+8, 2c+9; a byte
+//      permute puts the same element of two neighbouring tokens side by side,
+//      so that the conversion yields A-fragment registers: m-tile 2 wj + p
+//      holds d = 4 (r + 8 wj) + p in row r and d + 2 in row r + 8.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cvt_e4m3x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, l;\n\tcvt.rn.f16x2.e4m3x2 %1, h;\n\t}" : "=r"(lo), "=r"(hi) : "r"(w));
+}
+
+template <int D, int NTQ, bool kBf16>
+__device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& w) {
+  static_assert(D == 128, "fp8 rows are one 128-byte swizzle row");
+  using T = typename Half2Type<kBf16>::T;
+  constexpr int KS = D / 16;   // k-steps of K Q^T
+  constexpr int MTV = D / 16;  // m-tiles of V^T P^T
+  constexpr int WJ = D / 32;   // V words per thread and token
+  constexpr int kQRowBytes = D * 2;
+  constexpr int kCmbRow = D + 2;
+  constexpr int kSps = DecStage<D, kFmtFp8>::kSubTiles;
+  constexpr float kLazy = 4.f;  // as in the int4 consumer
+  const int lane = w.lane, r = lane >> 2, c = lane & 3;
+  const int R = a.rows, hw = w.hw, hb = a.hb;
+  const int box_shift = __ffs(a.box_tok) - 1;
+  const int head_bytes = a.box_tok * 128;      // one head of a box
+  const int box_bytes = head_bytes * hb;
+
+  // B fragments of Q^T (n = query row nt*8 + r): f16 of q * 2^-k, k per row so that nothing overflows
+  uint32_t qf[NTQ][KS][2];
+  float qsum[NTQ][2];  // sum over d of the scaled q, rows 2c, 2c+1 of each n-tile
+  float qfac[NTQ][2];  // 2^k * softmax scale * log2(e) of those rows
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+    const T* qrow = reinterpret_cast<const T*>(w.qs + (nt * 8 + r) * kQRowBytes);
+    float amax = 0.f;
+    for (int d = c; d < D; d += 4) amax = fmaxf(amax, fabsf(float(qrow[d])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int kexp = 0;
+    if (amax >= 32768.f && amax < INFINITY) kexp = int(__float_as_uint(amax) >> 23) - 127 - 14;
+    const float qmul = __uint_as_float(uint32_t(127 - kexp) << 23);  // 2^-k
+    float sr = 0.f;
+    for (int d = c; d < D; d += 4) sr += __half2float(__float2half_rn(float(qrow[d]) * qmul));
+    sr += __shfl_xor_sync(0xffffffffu, sr, 1);
+    sr += __shfl_xor_sync(0xffffffffu, sr, 2);
+    const float fac = __uint_as_float(uint32_t(127 + kexp) << 23) * a.scale_log2;
+    qsum[nt][0] = __shfl_sync(0xffffffffu, sr, 8 * c);
+    qsum[nt][1] = __shfl_sync(0xffffffffu, sr, 8 * c + 4);
+    qfac[nt][0] = __shfl_sync(0xffffffffu, fac, 8 * c);
+    qfac[nt][1] = __shfl_sync(0xffffffffu, fac, 8 * c + 4);
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const T* q0 = qrow + 16 * ks + 4 * c;
+      const __half2 h01 = __floats2half2_rn(float(q0[0]) * qmul, float(q0[1]) * qmul);
+      const __half2 h23 = __floats2half2_rn(float(q0[2]) * qmul, float(q0[3]) * qmul);
+      qf[nt][ks][0] = *reinterpret_cast<const uint32_t*>(&h01);
+      qf[nt][ks][1] = *reinterpret_cast<const uint32_t*>(&h23);
+    }
+  }
+  // Q now lives in registers: release the staging area to the producer
+  __syncwarp();
+  if (lane == 0) mbar_arrive(w.q_done_bar);
+
+  int lim[NTQ][2];
+  int lim_min = w.chunk_hi;
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = w.row0 + nt * 8 + 2 * c + e;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
+      lim_min = min(lim_min, l);
+    }
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
+
+  float acc[MTV][NTQ][4];
+  float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+    corr[nt][0] = corr[nt][1] = 0.f;
+  }
+
+  for (int tile = 0; tile < w.n_tiles; ++tile) {
+    const int st = tile % w.stages;
+    if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
+      if (lane == 0) atomicExch(a.status, 2);
+      break;
+    }
+    const uint8_t* kst = w.stage_base + st * w.stage_bytes;
+    const uint8_t* vst = kst + w.kv_bytes;
+    const uint32_t* ssk = reinterpret_cast<const uint32_t*>(kst + 2 * w.kv_bytes) + hw * w.tok_per_stage;
+    const uint32_t* ssv = ssk + hb * w.tok_per_stage;
+#pragma unroll 1
+    for (int sp = 0; sp < kSps; ++sp) {
+      const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
+      const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;  // its first token
+      if (t_sub >= w.chunk_hi) continue;
+      const int tok0 = usub * 16;  // first token of the sub-tile inside the stage (a multiple of 16 inside its box)
+      const int boff = (tok0 >> box_shift) * box_bytes + hw * head_bytes + (tok0 & (a.box_tok - 1)) * 128;
+
+      // ------------------------------------------- S^T = K Q^T (16 tokens x 8*NTQ)
+      float s[NTQ][4], s2[NTQ][4];  // two chains of dependent MMAs instead of one
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+      }
+      {
+        const uint8_t* k0 = kst + boff + r * 128 + c * 4;  // token r (chunk swizzle r & 7 = r); token r + 8 is 8 rows on, same swizzle
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int co = (ks ^ r) * 16;
+          const uint32_t w0 = *reinterpret_cast<const uint32_t*>(k0 + co);
+          const uint32_t w1 = *reinterpret_cast<const uint32_t*>(k0 + 8 * 128 + co);
+          uint32_t ka[4];
+          cvt_e4m3x4(w0, ka[0], ka[2]);
+          cvt_e4m3x4(w1, ka[1], ka[3]);
+#pragma unroll
+          for (int nt = 0; nt < NTQ; ++nt) mma_16816<false>((ks & 1) ? s2[nt] : s[nt], ka, qf[nt][ks][0], qf[nt][ks][1]);
+        }
+      }
+
+      // ------------------ scale/shift of tokens r, r+8; mask; online softmax
+      const uint32_t kw0 = ssk[tok0 + r], kw1 = ssk[tok0 + r + 8], vw0 = ssv[tok0 + r], vw1 = ssv[tok0 + r + 8];
+      const float ksc0 = half_bits_to_float(kw0 & 0xFFFFu), ksh0 = half_bits_to_float(kw0 >> 16);
+      const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
+      float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
+      float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
+      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
+      float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
+      bool need = false;
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc0[nt][e] = fmaf(ksc0, s[nt][e] + s2[nt][e], ksh0 * qsum[nt][e]) * qfac[nt][e];
+          sc1[nt][e] = fmaf(ksc1, s[nt][2 + e] + s2[nt][2 + e], ksh1 * qsum[nt][e]) * qfac[nt][e];
+        }
+      if (!all_visible) {
+        const int t0 = t_sub + r, t1 = t_sub + r + 8;
+        // tokens past the end were not copied: their scale words are garbage
+        if (t0 >= w.chunk_hi) vsc0 = 0.f, vsh0 = 0.f;
+        if (t1 >= w.chunk_hi) vsc1 = 0.f, vsh1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
+          }
+      }
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) need |= fmaxf(sc0[nt][e], sc1[nt][e]) > m_run[nt][e] + kLazy;
+      if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt) {
+          float alpha[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float mx = fmaxf(sc0[nt][e], sc1[nt][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[nt][e], mx);
+            alpha[e] = fast_exp2(m_run[nt][e] - (m_new == -INFINITY ? 0.f : m_new));
+            m_run[nt][e] = m_new;
+            l_run[nt][e] *= alpha[e];
+            corr[nt][e] *= alpha[e];
+          }
+#pragma unroll
+          for (int mt = 0; mt < MTV; ++mt) {
+            acc[mt][nt][0] *= alpha[0];
+            acc[mt][nt][1] *= alpha[1];
+            acc[mt][nt][2] *= alpha[0];
+            acc[mt][nt][3] *= alpha[1];
+          }
+        }
+      }
+      uint32_t pb[NTQ][2];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+        float p0[2], p1[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_use = m_run[nt][e] == -INFINITY ? 0.f : m_run[nt][e];
+          p0[e] = fast_exp2(sc0[nt][e] - m_use);
+          p1[e] = fast_exp2(sc1[nt][e] - m_use);
+          l_run[nt][e] += p0[e] + p1[e];
+          corr[nt][e] = fmaf(p0[e], vsh0, fmaf(p1[e], vsh1, corr[nt][e]));
+        }
+        pb[nt][0] = movmatrix_trans(pack2<false>(p0[0] * vsc0, p0[1] * vsc0));  // tokens 2c, 2c+1   of row r
+        pb[nt][1] = movmatrix_trans(pack2<false>(p1[0] * vsc1, p1[1] * vsc1));  // tokens 2c+8, 2c+9 of row r
+      }
+
+      // ------------------------------------------------- O^T += V^T P^T
+      {
+        const uint8_t* v0 = vst + boff + (2 * c) * 128 + (r & 3) * 4;  // token 2c; +128: 2c+1; +1024: 2c+8; +1152: 2c+9
+        const int x0s = (2 * c) & 7, x1s = (2 * c + 1) & 7;            // chunk swizzles of the even / odd token
+#pragma unroll
+        for (int wj = 0; wj < WJ; ++wj) {
+          const int ch = (r >> 2) + 2 * wj;  // 16-byte chunk of word r + 8 wj
+          const uint32_t xa = *reinterpret_cast<const uint32_t*>(v0 + (ch ^ x0s) * 16);
+          const uint32_t xb = *reinterpret_cast<const uint32_t*>(v0 + 128 + (ch ^ x1s) * 16);
+          const uint32_t xc = *reinterpret_cast<const uint32_t*>(v0 + 1024 + (ch ^ x0s) * 16);
+          const uint32_t xd = *reinterpret_cast<const uint32_t*>(v0 + 1152 + (ch ^ x1s) * 16);
+          // bytes (a0 b0 a1 b1) and (a2 b2 a3 b3): element e of the two tokens side by side
+          uint32_t y01[2], y23[2], z01[2], z23[2];
+          cvt_e4m3x4(__byte_perm(xa, xb, 0x5140), y01[0], y01[1]);
+          cvt_e4m3x4(__byte_perm(xa, xb, 0x7362), y23[0], y23[1]);
+          cvt_e4m3x4(__byte_perm(xc, xd, 0x5140), z01[0], z01[1]);
+          cvt_e4m3x4(__byte_perm(xc, xd, 0x7362), z23[0], z23[1]);
+#pragma unroll
+          for (int p = 0; p < 2; ++p) {
+            const uint32_t vf[4] = {y01[p], y23[p], z01[p], z23[p]};  // rows r: d = 4(r+8wj)+p, rows r+8: d+2
+#pragma unroll
+            for (int nt = 0; nt < NTQ; ++nt) mma_16816<false>(acc[wj * 2 + p][nt], vf, pb[nt][0], pb[nt][1]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&w.empty_bar[st]);
+  }
+
+  // full row sums (each thread saw tokens r and r+8 of every sub-tile)
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float l = l_run[nt][e], cs = corr[nt][e];
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l += __shfl_xor_sync(0xffffffffu, l, o);
+        cs += __shfl_xor_sync(0xffffffffu, cs, o);
+      }
+      l_run[nt][e] = l;
+      corr[nt][e] = cs;
+    }
+
+  // the ring is no longer in use once every consumer warp got here
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int d = 4 * (r + 8 * (mt >> 1)) + (mt & 1) + (q >> 1) * 2;
+        const int rr = nt * 8 + 2 * c + (q & 1);
+        w.mine[rr * kCmbRow + d] = acc[mt][nt][q] + corr[nt][q & 1];
+      }
+    if (r == 0) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D] = m_run[nt][e];
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D + 1] = l_run[nt][e];
+      }
+    }
+  }
+}
+
+template <int D, int MT, int kFmt, bool kBf16>
+__global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
+  using Stage = DecStage<D, kFmt>;
+  constexpr bool kInt4 = kFmt == kFmtInt4, kFp8 = kFmt == kFmtFp8, kQuant = kFmt != kFmtPlain;
   using T = typename Half2Type<kBf16>::T;
   constexpr int W = 1 + D / 8;  // int4 words per row (one quantisation group)
   // query rows of one kv head per CTA: MT m-tiles of 16 (16-bit cache) or MT
-  // n-tiles of 8 (int4 cache, transposed products)
-  constexpr int ROWS = kInt4 ? 8 * MT : 16 * MT;
+  // n-tiles of 8 (int4 and fp8 caches, transposed products)
+  constexpr int ROWS = kQuant ? 8 * MT : 16 * MT;
 
   // bytes in flight per SM are what hide HBM latency: the ring takes ~200 KB,
   // i.e. 3 stages of 64 KB (bf16, D = 128) up to 12 stages of 17 KB (int4)
@@ -701,7 +996,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   const int lane = threadIdx.x & 31;
   const int hb = a.hb;
   const int wph = kDecConsumerWarps / hb;  // consumer warps per kv head
-  constexpr int kSps = DecStage<D, kInt4>::kSubTiles;
+  constexpr int kSps = DecStage<D, kFmt>::kSubTiles;
   const int TOK = 16 * wph * kSps;
 
   const int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
@@ -729,14 +1024,14 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   }
   const int n_tiles = (chunk_hi - chunk_lo + TOK - 1) / TOK;
 
-  const int kv_bytes = a.kv_bytes;
+  const int kv_bytes = a.kv_bytes, stage_bytes = a.stage_bytes;
   const int row_bytes = Stage::row_bytes(hb);
   // swizzled tiles want 1024-byte aligned stages; the static barriers precede the dynamic part
   // (an offset from the array, not a cast of a rounded integer: the compiler must keep seeing shared memory)
   uint8_t* stage_base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   // Q is staged once in the region of the LAST stages; the producer does not
   // fill those before every consumer warp has taken its Q fragments
-  uint8_t* q_smem = stage_base + a.q_first_stage * 2 * kv_bytes;     // 8 warps * 16*MT rows * D*2 B
+  uint8_t* q_smem = stage_base + a.q_first_stage * stage_bytes;     // 8 warps * 16*MT rows * D*2 B
   constexpr int kQRowBytes = D * 2;
 
   if (threadIdx.x == 0) {
@@ -753,9 +1048,27 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
     // ------------------------------------------------------------ producer
     const uint8_t* kg = reinterpret_cast<const uint8_t*>(a.k);
     const uint8_t* vg = reinterpret_cast<const uint8_t*>(a.v);
-    constexpr int kElem = kInt4 ? 4 : 2;
-    constexpr int kHeadBytes = kInt4 ? W * 4 : D * 2;
+    constexpr int kElem = kQuant ? 4 : 2;  // bytes per element of the k/v tensors (int32 words when quantised)
+    constexpr int kHeadBytes = kInt4 ? W * 4 : kFp8 ? D : D * 2;
     const int head0 = hblk * hb;
+    // fp8: scale/shift words of the next tile, 128 per tensor and stage = 4 per lane
+    uint32_t ss_k[4] = {0, 0, 0, 0}, ss_v[4] = {0, 0, 0, 0};
+    auto load_ss = [&](int tile) {
+      const int t0 = chunk_lo + tile * TOK;
+      const int nvalid = min(TOK, chunk_hi - t0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = lane + 32 * j;
+        if (i < nvalid * hb) {
+          const int hh = i / nvalid, t = t0 + i % nvalid;
+          const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
+                                             : int64_t(b) * a.kv_padding + t;
+          ss_k[j] = uint32_t(__ldg(a.k_ss + row * a.kss_m + (head0 + hh) * a.kss_g));
+          ss_v[j] = uint32_t(__ldg(a.v_ss + row * a.vss_m + (head0 + hh) * a.vss_g));
+        }
+      }
+    };
+    if constexpr (kFp8) load_ss(0);
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int st = tile % kDecStages;
       if (tile >= kDecStages) {
@@ -763,7 +1076,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
           if (lane == 0) atomicExch(a.status, 1);
           return;
         }
-      } else if (kInt4 && tile == a.q_first_stage) {
+      } else if (kQuant && tile == a.q_first_stage) {
         if (!mbar_wait(&q_done_bar, 0)) {
           if (lane == 0) atomicExch(a.status, 3);
           return;
@@ -771,21 +1084,47 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
       }
       const int t0 = chunk_lo + tile * TOK;
       const int nvalid = min(TOK, chunk_hi - t0);
-      uint8_t* ks = stage_base + st * 2 * kv_bytes;
+      uint8_t* ks = stage_base + st * stage_bytes;
       uint8_t* vs = ks + kv_bytes;
       if (a.copy_mode == 3) {
         // one tiled copy per run of box_tok tokens: {64 elements} x {box_tok rows} x {hb*D/64 column groups}
         if (lane == 0) {
           const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
           const uint32_t box_bytes = uint32_t(a.box_tok) * hb * kHeadBytes;
-          mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
+          if constexpr (!kFp8) mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
           for (int bx = 0; bx < nbox; ++bx) {
             const int t = t0 + bx * a.box_tok;
             const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
                                                : int64_t(b) * a.kv_padding + t;
-            tma_load_3d(ks + bx * box_bytes, &a.tm_k, &full_bar[st], 0, int(row), head0 * (D / 64));
-            tma_load_3d(vs + bx * box_bytes, &a.tm_v, &full_bar[st], 0, int(row), head0 * (D / 64));
+            // third coordinate: 128-byte column group (16-bit cache) or kv head (fp8: a head is one 128-byte row)
+            const int c2 = kFp8 ? head0 : head0 * (D / 64);
+            tma_load_3d(ks + bx * box_bytes, &a.tm_k, &full_bar[st], 0, int(row), c2);
+            tma_load_3d(vs + bx * box_bytes, &a.tm_v, &full_bar[st], 0, int(row), c2);
           }
+        }
+        if constexpr (kFp8) {
+          // The scale/shift words travel by ordinary loads: [head][token] behind the K
+          // and V parts of the stage.  They were requested one tile ahead (ss_k / ss_v
+          // registers), so their latency overlaps the wait for the stage.  The arrival
+          // that opens the transaction count comes last, after these stores, so that
+          // the barrier cannot complete before they are visible.
+          uint32_t* ssk = reinterpret_cast<uint32_t*>(ks + 2 * kv_bytes);
+          uint32_t* ssv = ssk + hb * TOK;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int i = lane + 32 * j;
+            if (i < nvalid * hb) {
+              const int hh = i / nvalid, tok = i % nvalid;
+              ssk[hh * TOK + tok] = ss_k[j];
+              ssv[hh * TOK + tok] = ss_v[j];
+            }
+          }
+          __syncwarp();
+          if (lane == 0) {
+            const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
+            mbar_expect_tx(&full_bar[st], uint32_t(nbox) * uint32_t(a.box_tok) * hb * kHeadBytes * 2u);
+          }
+          if (tile + 1 < n_tiles) load_ss(tile + 1);
         }
         __syncwarp();
         continue;
@@ -844,7 +1183,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   // nothing consumes yet could still be in flight when the staging area is handed
   // back to the copy engine.  The int4 path converts what it loads before it
   // arrives on q_done, so its loads have returned by then.)
-  if constexpr (kInt4) {
+  if constexpr (kQuant) {
     uint8_t* qs = q_smem + warp * ROWS * kQRowBytes;
     const T* qg = reinterpret_cast<const T*>(a.q);
     for (int i = lane; i < ROWS * (D / 8); i += 32) {
@@ -871,9 +1210,11 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kInt4>::kCtasPerSm) 
   w.lane = lane, w.hw = hw, w.sub = sub, w.wph = wph, w.row0 = row0;
   w.b = b, w.head = head;
   w.chunk_lo = chunk_lo, w.chunk_hi = chunk_hi, w.kv_len = kv_len, w.n_tiles = n_tiles;
-  w.tok_per_stage = TOK, w.kv_bytes = kv_bytes, w.row_bytes = row_bytes, w.stages = kDecStages;
+  w.tok_per_stage = TOK, w.kv_bytes = kv_bytes, w.stage_bytes = stage_bytes, w.row_bytes = row_bytes, w.stages = kDecStages;
   if constexpr (kInt4)
     consume_int4<D, MT, kBf16>(a, w);
+  else if constexpr (kFp8)
+    consume_fp8<D, MT, kBf16>(a, w);
   else
     consume_plain<D, MT, kBf16>(a, w);
   asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
@@ -1017,28 +1358,32 @@ int decode_chunk_tokens(int kv_bound, int split_k) {
   return c < kDecChunkAlign ? kDecChunkAlign : c;
 }
 
-template <int D, int MT, bool kInt4, bool kBf16>
+template <int D, int MT, int kFmt, bool kBf16>
 static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
-  using Stage = DecStage<D, kInt4>;
-  constexpr int ROWS = kInt4 ? 8 * MT : 16 * MT;
+  using Stage = DecStage<D, kFmt>;
+  constexpr bool kQuant = kFmt != kFmtPlain;
+  constexpr int ROWS = kQuant ? 8 * MT : 16 * MT;
   // tiled copies need no row padding
-  const int kv_bytes = a_in.copy_mode == 3 ? Stage::tokens(a_in.hb) * a_in.hb * D * 2 : Stage::kv_bytes(a_in.hb);
-  const size_t stage_bytes = 2 * size_t(kv_bytes);
+  const int kv_bytes = kFmt == kFmtFp8      ? Stage::tokens(a_in.hb) * a_in.hb * D
+                       : a_in.copy_mode == 3 ? Stage::tokens(a_in.hb) * a_in.hb * D * 2
+                                             : Stage::kv_bytes(a_in.hb);
+  const size_t stage_bytes = 2 * size_t(kv_bytes) + 2 * size_t(Stage::ss_bytes(a_in.hb));
   const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
-  int stages = int(DecOccupancy<kInt4>::kRingBudget / stage_bytes);
+  int stages = int(DecOccupancy<kFmt>::kRingBudget / stage_bytes);
   stages = stages > kDecMaxStages ? kDecMaxStages : stages;
-  const int q_stages = kInt4 ? int((qbytes + stage_bytes - 1) / stage_bytes) : 0;  // only the int4 path stages Q
+  const int q_stages = kQuant ? int((qbytes + stage_bytes - 1) / stage_bytes) : 0;  // only the quantised paths stage Q
   if (stages < 2 || q_stages > stages) return set_error(XFB200_E_UNSUPPORTED, "decode: shared-memory ring too small for this shape");
   DecodeArgs a = a_in;
   a.stages = stages;
   a.q_first_stage = stages - q_stages;
   a.kv_bytes = kv_bytes;
+  a.stage_bytes = int(stage_bytes);
   const size_t ring = stages * stage_bytes + 1024;  // the kernel aligns the ring to 1024 B
   const size_t smem = ring > cmb ? ring : cmb;
-  auto kern = decode_splitk_kernel<D, MT, kInt4, kBf16>;
+  auto kern = decode_splitk_kernel<D, MT, kFmt, kBf16>;
   // 227 KB per CTA includes the static part (the mbarriers)
-  if (smem + 1024 > size_t(227 * 1024) / DecOccupancy<kInt4>::kCtasPerSm) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
+  if (smem + 1024 > size_t(227 * 1024) / DecOccupancy<kFmt>::kCtasPerSm) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
   static size_t configured = 0;  // per instantiation: largest size opted into so far
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -1057,10 +1402,10 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   return rc;
 }
 
-template <int D, bool kInt4, bool kBf16>
+template <int D, int kFmt, bool kBf16>
 static int launch_decode_mt(const DecodeArgs& a, int mt, int head_blocks, cudaStream_t stream) {
-  if (mt == 1) return launch_decode_t<D, 1, kInt4, kBf16>(a, head_blocks, stream);
-  return launch_decode_t<D, 2, kInt4, kBf16>(a, head_blocks, stream);
+  if (mt == 1) return launch_decode_t<D, 1, kFmt, kBf16>(a, head_blocks, stream);
+  return launch_decode_t<D, 2, kFmt, kBf16>(a, head_blocks, stream);
 }
 
 }  // namespace xfb
@@ -1085,9 +1430,13 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     return set_error(XFB200_E_UNSUPPORTED, "decode: head_dim %d not in {64, 128}", p->head_dim);
   if (p->dtype != XFB200_BF16 && p->dtype != XFB200_F16) return set_error(XFB200_E_INVALID, "decode: q dtype must be bf16 or f16");
   const bool int4 = p->kv_format == XFB200_KV_INT4_ROWWISE;
+  const bool fp8 = p->kv_format == XFB200_KV_FP8_ROWWISE;
   if (int4 && p->num_quant_groups != 1)
     return set_error(XFB200_E_UNSUPPORTED, "decode: int4 cache with %d quantisation groups per row (only 1)", p->num_quant_groups);
-  if (!int4 && p->kv_format != XFB200_KV_PLAIN) return set_error(XFB200_E_INVALID, "decode: bad kv_format %d", p->kv_format);
+  if (!int4 && !fp8 && p->kv_format != XFB200_KV_PLAIN) return set_error(XFB200_E_INVALID, "decode: bad kv_format %d", p->kv_format);
+  if (fp8 && (p->k_scale_shift == nullptr || p->v_scale_shift == nullptr))
+    return set_error(XFB200_E_INVALID, "decode: an fp8 cache needs k_scale_shift and v_scale_shift");
+  if (fp8 && p->head_dim != 128) return set_error(XFB200_E_UNSUPPORTED, "decode: fp8 cache with head_dim %d (only 128)", p->head_dim);
   if (p->split_k < 1 || p->split_k > 1024) return set_error(XFB200_E_INVALID, "decode: split_k %d out of range", p->split_k);
   if (p->kv_padding < 1) return set_error(XFB200_E_INVALID, "decode: kv_padding must be positive");
   if (p->block_tables != nullptr && (p->page_size < 1 || p->block_table_stride < 1))
@@ -1096,7 +1445,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     return set_error(XFB200_E_UNSUPPORTED, "decode: mask_type %d", p->mask_type);
   const int R = p->mq * p->q_per_kv;
   // query rows of one kv head per CTA: 16 or 32 (16-bit cache), 8 or 16 (int4 cache)
-  const int tile_rows = int4 ? 8 : 16;
+  const int tile_rows = (int4 || fp8) ? 8 : 16;
   const int mt = R <= tile_rows ? 1 : 2;
   const int row_blocks = (R + tile_rows * mt - 1) / (tile_rows * mt);
   if (p->split_k > 1 && p->scratch == nullptr) return set_error(XFB200_E_INVALID, "decode: split_k > 1 needs scratch");
@@ -1115,6 +1464,9 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (p->kv_heads == 1) a.k_sg = a.v_sg = 0;  // the stride of an extent-1 axis is meaningless
   a.o_sm = p->o_stride_m, a.o_sg = p->o_stride_g, a.o_sh = p->o_stride_h;
   a.lse_sg = p->lse_stride_g, a.lse_sh = p->lse_stride_h;
+  a.k_ss = p->k_scale_shift, a.v_ss = p->v_scale_shift;
+  a.kss_m = p->ks_stride_m, a.kss_g = p->kv_heads == 1 ? 0 : p->ks_stride_g;
+  a.vss_m = p->vs_stride_m, a.vss_g = p->kv_heads == 1 ? 0 : p->vs_stride_g;
   a.causal = p->mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT;
   a.out_dtype = p->out_dtype;
   a.scale_log2 = p->scale * 1.4426950408889634f;
@@ -1133,8 +1485,8 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   const int head_blocks = p->kv_heads / hb;
 
   // how the producer may copy: whole stripes by TMA when alignment allows
-  const int elem = int4 ? 4 : 2;
-  const int head_elems = int4 ? (1 + p->head_dim / 8) : p->head_dim;
+  const int elem = (int4 || fp8) ? 4 : 2;
+  const int head_elems = int4 ? (1 + p->head_dim / 8) : fp8 ? p->head_dim / 4 : p->head_dim;
   const bool heads_contig = hb == 1 || (a.k_sg == head_elems && a.v_sg == head_elems);
   auto al16 = [&](int64_t elems) { return (elems * elem) % 16 == 0; };
   const bool base_al = (reinterpret_cast<uintptr_t>(p->k) % 16 == 0) && (reinterpret_cast<uintptr_t>(p->v) % 16 == 0);
@@ -1151,7 +1503,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     if (int4 && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
       const int span = p->block_tables ? p->page_size : p->kv_padding;
       // a run must fit the stage it is copied into (a power of two of tokens)
-      const int stage_tokens = p->head_dim == 128 ? DecStage<128, true>::tokens(hb) : DecStage<64, true>::tokens(hb);
+      const int stage_tokens = p->head_dim == 128 ? DecStage<128, kFmtInt4>::tokens(hb) : DecStage<64, kFmtInt4>::tokens(hb);
       int g = stage_tokens < 64 ? stage_tokens : 64;
       while (g > 1 && span % g) g >>= 1;
       a.copy_group = g;
@@ -1174,8 +1526,9 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     a.copy_mode = 2;
   }
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
+  if (fp8 && a.copy_mode != 0) return set_error(XFB200_E_UNSUPPORTED, "decode: the heads of an fp8 cache row must be contiguous");
   a.box_tok = 16;
-  if (!int4 && a.copy_mode == 0 && (p->kv_heads == 1 || (a.k_sg == p->head_dim && a.v_sg == p->head_dim))) {
+  if (!int4 && a.copy_mode == 0 && (p->kv_heads == 1 || (a.k_sg == head_elems && a.v_sg == head_elems))) {
     // The copy engine's throughput is set by the number of copies: one tiled
     // copy per run of tokens that is contiguous in the cache (a whole stage, or
     // what a page allows) instead of one bulk copy per token.
@@ -1184,15 +1537,18 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     if (p->block_tables != nullptr)
       while (box > 1 && p->page_size % box) box >>= 1;
     EncodeTiledFn enc = encode_tiled_fn();
-    if (box >= 8 && enc != nullptr) {
+    if (box >= (fp8 ? 16 : 8) && enc != nullptr) {
       // token rows: all of a padded cache (rows past the end read as zero); a paged
       // pool's size is not part of the call, and a copy never leaves its page
       const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : cuuint64_t(p->batch) * p->kv_padding;
-      const cuuint64_t dims[3] = {64, rows, cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
-      const cuuint32_t bx[3] = {64, cuuint32_t(box), cuuint32_t(hb * (p->head_dim / 64))};
+      // 16-bit cache: {64 elements, token rows, 128-byte column groups}; fp8: {128 bytes, token rows, kv heads}
+      const cuuint64_t dims[3] = {cuuint64_t(fp8 ? 128 : 64), rows, fp8 ? cuuint64_t(p->kv_heads) : cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
+      const cuuint32_t bx[3] = {cuuint32_t(fp8 ? 128 : 64), cuuint32_t(box), cuuint32_t(fp8 ? hb : hb * (p->head_dim / 64))};
       const cuuint32_t estr[3] = {1, 1, 1};
-      const CUtensorMapDataType dt = p->dtype == XFB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-      const cuuint64_t ks[2] = {cuuint64_t(p->k_stride_m) * 2, 128}, vs[2] = {cuuint64_t(p->v_stride_m) * 2, 128};
+      const CUtensorMapDataType dt = fp8                      ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                     : p->dtype == XFB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      const cuuint64_t ks[2] = {cuuint64_t(p->k_stride_m) * elem, 128}, vs[2] = {cuuint64_t(p->v_stride_m) * elem, 128};
       const CUresult rk = enc(&a.tm_k, dt, 3, const_cast<void*>(p->k), dims, ks, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       const CUresult rv = enc(&a.tm_v, dt, 3, const_cast<void*>(p->v), dims, vs, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1204,16 +1560,21 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     }
   }
 
+  if (fp8 && a.copy_mode != 3)
+    return set_error(XFB200_E_UNSUPPORTED, "decode: fp8 cache needs tiled copies (16-byte aligned rows, pages that are multiples of 16 tokens)");
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = p->dtype == XFB200_BF16;
-#define XFB_DISPATCH(DD)                                                                           \
-  if (int4) {                                                                                      \
-    return bf16 ? launch_decode_mt<DD, true, true>(a, mt, head_blocks, st)                         \
-                : launch_decode_mt<DD, true, false>(a, mt, head_blocks, st);                       \
-  } else {                                                                                         \
-    return bf16 ? launch_decode_mt<DD, false, true>(a, mt, head_blocks, st)                        \
-                : launch_decode_mt<DD, false, false>(a, mt, head_blocks, st);                      \
+#define XFB_DISPATCH(DD)                                                                                          \
+  if (int4) {                                                                                                     \
+    return bf16 ? launch_decode_mt<DD, kFmtInt4, true>(a, mt, head_blocks, st)                                    \
+                : launch_decode_mt<DD, kFmtInt4, false>(a, mt, head_blocks, st);                                  \
+  } else {                                                                                                        \
+    return bf16 ? launch_decode_mt<DD, kFmtPlain, true>(a, mt, head_blocks, st)                                   \
+                : launch_decode_mt<DD, kFmtPlain, false>(a, mt, head_blocks, st);                                 \
   }
+  if (fp8)
+    return bf16 ? launch_decode_mt<128, kFmtFp8, true>(a, mt, head_blocks, st) : launch_decode_mt<128, kFmtFp8, false>(a, mt, head_blocks, st);
   if (p->head_dim == 128) {
     XFB_DISPATCH(128)
   } else {

@@ -111,6 +111,19 @@ def memory_efficient_attention_forward_requires_grad(
     return out, lse
 
 
+def _memory_efficient_attention_forward(inp: Inputs, op=None) -> torch.Tensor:
+    """Forward on a prepared :class:`Inputs` (or :class:`InputsFp8`) object
+    (used as ``fmha._memory_efficient_attention_forward`` by the reference's tests)."""
+    return _run_forward(inp, op, needs_lse=False)[0]
+
+
+def _memory_efficient_attention_forward_requires_grad(inp: Inputs, op=None) -> Tuple[torch.Tensor, Context]:
+    """Same, returning ``(out, Context)`` with the log-sum-exp
+    (tests/test_mem_eff_attention.py:2843-2848)."""
+    out, lse = _run_forward(inp, op, needs_lse=True)
+    return out, Context(out=out, lse=lse)
+
+
 def memory_efficient_attention_partial(
     query: torch.Tensor,
     key: torch.Tensor,

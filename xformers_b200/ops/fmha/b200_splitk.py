@@ -5,7 +5,8 @@ CUDA replacement of the reference's Triton flash-decoding operator
 xformers/ops/fmha/triton_splitk.py:18-27): few queries per sequence against a
 long KV cache, padded or paged, in bf16/f16 or in the int4 row-wise format
 (K/V of dtype int32 whose last dim is ``D/8 + NUM_GROUPS``,
-tests/test_mem_eff_attention.py:1700-1707).  The split count is chosen from
+tests/test_mem_eff_attention.py:1700-1707) or in the row-wise fp8 format
+(``InputsFp8``, tests/utils.py:134-340).  The split count is chosen from
 static shape quantities only, never from device-side lengths, so a call can be
 captured in a CUDA graph and replayed after the lengths changed.
 """
@@ -24,7 +25,7 @@ from .attn_bias import (
     PagedBlockDiagonalCausalWithOffsetPaddedKeysMask,
     PagedBlockDiagonalPaddedKeysMask,
 )
-from .common import AttentionFwOpBase, Context, Inputs, check_lastdim_alignment_stride1
+from .common import AttentionFwOpBase, Context, Inputs, InputsFp8, check_lastdim_alignment_stride1
 
 _DTYPE_CODE = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 _SM_COUNT = 148
@@ -88,7 +89,18 @@ class FwOp(AttentionFwOpBase):
         K = d.query.shape[-1]
         if K not in (64, 128):
             reasons.append(f"head dim {K} not in (64, 128)")
-        if quantized:
+        fp8 = isinstance(d, InputsFp8)
+        if fp8:
+            if not quantized or d.value.dtype != torch.int32:
+                reasons.append("fp8 K/V must be passed as int32 words of four e4m3 values")
+            elif d.key.shape[-1] != K // 4 or d.value.shape[-1] != K // 4:
+                reasons.append(f"fp8 K/V rows must have {K // 4} int32 words, got {d.key.shape[-1]}")
+            if K != 128:
+                reasons.append("fp8 caches are supported for head dim 128 only")
+            for name, t in (("k_fp8_scale_shift", d.k_fp8_scale_shift), ("v_fp8_scale_shift", d.v_fp8_scale_shift)):
+                if t is None or t.dtype != torch.int32 or tuple(t.shape) != tuple(d.key.shape[:-1]):
+                    reasons.append(f"{name} must be an int32 tensor of shape key.shape[:-1]")
+        elif quantized:
             if d.value.dtype != torch.int32:
                 reasons.append("key is int32 (quantised) but value is not")
             if cls.NUM_GROUPS != 1:
@@ -175,13 +187,23 @@ class FwOp(AttentionFwOpBase):
             p.lse = lse.data_ptr() if lse is not None else None
             p.dtype = _DTYPE_CODE[q.dtype]
             p.out_dtype = _DTYPE_CODE[out_dtype]
-            p.kv_format = _lib.KV_INT4_ROWWISE if quantized else _lib.KV_PLAIN
-            p.num_quant_groups = cls.NUM_GROUPS if quantized else 0
+            fp8 = isinstance(inp, InputsFp8)
+            p.kv_format = _lib.KV_FP8_ROWWISE if fp8 else _lib.KV_INT4_ROWWISE if quantized else _lib.KV_PLAIN
+            p.num_quant_groups = cls.NUM_GROUPS if quantized and not fp8 else 0
+            if fp8:
+                kss, vss = inp.k_fp8_scale_shift, inp.v_fp8_scale_shift
+                # same axes as key without the last one: [B, M, G, H] (or [B, M, H])
+                if kss.ndim == 3:
+                    kss, vss = kss.unsqueeze(2), vss.unsqueeze(2)
+                p.k_scale_shift, p.v_scale_shift = kss.data_ptr(), vss.data_ptr()
+                p.ks_stride_m, p.vs_stride_m = kss.stride(1), vss.stride(1)
             p.head_dim = D
             if broadcast:
                 p.kv_heads, p.q_per_kv = G, H
                 p.q_stride_g, p.q_stride_h = q.stride(2), q.stride(3)
                 p.k_stride_g, p.v_stride_g = k.stride(2), v.stride(2)
+                if fp8:
+                    p.ks_stride_g, p.vs_stride_g = kss.stride(2), vss.stride(2)
                 p.o_stride_g, p.o_stride_h = out.stride(2), out.stride(3)
                 lse_g, lse_h = (lse.stride(0), lse.stride(1)) if lse is not None else (0, 0)
             else:
@@ -190,6 +212,8 @@ class FwOp(AttentionFwOpBase):
                 hs = lambda t: t.stride(3) if H > 1 else t.stride(2)
                 p.q_stride_g, p.q_stride_h = hs(q), 0
                 p.k_stride_g, p.v_stride_g = hs(k), hs(v)
+                if fp8:
+                    p.ks_stride_g, p.vs_stride_g = hs(kss), hs(vss)
                 p.o_stride_g, p.o_stride_h = hs(out), 0
                 lse_g, lse_h = (lse.stride(1), 0) if lse is not None else (0, 0)
             p.lse_stride_g, p.lse_stride_h = lse_g, lse_h
@@ -212,7 +236,7 @@ class FwOp(AttentionFwOpBase):
                 p.batch, p.mq = B, Mq
                 p.seqlen_k = None
                 p.kv_padding = k.shape[1]
-            row_bytes = (D // 8 + cls.NUM_GROUPS) * 4 if quantized else D * 2
+            row_bytes = D if fp8 else (D // 8 + cls.NUM_GROUPS) * 4 if quantized else D * 2
             p.split_k = cls.get_split_k(p.batch, p.kv_padding, p.kv_heads, row_bytes)
             lib = _lib.load()
             nbytes = lib.xfb200_decode_scratch_bytes(p.batch, p.mq, p.kv_heads, p.q_per_kv, D, p.split_k)

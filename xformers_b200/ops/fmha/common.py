@@ -146,6 +146,19 @@ class Inputs:
 
 
 @dataclass
+class InputsFp8(Inputs):
+    """Inputs of the split-K operator with a row-wise fp8 KV cache
+    (xformers/ops/fmha/triton_splitk.py:28; built in tests/utils.py:215-222):
+    ``key`` / ``value`` are int32 words of four e4m3 values, element
+    ``x = fp8 * scale + shift`` with one ``(fp16 scale | fp16 shift << 16)``
+    int32 per token and head in ``k_fp8_scale_shift`` / ``v_fp8_scale_shift``
+    (shape of ``key`` without its last axis)."""
+
+    k_fp8_scale_shift: Optional[torch.Tensor] = None
+    v_fp8_scale_shift: Optional[torch.Tensor] = None
+
+
+@dataclass
 class Context:
     """What a forward call leaves behind for its caller: the log-sum-exp
     (tests/test_mem_eff_attention.py:2860-2861) and the output."""

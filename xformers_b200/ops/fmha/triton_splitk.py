@@ -14,4 +14,5 @@ from .b200_splitk import (  # noqa: F401
     FwOp_S64,
     FwOp_S128,
 )
+from .common import InputsFp8  # noqa: F401
 from .merge import merge_attentions, merge_attentions_varargs  # noqa: F401
