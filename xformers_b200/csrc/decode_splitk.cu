@@ -1036,7 +1036,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kDecStages; ++i) {
-      mbar_init(&full_bar[i], 1);
+      mbar_init(&full_bar[i], kFp8 ? 33 : 1);  // fp8: + one arrival per lane of the copy warp (scale/shift copies)
       mbar_init(&empty_bar[i], kDecConsumerWarps);
     }
     mbar_init(&q_done_bar, kDecConsumerWarps);
@@ -1051,24 +1051,19 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
     constexpr int kElem = kQuant ? 4 : 2;  // bytes per element of the k/v tensors (int32 words when quantised)
     constexpr int kHeadBytes = kInt4 ? W * 4 : kFp8 ? D : D * 2;
     const int head0 = hblk * hb;
-    // fp8: scale/shift words of the next tile, 128 per tensor and stage = 4 per lane
-    uint32_t ss_k[4] = {0, 0, 0, 0}, ss_v[4] = {0, 0, 0, 0};
-    auto load_ss = [&](int tile) {
-      const int t0 = chunk_lo + tile * TOK;
-      const int nvalid = min(TOK, chunk_hi - t0);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = lane + 32 * j;
-        if (i < nvalid * hb) {
-          const int hh = i / nvalid, t = t0 + i % nvalid;
-          const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
-                                             : int64_t(b) * a.kv_padding + t;
-          ss_k[j] = uint32_t(__ldg(a.k_ss + row * a.kss_m + (head0 + hh) * a.kss_g));
-          ss_v[j] = uint32_t(__ldg(a.v_ss + row * a.vss_m + (head0 + hh) * a.vss_g));
-        }
+    // physical row of token t; the page-table entry is kept while t stays on its page,
+    // so that a lane waits for that load once per page instead of once per stage
+    int cached_page = -1;
+    int64_t cached_base = 0;
+    auto row_of = [&](int t) -> int64_t {
+      if (a.block_tables == nullptr) return int64_t(b) * a.kv_padding + t;
+      const int pg = t / a.page_size;
+      if (pg != cached_page) {
+        cached_page = pg;
+        cached_base = int64_t(a.block_tables[int64_t(b) * a.bt_stride + pg]) * a.page_size;
       }
+      return cached_base + (t - pg * a.page_size);
     };
-    if constexpr (kFp8) load_ss(0);
     for (int tile = 0; tile < n_tiles; ++tile) {
       const int st = tile % kDecStages;
       if (tile >= kDecStages) {
@@ -1091,11 +1086,9 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
         if (lane == 0) {
           const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
           const uint32_t box_bytes = uint32_t(a.box_tok) * hb * kHeadBytes;
-          if constexpr (!kFp8) mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
+          mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
           for (int bx = 0; bx < nbox; ++bx) {
-            const int t = t0 + bx * a.box_tok;
-            const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
-                                               : int64_t(b) * a.kv_padding + t;
+            const int64_t row = row_of(t0 + bx * a.box_tok);
             // third coordinate: 128-byte column group (16-bit cache) or kv head (fp8: a head is one 128-byte row)
             const int c2 = kFp8 ? head0 : head0 * (D / 64);
             tma_load_3d(ks + bx * box_bytes, &a.tm_k, &full_bar[st], 0, int(row), c2);
@@ -1103,28 +1096,21 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
           }
         }
         if constexpr (kFp8) {
-          // The scale/shift words travel by ordinary loads: [head][token] behind the K
-          // and V parts of the stage.  They were requested one tile ahead (ss_k / ss_v
-          // registers), so their latency overlaps the wait for the stage.  The arrival
-          // that opens the transaction count comes last, after these stores, so that
-          // the barrier cannot complete before they are visible.
+          // The scale/shift words (one per token and head, 128 per tensor and stage)
+          // go straight from global to shared memory with 4-byte asynchronous copies,
+          // [head][token] behind the K and V parts of the stage.  Every lane then lets
+          // the full barrier count the completion of its copies (the barrier expects
+          // 32 such arrivals besides the one that carries the TMA byte count), so the
+          // copy warp never waits for this data itself.
           uint32_t* ssk = reinterpret_cast<uint32_t*>(ks + 2 * kv_bytes);
           uint32_t* ssv = ssk + hb * TOK;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int i = lane + 32 * j;
-            if (i < nvalid * hb) {
-              const int hh = i / nvalid, tok = i % nvalid;
-              ssk[hh * TOK + tok] = ss_k[j];
-              ssv[hh * TOK + tok] = ss_v[j];
-            }
+          for (int i = lane; i < nvalid * hb; i += 32) {
+            const int tok = i / hb, hh = i % hb;  // heads fastest: neighbouring lanes read neighbouring words
+            const int64_t row = row_of(t0 + tok);
+            cp_async_4(ssk + hh * TOK + tok, a.k_ss + row * a.kss_m + (head0 + hh) * a.kss_g);
+            cp_async_4(ssv + hh * TOK + tok, a.v_ss + row * a.vss_m + (head0 + hh) * a.vss_g);
           }
-          __syncwarp();
-          if (lane == 0) {
-            const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
-            mbar_expect_tx(&full_bar[st], uint32_t(nbox) * uint32_t(a.box_tok) * hb * kHeadBytes * 2u);
-          }
-          if (tile + 1 < n_tiles) load_ss(tile + 1);
+          cp_async_mbar_arrive_noinc(&full_bar[st]);
         }
         __syncwarp();
         continue;

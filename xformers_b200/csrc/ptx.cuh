@@ -233,6 +233,16 @@ __device__ __forceinline__ void cp_async_16(void* dst_smem, const void* src, boo
   uint32_t sz = valid ? 16u : 0u;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(sz) : "memory");
 }
+// 4-byte asynchronous copy global -> shared (both addresses 4-byte aligned)
+__device__ __forceinline__ void cp_async_4(void* dst_smem, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+// The barrier receives one arrival from this thread once all of its earlier
+// cp.async copies have landed; .noinc: the arrival is part of the count the
+// barrier was initialised with.
+__device__ __forceinline__ void cp_async_mbar_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
