@@ -56,7 +56,8 @@ CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from the ncu captures summarised
 # under profiles/: bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
-NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6}
+NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
+               "decode_fp8": (613.01e6 + 14.01e6) / 505.51e6}
 
 
 def causal_flops(B, M, H, D):
@@ -476,7 +477,8 @@ def main():
         gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
         out_line["decode_fp8"] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes,
                                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                               "frac": gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"]},
+                                               "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode_fp8"] * nbytes,
+                                               "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 16-sequence case)", "of": peaks["source"]},
                                   "workload": "as decode_bf16 with a row-wise fp8 cache (128 B + one scale/shift word per token and head)"}
         del dq, dk, dv, dbias, kss, vss, inp
         torch.cuda.empty_cache()

@@ -120,7 +120,13 @@ struct DecStage {
   // sub-tiles of 16 tokens each warp takes from one stage: the int4 cache is 4x
   // denser, so its stages hold more tokens to keep the per-stage overhead
   // (barrier round trip, page-table look-ups of the producer) off the critical path
-  static constexpr int kSubTiles = kFmt == kFmtInt4 ? 2 : 1;
+#ifndef XFB_FP8_SUBTILES
+#define XFB_FP8_SUBTILES 1
+#endif
+#ifndef XFB_FP8_CTAS
+#define XFB_FP8_CTAS 2
+#endif
+  static constexpr int kSubTiles = kFmt == kFmtInt4 ? 2 : kFmt == kFmtFp8 ? XFB_FP8_SUBTILES : 1;
   __host__ __device__ static int tokens(int hb) { return 16 * kSubTiles * (kDecConsumerWarps / hb); }
   __host__ __device__ static int kv_bytes(int hb) {  // K or V part of a stage, rounded to 128 B
     return (row_bytes(hb) * tokens(hb) + 127) & ~127;
@@ -137,8 +143,8 @@ constexpr int kDecMaxStages = 12;
 // so does the fp8 kernel, which shares its structure.
 template <int kFmt>
 struct DecOccupancy {
-  static constexpr int kCtasPerSm = kFmt != kFmtPlain ? 2 : 1;
-  static constexpr int kRingBudget = kFmt != kFmtPlain ? 106 * 1024 : 212 * 1024;
+  static constexpr int kCtasPerSm = kFmt == kFmtInt4 ? 2 : kFmt == kFmtFp8 ? XFB_FP8_CTAS : 1;
+  static constexpr int kRingBudget = kCtasPerSm == 2 ? 106 * 1024 : 212 * 1024;
 };
 
 // What a consumer warp needs to know about its CTA.
