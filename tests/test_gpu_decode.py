@@ -12,7 +12,7 @@ from xformers_b200.ops.fmha import attn_bias as ab
 S = fmha.b200_splitk
 
 
-def _decoder_case(n_heads, kv_heads, padding, bsz, dtype, num_queries=1, d=128, seed=1, quant=False, rand_scale=False):
+def _decoder_case(n_heads, kv_heads, padding, bsz, dtype, num_queries=1, d=128, seed=1, quant=False, rand_scale=False, groups=1):
     """Tensors of tests/test_mem_eff_attention.py:1657-1747."""
     g = torch.Generator().manual_seed(seed)
     if kv_heads is not None and kv_heads > 1:
@@ -24,24 +24,24 @@ def _decoder_case(n_heads, kv_heads, padding, bsz, dtype, num_queries=1, d=128, 
     q = torch.randn(q_shape, generator=g).to(dtype).cuda()
     k_seqlen = torch.randint(num_queries, padding + 1, (bsz,), generator=g).tolist()
     if quant:
-        w_shape = k_shape[:-1] + (d // 8 + 1,)
+        w_shape = k_shape[:-1] + (d // 8 + groups,)
         if rand_scale:
             kf = torch.randn(k_shape[:-2] + (1, d) if kv_heads is not None else k_shape, generator=g)
             vf = torch.randn(kf.shape, generator=g)
-            k, v = oracle.quantize_kv_int4(kf), oracle.quantize_kv_int4(vf)
+            k, v = oracle.quantize_kv_int4(kf, groups), oracle.quantize_kv_int4(vf, groups)
         else:
             # the reference's pattern: random words, scale = shift = 1.0
             k = torch.randint(-(2**31), 2**31 - 1, w_shape, generator=g, dtype=torch.int64).to(torch.int32)
             v = torch.randint(-(2**31), 2**31 - 1, w_shape, generator=g, dtype=torch.int64).to(torch.int32)
-            k[..., :1].view(torch.float16).fill_(1.0)
-            v[..., :1].view(torch.float16).fill_(1.0)
+            k[..., :groups].view(torch.float16).fill_(1.0)
+            v[..., :groups].view(torch.float16).fill_(1.0)
             if kv_heads is not None:
                 k, v = k[..., :1, :], v[..., :1, :]
         k, v = k.cuda(), v.cuda()
         if kv_heads is not None:
             k, v = k.expand(w_shape), v.expand(w_shape)
-        k_ref = oracle.dequantize_kv_int4(k.cpu().contiguous())
-        v_ref = oracle.dequantize_kv_int4(v.cpu().contiguous())
+        k_ref = oracle.dequantize_kv_int4(k.cpu().contiguous(), groups)
+        v_ref = oracle.dequantize_kv_int4(v.cpu().contiguous(), groups)
     else:
         k = torch.randn(k_shape, generator=g).to(dtype).cuda()
         v = torch.randn(k_shape, generator=g).to(dtype).cuda()
@@ -91,6 +91,27 @@ def test_decoder_int4(kv_heads, padding, bsz, dtype, split_k, rand_scale):
     assert_o_lse(out, None, ro, rl, dtype, "int4", o_scale=4.0 if not rand_scale else 1.0)
     lerr = (lse.cpu() - rl).abs().max().item()
     assert lerr <= (2e-2 if not rand_scale else 2e-3), f"int4 LSE error {lerr}"
+
+
+@gpu
+@pytest.mark.parametrize("rand_scale", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("padding,bsz", [(32, 8), (4096, 1)])
+@pytest.mark.parametrize("kv_heads", [None, 1, 2])
+@pytest.mark.parametrize("groups,d", [(2, 128), (4, 128), (8, 128), (2, 64), (4, 64)])
+def test_decoder_int4_groups(groups, d, kv_heads, padding, bsz, dtype, rand_scale):
+    """Several quantisation groups per row (``NUM_GROUPS``,
+    tests/test_mem_eff_attention.py:1700-1707,1759)."""
+    require_cuda()
+    op = type(f"S2_{groups}", (S.FwOp_S2,), {"NUM_GROUPS": groups, "NAME": f"S2_{groups}"})
+    q, k, v, bias, k_ref, v_ref = _decoder_case(16, kv_heads, padding, bsz, dtype, d=d, quant=True, rand_scale=rand_scale, groups=groups)
+    reasons = op.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    assert not reasons, reasons
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k_ref, v_ref, bias.to("cpu"))
+    assert_o_lse(out, None, ro, rl, dtype, f"int4 x{groups}", o_scale=4.0 if not rand_scale else 1.0)
+    lerr = (lse.cpu() - rl).abs().max().item()
+    assert lerr <= (2e-2 if not rand_scale else 2e-3), f"int4 x{groups} LSE error {lerr}"
 
 
 @gpu

@@ -108,14 +108,14 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
 // cache formats (the template parameter kFmt of what follows)
 constexpr int kFmtPlain = 0, kFmtInt4 = 1, kFmtFp8 = 2;
 
-template <int D, int kFmt>
+template <int D, int kFmt, int NG = 1>
 struct DecStage {
   // plain: one row per token = hb heads * D elements (+16 B pad against bank conflicts; unpadded and
   //        swizzled when the stage is filled by a tiled copy)
-  // int4 : one row per token = hb heads * (1 + D/8) words, unpadded
+  // int4 : one row per token = hb heads * (NG + D/8) words (NG quantisation groups), unpadded
   // fp8  : [head][token][D bytes] boxes (tiled copy, 128-byte swizzle), then the scale/shift words
   __host__ __device__ static int row_bytes(int hb) {
-    return kFmt == kFmtInt4 ? hb * (1 + D / 8) * 4 : kFmt == kFmtFp8 ? hb * D : hb * D * 2 + 16;
+    return kFmt == kFmtInt4 ? hb * (NG + D / 8) * 4 : kFmt == kFmtFp8 ? hb * D : hb * D * 2 + 16;
   }
   // sub-tiles of 16 tokens each warp takes from one stage: the int4 cache is 4x
   // denser, so its stages hold more tokens to keep the per-stage overhead
@@ -697,6 +697,319 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
 }
 
 // ---------------------------------------------------------------------------
+// int4 row-wise cache with NG > 1 quantisation groups per row (the first NG
+// words of a row are the (scale | shift << 16) words of its groups of D / NG
+// elements).  Same products as consume_int4, but a scale now belongs to a
+// (token, group) pair and a k-step or an output tile may mix groups, so the
+// scales are folded into the unpacked elements themselves (one more half2
+// multiply per nibble pair, on the FMA pipe) instead of into the scores and the
+// probabilities; the shifts become per-group terms: shift_g x (sum of q over
+// group g) for K, sum_t p_t x shift_{t,g} added to the columns of group g for V.
+// ---------------------------------------------------------------------------
+template <int D, int NTQ, bool kBf16, int NG>
+__device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const DecWarp& w) {
+  using T = typename Half2Type<kBf16>::T;
+  constexpr int W = NG + D / 8;      // words per row
+  constexpr int KS = D / 16;         // k-steps of K Q^T
+  constexpr int MTV = D / 16;        // m-tiles of V^T P^T
+  constexpr int WPT = D / 64;        // V words per thread and token
+  constexpr int GW = (D / 8) / NG;   // nibble words per group
+  static_assert(GW >= WPT && GW >= 1 && (D / 8) % NG == 0, "groups of at least 16 elements");
+  constexpr int kQRowBytes = D * 2;
+  constexpr int kCmbRow = D + 2;
+  constexpr int kSps = DecStage<D, kFmtInt4, NG>::kSubTiles;
+  constexpr float kLazy = 4.f;
+  const int lane = w.lane, r = lane >> 2, c = lane & 3;
+  const int R = a.rows, hw = w.hw, row_bytes = w.row_bytes;
+
+  // nibble pairs (e, e+4), e = 0..3, of a packed word as f16 pairs n * mul (mul: one factor per half)
+  auto unpack4s = [](uint32_t x, __half2 mul, uint32_t (&out)[4]) {
+    constexpr uint32_t kMagic = 0x64006400u;
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 k64 = __half2half2(__ushort_as_half(0x5400));
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));
+    const uint32_t hi = x >> 8;
+    uint32_t v0 = (x & 0x000F000Fu) | kMagic, v1 = (x & 0x00F000F0u) | kMagic;
+    uint32_t v2 = (hi & 0x000F000Fu) | kMagic, v3 = (hi & 0x00F000F0u) | kMagic;
+    __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v0), k1024), mul);
+    __half2 h1 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&v1), k16th, __hneg2(k64)), mul);
+    __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&v2), k1024), mul);
+    __half2 h3 = __hmul2(__hfma2(*reinterpret_cast<__half2*>(&v3), k16th, __hneg2(k64)), mul);
+    out[0] = *reinterpret_cast<uint32_t*>(&h0);
+    out[1] = *reinterpret_cast<uint32_t*>(&h1);
+    out[2] = *reinterpret_cast<uint32_t*>(&h2);
+    out[3] = *reinterpret_cast<uint32_t*>(&h3);
+  };
+  auto scale_of = [](uint32_t word) { return __ushort_as_half(static_cast<unsigned short>(word & 0xFFFFu)); };
+
+  uint32_t qf[NTQ][KS][2];
+  float qsum[NTQ][NG][2];  // per group: sum of the scaled q, rows 2c, 2c+1 of each n-tile
+  float qfac[NTQ][2];
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+    const T* qrow = reinterpret_cast<const T*>(w.qs + (nt * 8 + r) * kQRowBytes);
+    float amax = 0.f;
+    for (int d = c; d < D; d += 4) amax = fmaxf(amax, fabsf(float(qrow[d])));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    int kexp = 0;
+    if (amax >= 32768.f && amax < INFINITY) kexp = int(__float_as_uint(amax) >> 23) - 127 - 14;
+    const float qmul = __uint_as_float(uint32_t(127 - kexp) << 23);
+    const float fac = __uint_as_float(uint32_t(127 + kexp) << 23) * a.scale_log2;
+    qfac[nt][0] = __shfl_sync(0xffffffffu, fac, 8 * c);
+    qfac[nt][1] = __shfl_sync(0xffffffffu, fac, 8 * c + 4);
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      float sr = 0.f;
+      for (int d = g * (D / NG) + c; d < (g + 1) * (D / NG); d += 4) sr += __half2float(__float2half_rn(float(qrow[d]) * qmul));
+      sr += __shfl_xor_sync(0xffffffffu, sr, 1);
+      sr += __shfl_xor_sync(0xffffffffu, sr, 2);
+      qsum[nt][g][0] = __shfl_sync(0xffffffffu, sr, 8 * c);
+      qsum[nt][g][1] = __shfl_sync(0xffffffffu, sr, 8 * c + 4);
+    }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const T* q0 = qrow + (4 * (ks >> 1) + c) * 8;
+      const int e0 = (ks & 1) * 2;
+      auto pk = [qmul](const T* p, int i0, int i1) {
+        const __half2 h = __floats2half2_rn(float(p[i0]) * qmul, float(p[i1]) * qmul);
+        return *reinterpret_cast<const uint32_t*>(&h);
+      };
+      qf[nt][ks][0] = pk(q0, e0, e0 + 4);
+      qf[nt][ks][1] = pk(q0, e0 + 1, e0 + 5);
+    }
+  }
+  __syncwarp();
+  if (lane == 0) mbar_arrive(w.q_done_bar);
+
+  int lim[NTQ][2];
+  int lim_min = w.chunk_hi;
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int row = w.row0 + nt * 8 + 2 * c + e;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
+      lim_min = min(lim_min, l);
+    }
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
+  lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
+
+  float acc[MTV][NTQ][4];
+  float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][NG][2];
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.f;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) corr[nt][g][0] = corr[nt][g][1] = 0.f;
+  }
+  const int gv = (WPT * r) / GW;  // group of the V words this thread unpacks (both words of a token share it)
+
+  const int rw = row_bytes / 4;
+  for (int tile = 0; tile < w.n_tiles; ++tile) {
+    const int st = tile % w.stages;
+    if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
+      if (lane == 0) atomicExch(a.status, 2);
+      break;
+    }
+    const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * w.stage_bytes) + hw * W;
+    const uint32_t* vst = kst + w.kv_bytes / 4;
+#pragma unroll 1
+    for (int sp = 0; sp < kSps; ++sp) {
+      const int usub = w.sub + w.wph * sp;
+      const int t_sub = w.chunk_lo + tile * w.tok_per_stage + usub * 16;
+      if (t_sub >= w.chunk_hi) continue;
+      const uint32_t* k0 = kst + (usub * 16 + r) * rw;  // token r; token r + 8 is 8 rows on
+      const uint32_t* v0 = vst + (usub * 16 + r) * rw;
+      const bool all_visible = t_sub + 16 <= lim_min;
+      const int t0 = t_sub + r, t1 = t_sub + r + 8;
+      const bool in0 = t0 < w.chunk_hi, in1 = t1 < w.chunk_hi;  // tokens past the end were not copied
+
+      // ------------------------------------------- S^T = K Q^T with K already scaled
+      float s[NTQ][4], s2[NTQ][4];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < KS / 2; ++i) {
+        const int g = (4 * i + c) / GW;  // group of word 4i + c
+        const __half2 m0 = __half2half2(scale_of(k0[g])), m1 = __half2half2(scale_of(k0[8 * rw + g]));
+        uint32_t u0[4], u1[4];
+        unpack4s(k0[NG + 4 * i + c], m0, u0);
+        unpack4s(k0[8 * rw + NG + 4 * i + c], m1, u1);
+        const uint32_t ka[4] = {u0[0], u1[0], u0[1], u1[1]};
+        const uint32_t kb[4] = {u0[2], u1[2], u0[3], u1[3]};
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt) {
+          mma_16816<false>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
+          mma_16816<false>(s2[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+        }
+      }
+      // shifts of K: one term per group
+      float sc0[NTQ][2], sc1[NTQ][2];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc0[nt][e] = s[nt][e] + s2[nt][e];
+          sc1[nt][e] = s[nt][2 + e] + s2[nt][2 + e];
+        }
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const float ksh0 = half_bits_to_float(k0[g] >> 16), ksh1 = half_bits_to_float(k0[8 * rw + g] >> 16);
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            sc0[nt][e] = fmaf(ksh0, qsum[nt][g][e], sc0[nt][e]);
+            sc1[nt][e] = fmaf(ksh1, qsum[nt][g][e], sc1[nt][e]);
+          }
+      }
+      bool need = false;
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc0[nt][e] *= qfac[nt][e];
+          sc1[nt][e] *= qfac[nt][e];
+          if (!all_visible) {
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
+          }
+          need |= fmaxf(sc0[nt][e], sc1[nt][e]) > m_run[nt][e] + kLazy;
+        }
+      if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt) {
+          float alpha[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float mx = fmaxf(sc0[nt][e], sc1[nt][e]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[nt][e], mx);
+            alpha[e] = fast_exp2(m_run[nt][e] - (m_new == -INFINITY ? 0.f : m_new));
+            m_run[nt][e] = m_new;
+            l_run[nt][e] *= alpha[e];
+#pragma unroll
+            for (int g = 0; g < NG; ++g) corr[nt][g][e] *= alpha[e];
+          }
+#pragma unroll
+          for (int mt = 0; mt < MTV; ++mt) {
+            acc[mt][nt][0] *= alpha[0];
+            acc[mt][nt][1] *= alpha[1];
+            acc[mt][nt][2] *= alpha[0];
+            acc[mt][nt][3] *= alpha[1];
+          }
+        }
+      }
+      uint32_t pb[NTQ][2];
+      float p0[NTQ][2], p1[NTQ][2];
+#pragma unroll
+      for (int nt = 0; nt < NTQ; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float m_use = m_run[nt][e] == -INFINITY ? 0.f : m_run[nt][e];
+          p0[nt][e] = fast_exp2(sc0[nt][e] - m_use);
+          p1[nt][e] = fast_exp2(sc1[nt][e] - m_use);
+          l_run[nt][e] += p0[nt][e] + p1[nt][e];
+        }
+        pb[nt][0] = movmatrix_trans(pack2<false>(p0[nt][0], p0[nt][1]));  // tokens 2c, 2c+1   of row r
+        pb[nt][1] = movmatrix_trans(pack2<false>(p1[nt][0], p1[nt][1]));  // tokens 2c+8, 2c+9 of row r
+      }
+      // shifts of V: sum_t p_t shift_{t,g}, one accumulator per group
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        const float vsh0 = in0 ? half_bits_to_float(v0[g] >> 16) : 0.f;
+        const float vsh1 = in1 ? half_bits_to_float(v0[8 * rw + g] >> 16) : 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) corr[nt][g][e] = fmaf(p0[nt][e], vsh0, fmaf(p1[nt][e], vsh1, corr[nt][g][e]));
+      }
+
+      // ------------------------------------------------- O^T += V^T P^T with V already scaled
+      {
+        const uint32_t* va = vst + (usub * 16 + 2 * c) * rw;  // token 2c; +rw: 2c+1; +8rw: 2c+8; +9rw: 2c+9
+        const int tv = t_sub + 2 * c;
+        // scales of the four tokens for this thread's group (0 past the end: garbage words there)
+        const __half hz = __ushort_as_half(0);
+        const __half2 ma = __halves2half2(tv < w.chunk_hi ? scale_of(va[gv]) : hz, tv + 1 < w.chunk_hi ? scale_of(va[rw + gv]) : hz);
+        const __half2 mb = __halves2half2(tv + 8 < w.chunk_hi ? scale_of(va[8 * rw + gv]) : hz, tv + 9 < w.chunk_hi ? scale_of(va[9 * rw + gv]) : hz);
+#pragma unroll
+        for (int wi = 0; wi < WPT; ++wi) {
+          const int wd = NG + WPT * r + wi;
+          const uint32_t x0 = va[wd], x1 = va[rw + wd], x2 = va[8 * rw + wd], x3 = va[9 * rw + wd];
+          uint32_t ylo[4], yhi[4], zlo[4], zhi[4];
+          unpack4s(__byte_perm(x0, x1, 0x5410), ma, ylo);
+          unpack4s(__byte_perm(x0, x1, 0x7632), ma, yhi);
+          unpack4s(__byte_perm(x2, x3, 0x5410), mb, zlo);
+          unpack4s(__byte_perm(x2, x3, 0x7632), mb, zhi);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t vf[4] = {ylo[e], yhi[e], zlo[e], zhi[e]};
+#pragma unroll
+            for (int nt = 0; nt < NTQ; ++nt) mma_16816<false>(acc[wi * 4 + e][nt], vf, pb[nt][0], pb[nt][1]);
+          }
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&w.empty_bar[st]);
+  }
+
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float l = l_run[nt][e];
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+      l_run[nt][e] = l;
+#pragma unroll
+      for (int g = 0; g < NG; ++g) {
+        float cs = corr[nt][g][e];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) cs += __shfl_xor_sync(0xffffffffu, cs, o);
+        corr[nt][g][e] = cs;
+      }
+    }
+
+  asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
+#pragma unroll
+  for (int nt = 0; nt < NTQ; ++nt) {
+    // the columns this thread holds all belong to group gv
+    float cv[2] = {0.f, 0.f};
+#pragma unroll
+    for (int g = 0; g < NG; ++g)
+      if (g == gv) cv[0] = corr[nt][g][0], cv[1] = corr[nt][g][1];
+#pragma unroll
+    for (int mt = 0; mt < MTV; ++mt)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int d = 8 * (WPT * r + (mt >> 2)) + (mt & 3) + (q >> 1) * 4;
+        const int rr = nt * 8 + 2 * c + (q & 1);
+        w.mine[rr * kCmbRow + d] = acc[mt][nt][q] + cv[q & 1];
+      }
+    if (r == 0) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D] = m_run[nt][e];
+        w.mine[(nt * 8 + 2 * c + e) * kCmbRow + D + 1] = l_run[nt][e];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // fp8 row-wise cache (four e4m3 values per int32 word, one fp16 scale / shift
 // pair per token and kv head in a tensor of its own; tests/utils.py:311-340 of
 // the reference).  Same structure as the int4 consumer: transposed products in
@@ -976,12 +1289,12 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
   }
 }
 
-template <int D, int MT, int kFmt, bool kBf16>
+template <int D, int MT, int kFmt, bool kBf16, int NG = 1>
 __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
-  using Stage = DecStage<D, kFmt>;
+  using Stage = DecStage<D, kFmt, NG>;
   constexpr bool kInt4 = kFmt == kFmtInt4, kFp8 = kFmt == kFmtFp8, kQuant = kFmt != kFmtPlain;
   using T = typename Half2Type<kBf16>::T;
-  constexpr int W = 1 + D / 8;  // int4 words per row (one quantisation group)
+  constexpr int W = NG + D / 8;  // int4 words per row (NG scale/shift words, then the nibbles)
   // query rows of one kv head per CTA: MT m-tiles of 16 (16-bit cache) or MT
   // n-tiles of 8 (int4 and fp8 caches, transposed products)
   constexpr int ROWS = kQuant ? 8 * MT : 16 * MT;
@@ -1002,7 +1315,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
   const int lane = threadIdx.x & 31;
   const int hb = a.hb;
   const int wph = kDecConsumerWarps / hb;  // consumer warps per kv head
-  constexpr int kSps = DecStage<D, kFmt>::kSubTiles;
+  constexpr int kSps = Stage::kSubTiles;
   const int TOK = 16 * wph * kSps;
 
   const int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
@@ -1203,8 +1516,10 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
   w.b = b, w.head = head;
   w.chunk_lo = chunk_lo, w.chunk_hi = chunk_hi, w.kv_len = kv_len, w.n_tiles = n_tiles;
   w.tok_per_stage = TOK, w.kv_bytes = kv_bytes, w.stage_bytes = stage_bytes, w.row_bytes = row_bytes, w.stages = kDecStages;
-  if constexpr (kInt4)
+  if constexpr (kInt4 && NG == 1)
     consume_int4<D, MT, kBf16>(a, w);
+  else if constexpr (kInt4)
+    consume_int4_groups<D, MT, kBf16, NG>(a, w);
   else if constexpr (kFp8)
     consume_fp8<D, MT, kBf16>(a, w);
   else
@@ -1350,9 +1665,9 @@ int decode_chunk_tokens(int kv_bound, int split_k) {
   return c < kDecChunkAlign ? kDecChunkAlign : c;
 }
 
-template <int D, int MT, int kFmt, bool kBf16>
+template <int D, int MT, int kFmt, bool kBf16, int NG = 1>
 static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
-  using Stage = DecStage<D, kFmt>;
+  using Stage = DecStage<D, kFmt, NG>;
   constexpr bool kQuant = kFmt != kFmtPlain;
   constexpr int ROWS = kQuant ? 8 * MT : 16 * MT;
   // tiled copies need no row padding
@@ -1373,7 +1688,7 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   a.stage_bytes = int(stage_bytes);
   const size_t ring = stages * stage_bytes + 1024;  // the kernel aligns the ring to 1024 B
   const size_t smem = ring > cmb ? ring : cmb;
-  auto kern = decode_splitk_kernel<D, MT, kFmt, kBf16>;
+  auto kern = decode_splitk_kernel<D, MT, kFmt, kBf16, NG>;
   // 227 KB per CTA includes the static part (the mbarriers)
   if (smem + 1024 > size_t(227 * 1024) / DecOccupancy<kFmt>::kCtasPerSm) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
   static size_t configured = 0;  // per instantiation: largest size opted into so far
@@ -1394,10 +1709,10 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   return rc;
 }
 
-template <int D, int kFmt, bool kBf16>
+template <int D, int kFmt, bool kBf16, int NG = 1>
 static int launch_decode_mt(const DecodeArgs& a, int mt, int head_blocks, cudaStream_t stream) {
-  if (mt == 1) return launch_decode_t<D, 1, kFmt, kBf16>(a, head_blocks, stream);
-  return launch_decode_t<D, 2, kFmt, kBf16>(a, head_blocks, stream);
+  if (mt == 1) return launch_decode_t<D, 1, kFmt, kBf16, NG>(a, head_blocks, stream);
+  return launch_decode_t<D, 2, kFmt, kBf16, NG>(a, head_blocks, stream);
 }
 
 }  // namespace xfb
@@ -1423,8 +1738,11 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (p->dtype != XFB200_BF16 && p->dtype != XFB200_F16) return set_error(XFB200_E_INVALID, "decode: q dtype must be bf16 or f16");
   const bool int4 = p->kv_format == XFB200_KV_INT4_ROWWISE;
   const bool fp8 = p->kv_format == XFB200_KV_FP8_ROWWISE;
-  if (int4 && p->num_quant_groups != 1)
-    return set_error(XFB200_E_UNSUPPORTED, "decode: int4 cache with %d quantisation groups per row (only 1)", p->num_quant_groups);
+  const int ng = int4 ? p->num_quant_groups : 1;
+  if (int4 && (ng != 1 && ng != 2 && ng != 4 && ng != 8))
+    return set_error(XFB200_E_UNSUPPORTED, "decode: int4 cache with %d quantisation groups per row (1, 2, 4 or 8)", ng);
+  if (int4 && p->head_dim / ng < 16)
+    return set_error(XFB200_E_UNSUPPORTED, "decode: int4 groups of %d elements (at least 16)", p->head_dim / ng);
   if (!int4 && !fp8 && p->kv_format != XFB200_KV_PLAIN) return set_error(XFB200_E_INVALID, "decode: bad kv_format %d", p->kv_format);
   if (fp8 && (p->k_scale_shift == nullptr || p->v_scale_shift == nullptr))
     return set_error(XFB200_E_INVALID, "decode: an fp8 cache needs k_scale_shift and v_scale_shift");
@@ -1478,7 +1796,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
 
   // how the producer may copy: whole stripes by TMA when alignment allows
   const int elem = (int4 || fp8) ? 4 : 2;
-  const int head_elems = int4 ? (1 + p->head_dim / 8) : fp8 ? p->head_dim / 4 : p->head_dim;
+  const int head_elems = int4 ? (ng + p->head_dim / 8) : fp8 ? p->head_dim / 4 : p->head_dim;
   const bool heads_contig = hb == 1 || (a.k_sg == head_elems && a.v_sg == head_elems);
   auto al16 = [&](int64_t elems) { return (elems * elem) % 16 == 0; };
   const bool base_al = (reinterpret_cast<uintptr_t>(p->k) % 16 == 0) && (reinterpret_cast<uintptr_t>(p->v) % 16 == 0);
@@ -1567,6 +1885,18 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   }
   if (fp8)
     return bf16 ? launch_decode_mt<128, kFmtFp8, true>(a, mt, head_blocks, st) : launch_decode_mt<128, kFmtFp8, false>(a, mt, head_blocks, st);
+  if (int4 && ng > 1) {
+#define XFB_DISPATCH_NG(DD, GG) \
+  return bf16 ? launch_decode_mt<DD, kFmtInt4, true, GG>(a, mt, head_blocks, st) : launch_decode_mt<DD, kFmtInt4, false, GG>(a, mt, head_blocks, st);
+    if (p->head_dim == 128) {
+      if (ng == 2) { XFB_DISPATCH_NG(128, 2) }
+      if (ng == 4) { XFB_DISPATCH_NG(128, 4) }
+      XFB_DISPATCH_NG(128, 8)
+    }
+    if (ng == 2) { XFB_DISPATCH_NG(64, 2) }
+    XFB_DISPATCH_NG(64, 4)
+#undef XFB_DISPATCH_NG
+  }
   if (p->head_dim == 128) {
     XFB_DISPATCH(128)
   } else {

@@ -103,8 +103,8 @@ class FwOp(AttentionFwOpBase):
         elif quantized:
             if d.value.dtype != torch.int32:
                 reasons.append("key is int32 (quantised) but value is not")
-            if cls.NUM_GROUPS != 1:
-                reasons.append("int4 caches with more than one quantisation group per row are not supported yet")
+            if cls.NUM_GROUPS not in (1, 2, 4, 8) or K // cls.NUM_GROUPS < 16:
+                reasons.append(f"int4 caches need 1, 2, 4 or 8 quantisation groups of at least 16 elements per row, got NUM_GROUPS={cls.NUM_GROUPS}")
             elif d.key.shape[-1] != K // 8 + cls.NUM_GROUPS or d.value.shape[-1] != d.key.shape[-1]:
                 reasons.append(f"int4 K/V rows must have {K // 8 + cls.NUM_GROUPS} int32 words, got {d.key.shape[-1]}")
         else:
