@@ -99,3 +99,33 @@ def test_fp8_rejects_what_it_cannot_run():
     assert any("k_fp8_scale_shift" in r for r in S.FwOp.not_supported_reasons(inp))
     with pytest.raises(ValueError):
         fmha._memory_efficient_attention_forward(inp, op=S.FwOp)
+
+
+@gpu
+def test_fp8_nan_bytes_in_padding_do_not_leak():
+    """tests/test_mem_eff_attention.py:1750-1853 (``test_nans_in_padding``) for
+    the fp8 cache: rows past a sequence's end hold the NaN byte pattern of e4m3
+    and NaN scale/shift words; the outputs must not change."""
+    require_cuda()
+    B, Mkv, Hkv, G = 3, 256, 2, 8
+    q, kw, vw, kss, vss, k_deq, v_deq = _fp8_case(B, Mkv, Hkv, G, torch.bfloat16, seed=4)
+    lens = [200, 1, 129]
+    bias = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=[1] * B, kv_seqlen=lens, kv_padding=Mkv, device="cuda")
+
+    def run(kw_, vw_, kss_, vss_):
+        inp = S.InputsFp8(
+            query=q.cuda(), key=_expand(kw_.cuda(), G), value=_expand(vw_.cuda(), G), attn_bias=bias,
+            k_fp8_scale_shift=_expand(kss_.cuda(), G).contiguous(), v_fp8_scale_shift=_expand(vss_.cuda(), G).contiguous(),
+        )
+        out, ctx = fmha._memory_efficient_attention_forward_requires_grad(inp, op=S.FwOp)
+        return out, ctx.lse
+
+    out0, lse0 = run(kw, vw, kss, vss)
+    kw2, vw2, kss2, vss2 = kw.clone(), vw.clone(), kss.clone(), vss.clone()
+    for b, n in enumerate(lens):
+        sl = slice(b * Mkv + n, (b + 1) * Mkv)
+        kw2[:, sl], vw2[:, sl] = 0x7F7F7F7F, 0x7F7F7F7F  # e4m3 NaN in every byte
+        kss2[:, sl], vss2[:, sl] = 0x7E007E00, 0x7E007E00  # fp16 NaN scale and shift
+    out1, lse1 = run(kw2, vw2, kss2, vss2)
+    assert not out1.isnan().any() and not lse1.isnan().any()
+    assert torch.equal(out0, out1) and torch.equal(lse0, lse1)

@@ -1226,6 +1226,15 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
       {
         const uint8_t* v0 = vst + boff + (2 * c) * 128 + (r & 3) * 4;  // token 2c; +128: 2c+1; +1024: 2c+8; +1152: 2c+9
         const int x0s = (2 * c) & 7, x1s = (2 * c + 1) & 7;            // chunk swizzles of the even / odd token
+        // Bytes of tokens past the end were never copied and may hold the NaN patterns of
+        // e4m3 (0 x NaN = NaN): they are cleared before the conversion.  After the byte
+        // permute, bytes 0 and 2 belong to the even token, bytes 1 and 3 to the odd one.
+        uint32_t vmask_a = 0xFFFFFFFFu, vmask_b = 0xFFFFFFFFu;
+        if (!all_visible) {
+          const int tv = t_sub + 2 * c;
+          vmask_a = (tv < w.chunk_hi ? 0x00FF00FFu : 0u) | (tv + 1 < w.chunk_hi ? 0xFF00FF00u : 0u);
+          vmask_b = (tv + 8 < w.chunk_hi ? 0x00FF00FFu : 0u) | (tv + 9 < w.chunk_hi ? 0xFF00FF00u : 0u);
+        }
 #pragma unroll
         for (int wj = 0; wj < WJ; ++wj) {
           const int ch = (r >> 2) + 2 * wj;  // 16-byte chunk of word r + 8 wj
@@ -1235,10 +1244,10 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
           const uint32_t xd = *reinterpret_cast<const uint32_t*>(v0 + 1152 + (ch ^ x1s) * 16);
           // bytes (a0 b0 a1 b1) and (a2 b2 a3 b3): element e of the two tokens side by side
           uint32_t y01[2], y23[2], z01[2], z23[2];
-          cvt_e4m3x4(__byte_perm(xa, xb, 0x5140), y01[0], y01[1]);
-          cvt_e4m3x4(__byte_perm(xa, xb, 0x7362), y23[0], y23[1]);
-          cvt_e4m3x4(__byte_perm(xc, xd, 0x5140), z01[0], z01[1]);
-          cvt_e4m3x4(__byte_perm(xc, xd, 0x7362), z23[0], z23[1]);
+          cvt_e4m3x4(__byte_perm(xa, xb, 0x5140) & vmask_a, y01[0], y01[1]);
+          cvt_e4m3x4(__byte_perm(xa, xb, 0x7362) & vmask_a, y23[0], y23[1]);
+          cvt_e4m3x4(__byte_perm(xc, xd, 0x5140) & vmask_b, z01[0], z01[1]);
+          cvt_e4m3x4(__byte_perm(xc, xd, 0x7362) & vmask_b, z23[0], z23[1]);
 #pragma unroll
           for (int p = 0; p < 2; ++p) {
             const uint32_t vf[4] = {y01[p], y23[p], z01[p], z23[p]};  // rows r: d = 4(r+8wj)+p, rows r+8: d+2
