@@ -162,6 +162,12 @@ typedef struct {
   const int32_t* v_scale_shift;
   int64_t ks_stride_m, ks_stride_g;
   int64_t vs_stride_m, vs_stride_g;
+  /* Gappy caches (BlockDiagonalGappyKeysMask and its paged form, fmha/attn_bias.py:33-47): NULL, or
+   * [batch] first key row of every sequence -- an absolute row of k/v for a padded cache (kv_rows
+   * = number of rows of k/v), a row inside the sequence's block table for a paged one.  kv_padding
+   * then bounds seqlen_k[b]. */
+  const int32_t* kv_seqstart;
+  int64_t kv_rows;
 } xfb200_decode_params;
 
 XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t kv_heads, int32_t q_per_kv, int32_t head_dim,

@@ -310,3 +310,24 @@ def test_fp8_rowwise_format():
     assert torch.allclose(shift, x.mean(dim=1)) and torch.allclose(scale, 448.0 / (x - shift[:, None]).abs().max(dim=1)[0])
     back = oracle.dequantize_fp8_asymmetric(q, scale, shift)
     assert (back - x).abs().max() < 0.5  # the reference's scale choice uses little of the e4m3 range
+
+
+def test_gappy_keys_mask_materialize():
+    """Keys of block b are the columns [starts[b], starts[b] + len[b]); the
+    causal form is bottom-right aligned inside the block."""
+    from xformers_b200.ops.fmha import attn_bias as ab
+
+    bias = ab.BlockDiagonalGappyKeysMask.from_seqlens(q_seqlen=[1, 2], kv_seqstarts=[1, 4, 8], kv_seqlen=[2, 3])
+    m = bias.materialize((3, 8))
+    vis = (m == 0).int().tolist()
+    assert vis == [[0, 1, 1, 0, 0, 0, 0, 0], [0, 0, 0, 0, 1, 1, 1, 0], [0, 0, 0, 0, 1, 1, 1, 0]]
+    cb = ab.BlockDiagonalCausalWithOffsetGappyKeysMask.from_seqlens(q_seqlen=[1, 2], kv_seqstarts=[1, 4, 8], kv_seqlen=[2, 3])
+    vis = (cb.materialize((3, 8)) == 0).int().tolist()
+    assert vis == [[0, 1, 1, 0, 0, 0, 0, 0], [0, 0, 0, 0, 1, 1, 0, 0], [0, 0, 0, 0, 1, 1, 1, 0]]
+    with pytest.raises(ValueError):
+        ab.BlockDiagonalGappyKeysMask.from_seqlens(q_seqlen=[1], kv_seqstarts=[0, 4], kv_seqlen=[5])
+    paged = bias.make_paged(torch.tensor([[1, 0], [0, 1]], dtype=torch.int32), 4, ab.PagedBlockDiagonalGappyKeysMask, notional_padding=4)
+    assert paged.slot_starts().tolist() == [1, 0]
+    pv = (paged.materialize((3, 8)) == 0).int().tolist()
+    # sequence 0: logical rows 1, 2 of its table [1, 0] -> physical rows 5, 6; sequence 1: rows 0..2 of table [0, 1] -> 0, 1, 2
+    assert pv == [[0, 0, 0, 0, 0, 1, 1, 0], [1, 1, 1, 0, 0, 0, 0, 0], [1, 1, 1, 0, 0, 0, 0, 0]]

@@ -121,6 +121,8 @@ class DecodeParams(C.Structure):
         ("ks_stride_g", C.c_int64),
         ("vs_stride_m", C.c_int64),
         ("vs_stride_g", C.c_int64),
+        ("kv_seqstart", C.c_void_p),
+        ("kv_rows", C.c_int64),
     ]
 
 

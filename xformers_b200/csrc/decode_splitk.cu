@@ -42,6 +42,7 @@ struct DecodeArgs {
   float* part_lse;  // [batch, split, kv_heads, R]
   int32_t* status;  // device status word (timed-out waits)
   const int32_t* seqlen_k;
+  const int32_t* kv_start;  // gappy caches: first key row of every sequence (padded: absolute row; paged: row inside its block table)
   const int32_t* block_tables;
   int32_t batch, mq, kv_heads, q_per_kv;
   int32_t kv_padding, page_size, bt_stride;
@@ -1383,8 +1384,11 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
     // so that a lane waits for that load once per page instead of once per stage
     int cached_page = -1;
     int64_t cached_base = 0;
-    auto row_of = [&](int t) -> int64_t {
-      if (a.block_tables == nullptr) return int64_t(b) * a.kv_padding + t;
+    const int64_t kv_base = a.kv_start != nullptr ? int64_t(a.kv_start[b]) : int64_t(b) * a.kv_padding;  // padded / gappy cache
+    const int t_shift = (a.block_tables != nullptr && a.kv_start != nullptr) ? a.kv_start[b] : 0;       // paged gappy cache
+    auto row_of = [&](int t_rel) -> int64_t {
+      if (a.block_tables == nullptr) return kv_base + t_rel;
+      const int t = t_rel + t_shift;
       const int pg = t / a.page_size;
       if (pg != cached_page) {
         cached_page = pg;
@@ -1452,8 +1456,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
           const int rem = i % (hb * words_per_head);
           const int hh = rem / words_per_head, wd = rem % words_per_head;
           const int t = t0 + tok;
-          const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
-                                             : int64_t(b) * a.kv_padding + t;
+          const int64_t row = row_of(t);
           const int64_t ko = (row * a.k_sm + (head0 + hh) * a.k_sg) * kElem + wd * 4;
           const int64_t vo = (row * a.v_sm + (head0 + hh) * a.v_sg) * kElem + wd * 4;
           *reinterpret_cast<uint32_t*>(ks + tok * row_bytes + hh * kHeadBytes + wd * 4) = __ldg(reinterpret_cast<const uint32_t*>(kg + ko));
@@ -1474,8 +1477,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
         const int hh = i % per_tok_copies;
         const int tok = gi * grp;
         const int t = t0 + tok;
-        const int64_t row = a.block_tables ? int64_t(a.block_tables[int64_t(b) * a.bt_stride + t / a.page_size]) * a.page_size + t % a.page_size
-                                           : int64_t(b) * a.kv_padding + t;
+        const int64_t row = row_of(t);
         const int64_t ko = (row * a.k_sm + (head0 + hh) * a.k_sg) * kElem;
         const int64_t vo = (row * a.v_sm + (head0 + hh) * a.v_sg) * kElem;
         bulk_g2s(ks + tok * row_bytes + hh * kHeadBytes, kg + ko, seg_bytes, &full_bar[st]);
@@ -1772,7 +1774,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
 
   DecodeArgs a{};
   a.q = p->q, a.k = p->k, a.v = p->v, a.out = p->out, a.lse = p->lse;
-  a.seqlen_k = p->seqlen_k, a.block_tables = p->block_tables;
+  a.seqlen_k = p->seqlen_k, a.block_tables = p->block_tables, a.kv_start = p->kv_seqstart;
   a.batch = p->batch, a.mq = p->mq, a.kv_heads = p->kv_heads, a.q_per_kv = p->q_per_kv;
   a.kv_padding = p->kv_padding, a.page_size = p->page_size, a.bt_stride = p->block_table_stride;
   a.split_k = p->split_k;
@@ -1819,7 +1821,8 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     // their bytes, and a packed token stripe is only hb * 68 B: when the
     // tokens of a page (or of the padded row) follow one another in memory,
     // copy runs of up to 64 tokens at once.
-    if (int4 && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
+    // (not for gappy caches: a run could cross a page, or the end of the tensor)
+    if (int4 && p->kv_seqstart == nullptr && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
       const int span = p->block_tables ? p->page_size : p->kv_padding;
       // a run must fit the stage it is copied into (a power of two of tokens)
       const int stage_tokens = p->head_dim == 128 ? DecStage<128, kFmtInt4>::tokens(hb) : DecStage<64, kFmtInt4>::tokens(hb);
@@ -1829,7 +1832,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     }
   } else if (al16(p->k_stride_m) && al16(p->v_stride_m) && al16(a.k_sg) && al16(a.v_sg) && al16(head_elems)) {
     a.copy_mode = 1;
-  } else if (int4 && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
+  } else if (int4 && p->kv_seqstart == nullptr && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
              p->v_stride_m == p->k_stride_m) {
     // tokens are contiguous: copy groups of 2 or 4 tokens so that each copy is a multiple of 16 B
     int g = 2;
@@ -1847,7 +1850,12 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
   if (fp8 && a.copy_mode != 0) return set_error(XFB200_E_UNSUPPORTED, "decode: the heads of an fp8 cache row must be contiguous");
   a.box_tok = 16;
-  if (!int4 && a.copy_mode == 0 && (p->kv_heads == 1 || (a.k_sg == head_elems && a.v_sg == head_elems))) {
+  const bool gappy = p->kv_seqstart != nullptr;
+  if (gappy && p->block_tables == nullptr && p->kv_rows <= 0)
+    return set_error(XFB200_E_INVALID, "decode: a gappy cache needs kv_rows, the number of key rows of the tensor");
+  // (a run of a paged gappy cache may start anywhere inside a page: per-token copies there)
+  if (!int4 && a.copy_mode == 0 && !(gappy && p->block_tables != nullptr) &&
+      (p->kv_heads == 1 || (a.k_sg == head_elems && a.v_sg == head_elems))) {
     // The copy engine's throughput is set by the number of copies: one tiled
     // copy per run of tokens that is contiguous in the cache (a whole stage, or
     // what a page allows) instead of one bulk copy per token.
@@ -1859,7 +1867,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     if (box >= (fp8 ? 16 : 8) && enc != nullptr) {
       // token rows: all of a padded cache (rows past the end read as zero); a paged
       // pool's size is not part of the call, and a copy never leaves its page
-      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : gappy ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
       // 16-bit cache: {64 elements, token rows, 128-byte column groups}; fp8: {128 bytes, token rows, kv heads}
       const cuuint64_t dims[3] = {cuuint64_t(fp8 ? 128 : 64), rows, fp8 ? cuuint64_t(p->kv_heads) : cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
       const cuuint32_t bx[3] = {cuuint32_t(fp8 ? 128 : 64), cuuint32_t(box), cuuint32_t(fp8 ? hb : hb * (p->head_dim / 64))};

@@ -255,6 +255,45 @@ class _PaddedSeqLenInfo(_SeqLenInfo):
         raise NotImplementedError("a padded cache is not split back into sequences")
 
 
+@dataclass
+class _GappySeqInfo(_PaddedSeqLenInfo):
+    """Sequence b owns the key rows ``[seqstart[b], seqstart[b] + seqlen[b])``;
+    ``seqstart`` has ``n + 1`` entries (the last one closes the last slot) and
+    the slots need not be equally long (fmha/attn_bias.py:21, ``_GappySeqInfo``;
+    tests/test_fmha_merge_attentions.py:406-414).  ``padding`` is the longest slot."""
+
+    def to(self, device) -> "_GappySeqInfo":
+        if self.seqlen.device == torch.device(device):
+            return self
+        return _GappySeqInfo(
+            seqstart=self.seqstart.to(device),
+            max_seqlen=self.max_seqlen,
+            min_seqlen=self.min_seqlen,
+            seqstart_py=self.seqstart_py,
+            seqlen=self.seqlen.to(device),
+            seqlen_py=self.seqlen_py,
+            padding=self.padding,
+        )
+
+    @classmethod
+    def from_seqlens_gappy(cls, seqstarts: Sequence[int], seqlens: Sequence[int], *, device=None) -> "_GappySeqInfo":
+        seqstarts, seqlens = [int(s) for s in seqstarts], [int(s) for s in seqlens]
+        if len(seqstarts) != len(seqlens) + 1:
+            raise ValueError(f"kv_seqstarts needs one entry more than kv_seqlen, got {len(seqstarts)} and {len(seqlens)}")
+        slots = [seqstarts[i + 1] - seqstarts[i] for i in range(len(seqlens))]
+        if any(n < 0 or n > slot for n, slot in zip(seqlens, slots)):
+            raise ValueError(f"Seqlens {seqlens} do not fit the slots between the starts {seqstarts}")
+        return cls(
+            seqstart=torch.tensor(seqstarts, dtype=torch.int32, device=device),
+            max_seqlen=max(seqlens) if seqlens else -1,
+            min_seqlen=min(seqlens) if seqlens else -1,
+            seqstart_py=seqstarts,
+            seqlen=torch.tensor(seqlens, dtype=torch.int32, device=device),
+            seqlen_py=seqlens,
+            padding=max(slots) if slots else 0,
+        )
+
+
 # ---------------------------------------------------------------------------
 # block-diagonal family (queries and keys concatenated, batch 1)
 # ---------------------------------------------------------------------------
@@ -485,6 +524,45 @@ class BlockDiagonalCausalWithOffsetPaddedKeysMask(BlockDiagonalPaddedKeysMask):
 
 
 @dataclass
+class BlockDiagonalGappyKeysMask(BlockDiagonalPaddedKeysMask):
+    """Keys of sequence b are the rows ``[kv_seqstarts[b], kv_seqstarts[b] +
+    kv_seqlen[b])`` of the flat key tensor: like the padded-keys mask, but the
+    first row of every sequence is free (tests/test_fmha_merge_attentions.py:406-414,
+    tests/test_mem_eff_attention.py:2521-2525)."""
+
+    k_seqinfo: _GappySeqInfo
+
+    @classmethod
+    def from_seqlens(cls, q_seqlen: Sequence[int], kv_seqstarts: Sequence[int], kv_seqlen: Sequence[int], *, device=None):  # type: ignore[override]
+        if len(q_seqlen) != len(kv_seqlen):
+            raise ValueError("q_seqlen and kv_seqlen must describe the same number of sequences")
+        return cls(
+            q_seqinfo=_SeqLenInfo.from_seqlens(q_seqlen, device=device),
+            k_seqinfo=_GappySeqInfo.from_seqlens_gappy(kv_seqstarts, kv_seqlen, device=device),
+        )
+
+    def make_paged(self, block_tables, page_size, paged_type, notional_padding=None):  # type: ignore[override]
+        """Keys reached through ``block_tables``; sequence b's logical rows are
+        those of the slot ``[b * notional_padding, (b+1) * notional_padding)``
+        (tests/test_mem_eff_attention.py:2516-2525)."""
+        if notional_padding is None:
+            raise ValueError("make_paged of a gappy bias needs notional_padding")
+        starts = self.k_seqinfo.seqstart_py
+        for b, n in enumerate(self.k_seqinfo.seqlen_py):
+            if not (b * notional_padding <= starts[b] and starts[b] + n <= (b + 1) * notional_padding):
+                raise ValueError(f"sequence {b} does not lie inside its notional slot of {notional_padding} rows")
+        return paged_type(
+            q_seqinfo=self.q_seqinfo, k_seqinfo=self.k_seqinfo, block_tables=block_tables, page_size=page_size,
+            notional_padding=notional_padding,
+        )
+
+
+@dataclass
+class BlockDiagonalCausalWithOffsetGappyKeysMask(BlockDiagonalGappyKeysMask):
+    _CAUSAL: ClassVar[bool] = True
+
+
+@dataclass
 class PagedBlockDiagonalPaddedKeysMask(AttentionBias):
     q_seqinfo: _SeqLenInfo
     k_seqinfo: _PaddedSeqLenInfo
@@ -544,6 +622,47 @@ class PagedBlockDiagonalPaddedKeysMask(AttentionBias):
 @dataclass
 class PagedBlockDiagonalCausalWithOffsetPaddedKeysMask(PagedBlockDiagonalPaddedKeysMask):
     _UNPAGED_TYPE: ClassVar[Type[BlockDiagonalPaddedKeysMask]] = BlockDiagonalCausalWithOffsetPaddedKeysMask
+
+
+@dataclass
+class PagedBlockDiagonalGappyKeysMask(PagedBlockDiagonalPaddedKeysMask):
+    """Gappy keys behind a block table: the logical row ``kv_seqstarts[b] - b *
+    notional_padding + t`` of sequence b is the physical row
+    ``block_tables[b, row // page_size] * page_size + row % page_size``."""
+
+    k_seqinfo: _GappySeqInfo
+    notional_padding: int = 0
+
+    _UNPAGED_TYPE: ClassVar[Type[BlockDiagonalPaddedKeysMask]] = BlockDiagonalGappyKeysMask
+
+    def to(self, device):
+        return type(self)(
+            q_seqinfo=self.q_seqinfo.to(device), k_seqinfo=self.k_seqinfo.to(device),
+            block_tables=self.block_tables.to(device), page_size=self.page_size, notional_padding=self.notional_padding,
+        )
+
+    def slot_starts(self) -> torch.Tensor:
+        """int32 ``[n]`` on the device of the lengths: first logical row of every sequence inside its block table."""
+        n = len(self.k_seqinfo.seqlen_py)
+        base = torch.arange(n, dtype=torch.int32, device=self.k_seqinfo.seqstart.device) * self.notional_padding
+        return (self.k_seqinfo.seqstart[:n] - base).contiguous()
+
+    def materialize(self, shape, dtype=torch.float32, device="cpu") -> torch.Tensor:
+        """Mask over *physical* key rows: shape[-1] = num_pages * page_size."""
+        out = torch.full((self.q_seqinfo.seqstart_py[-1], shape[-1]), -math.inf, dtype=dtype, device=device)
+        bt = self.block_tables.to(device).long()
+        causal = self._UNPAGED_TYPE._CAUSAL
+        for b, ((qs, qe), n) in enumerate(zip(self.q_seqinfo.intervals(), self.k_seqinfo.seqlen_py)):
+            t = torch.arange(n, device=device) + (self.k_seqinfo.seqstart_py[b] - b * self.notional_padding)
+            rows = bt[b, t // self.page_size] * self.page_size + t % self.page_size
+            block = _band(qe - qs, n, device, shift=n - (qe - qs)) if causal else torch.ones((qe - qs, n), dtype=torch.bool, device=device)
+            out[qs:qe, rows] = _additive(block, dtype)
+        return out.expand(*shape)
+
+
+@dataclass
+class PagedBlockDiagonalCausalWithOffsetGappyKeysMask(PagedBlockDiagonalGappyKeysMask):
+    _UNPAGED_TYPE: ClassVar[Type[BlockDiagonalPaddedKeysMask]] = BlockDiagonalCausalWithOffsetGappyKeysMask
 
 
 VARLEN_BIASES = (

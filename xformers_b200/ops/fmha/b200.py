@@ -20,7 +20,9 @@ from .attn_bias import (
     BlockDiagonalCausalLocalAttentionFromBottomRightMask,
     BlockDiagonalCausalLocalAttentionMask,
     BlockDiagonalCausalMask,
+    BlockDiagonalCausalWithOffsetGappyKeysMask,
     BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    BlockDiagonalGappyKeysMask,
     BlockDiagonalMask,
     BlockDiagonalPaddedKeysMask,
     LowerTriangularFromBottomRightMask,
@@ -43,7 +45,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 def _mask_of(bias: Any) -> Tuple[int, int]:
     """(mask_type, window_left) of a bias object."""
-    if bias is None or type(bias) in (BlockDiagonalMask, BlockDiagonalPaddedKeysMask):
+    if bias is None or type(bias) in (BlockDiagonalMask, BlockDiagonalPaddedKeysMask, BlockDiagonalGappyKeysMask):
         return _lib.MASK_NONE, -1
     if type(bias) in (LowerTriangularMask, BlockDiagonalCausalMask):
         return _lib.MASK_CAUSAL_TOP_LEFT, -1
@@ -51,6 +53,7 @@ def _mask_of(bias: Any) -> Tuple[int, int]:
         LowerTriangularFromBottomRightMask,
         BlockDiagonalCausalFromBottomRightMask,
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
+        BlockDiagonalCausalWithOffsetGappyKeysMask,
     ):
         return _lib.MASK_CAUSAL_BOTTOM_RIGHT, -1
     if type(bias) in (LowerTriangularMaskLocalAttention, BlockDiagonalCausalLocalAttentionMask):
@@ -80,6 +83,8 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalLocalAttentionFromBottomRightMask,
         BlockDiagonalPaddedKeysMask,
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
+        BlockDiagonalGappyKeysMask,
+        BlockDiagonalCausalWithOffsetGappyKeysMask,
     )
     SUPPORTS_DROPOUT = False
     SUPPORTS_CUSTOM_SCALE = True

@@ -20,9 +20,13 @@ import torch
 
 from ... import _lib
 from .attn_bias import (
+    BlockDiagonalCausalWithOffsetGappyKeysMask,
     BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    BlockDiagonalGappyKeysMask,
     BlockDiagonalPaddedKeysMask,
+    PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
     PagedBlockDiagonalCausalWithOffsetPaddedKeysMask,
+    PagedBlockDiagonalGappyKeysMask,
     PagedBlockDiagonalPaddedKeysMask,
 )
 from .common import AttentionFwOpBase, Context, Inputs, InputsFp8, check_lastdim_alignment_stride1
@@ -59,6 +63,10 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
         PagedBlockDiagonalPaddedKeysMask,
         PagedBlockDiagonalCausalWithOffsetPaddedKeysMask,
+        BlockDiagonalGappyKeysMask,
+        BlockDiagonalCausalWithOffsetGappyKeysMask,
+        PagedBlockDiagonalGappyKeysMask,
+        PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
     )
     SUPPORTS_DROPOUT = False
     SUPPORTS_CUSTOM_SCALE = True
@@ -223,14 +231,31 @@ class FwOp(AttentionFwOpBase):
                 p.batch = len(bias.k_seqinfo.seqlen_py)
                 p.mq = bias.q_seqinfo.max_seqlen
                 p.seqlen_k = bias.k_seqinfo.seqlen.data_ptr()
+                kv_start = None  # keeps the tensor alive until the launch
                 if isinstance(bias, PagedBlockDiagonalPaddedKeysMask):
                     p.block_tables = bias.block_tables.data_ptr()
                     p.page_size = bias.page_size
                     p.block_table_stride = bias.block_tables.stride(0)
                     p.kv_padding = bias.block_tables.shape[1] * bias.page_size
+                    if isinstance(bias, PagedBlockDiagonalGappyKeysMask):
+                        kv_start = bias.slot_starts()
+                        p.kv_padding = bias.notional_padding
                 else:
                     p.kv_padding = bias.k_seqinfo.padding
-                if isinstance(bias, (BlockDiagonalCausalWithOffsetPaddedKeysMask, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask)):
+                    if isinstance(bias, BlockDiagonalGappyKeysMask):
+                        kv_start = bias.k_seqinfo.seqstart
+                        p.kv_rows = k.shape[1]
+                if kv_start is not None:
+                    p.kv_seqstart = kv_start.data_ptr()
+                if isinstance(
+                    bias,
+                    (
+                        BlockDiagonalCausalWithOffsetPaddedKeysMask,
+                        PagedBlockDiagonalCausalWithOffsetPaddedKeysMask,
+                        BlockDiagonalCausalWithOffsetGappyKeysMask,
+                        PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
+                    ),
+                ):
                     p.mask_type = _lib.MASK_CAUSAL_BOTTOM_RIGHT
             else:
                 p.batch, p.mq = B, Mq
