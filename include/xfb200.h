@@ -104,6 +104,15 @@ typedef struct {
   float scale;
   int32_t out_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
   int32_t reserved;
+  /* Additive bias (a plain tensor as attn_bias, or LowerTriangularMaskWithTensorBias,
+   * fmha/attn_bias.py:43; tests/test_mem_eff_attention.py:1440-1449): NULL, or
+   * [batch, G, H, mq, mkv] with unit stride on the last axis and element strides
+   * below (0 = broadcast), added to q k^T * scale before the mask and the softmax.
+   * Dense batches only; runs on the mma.sync kernel. */
+  const void* bias;
+  int32_t bias_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
+  int32_t reserved2;
+  int64_t bias_stride_b, bias_stride_g, bias_stride_h, bias_stride_m;
 } xfb200_prefill_params;
 
 XFB200_API int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream);

@@ -290,3 +290,50 @@ def test_custom_stream_and_output_dtype():
     ro, _ = ref(q, k, v, ab.LowerTriangularMask())
     assert (out.cpu() - ro).abs().max() <= ATOL_O[dtype]
     _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("bias_dtype", [None, torch.float32])
+@pytest.mark.parametrize("layout", ["BMHK", "BMGHK", "BMK"])
+@pytest.mark.parametrize("Mq,Mkv,D", [(64, 64, 64), (100, 300, 128), (257, 129, 32)])
+@pytest.mark.parametrize("op", [P.FwOp, P.FwOp_Generic])
+def test_additive_tensor_bias(op, Mq, Mkv, D, layout, bias_dtype):
+    """A plain tensor as attn_bias is added to q k^T * scale before the softmax
+    (tests/test_mem_eff_attention.py:420-440, 664-682)."""
+    require_cuda()
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(31)
+    B, G, H = 2, 2, 3
+    if layout == "BMHK":
+        qs, ks, bs = (B, Mq, H, D), (B, Mkv, H, D), (B, H, Mq, Mkv)
+    elif layout == "BMGHK":
+        qs, ks, bs = (B, Mq, G, H, D), (B, Mkv, G, H, D), (B, G, H, Mq, Mkv)
+    else:
+        qs, ks, bs = (B * H, Mq, D), (B * H, Mkv, D), (B * H, Mq, Mkv)
+    q, k, v = (torch.randn(s, generator=g).to(dtype).cuda() for s in (qs, ks, ks))
+    bias = (torch.randn(bs, generator=g) * 2).to(bias_dtype or dtype)
+    bias[..., 0, : Mkv // 2] = float("-inf")  # -inf entries mask keys like any mask
+    bias = bias.cuda()
+    assert not op.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), bias.float().cpu())
+    assert_o_lse(out, lse, ro, rl, dtype, f"tensor bias {layout}")
+
+
+@gpu
+@pytest.mark.parametrize("Mq,Mkv", [(128, 128), (70, 200)])
+def test_causal_with_tensor_bias(Mq, Mkv):
+    """LowerTriangularMaskWithTensorBias (tests/test_mem_eff_attention.py:1440-1449);
+    the tensor is broadcast over the heads with stride 0."""
+    require_cuda()
+    dtype, B, H, D = torch.float16, 2, 4, 64
+    g = torch.Generator().manual_seed(32)
+    q = torch.randn(B, Mq, H, D, generator=g).to(dtype).cuda()
+    k = torch.randn(B, Mkv, H, D, generator=g).to(dtype).cuda()
+    v = torch.randn(B, Mkv, H, D, generator=g).to(dtype).cuda()
+    t = torch.randn(B, 1, Mq, Mkv, generator=g).to(dtype).cuda().expand(B, H, Mq, Mkv)
+    bias = ab.LowerTriangularMaskWithTensorBias(t)
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=P.FwOp)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), ab.LowerTriangularMaskWithTensorBias(t.float().cpu()))
+    assert_o_lse(out, lse, ro, rl, dtype, "causal + tensor bias")
+    assert P.FwOp_Tcgen05.not_supported_reasons(fmha.Inputs(q, k, v, bias))

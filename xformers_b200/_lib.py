@@ -74,6 +74,13 @@ class PrefillParams(C.Structure):
         ("scale", C.c_float),
         ("out_dtype", C.c_int32),
         ("reserved", C.c_int32),
+        ("bias", C.c_void_p),
+        ("bias_dtype", C.c_int32),
+        ("reserved2", C.c_int32),
+        ("bias_stride_b", C.c_int64),
+        ("bias_stride_g", C.c_int64),
+        ("bias_stride_h", C.c_int64),
+        ("bias_stride_m", C.c_int64),
     ]
 
 

@@ -49,8 +49,15 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
   if (((p->o_strides.b | p->o_strides.m | p->o_strides.g | p->o_strides.h) * osz) % 8 || (reinterpret_cast<uintptr_t>(p->out) & 7))
     return set_error(XFB200_E_INVALID, "prefill: out rows must be 8-byte aligned");
 
+  if (p->bias != nullptr) {
+    if (p->seqstart_q != nullptr) return set_error(XFB200_E_UNSUPPORTED, "prefill: an additive bias with concatenated sequences");
+    if (p->bias_dtype != XFB200_BF16 && p->bias_dtype != XFB200_F16 && p->bias_dtype != XFB200_F32)
+      return set_error(XFB200_E_INVALID, "prefill: bad bias_dtype %d", p->bias_dtype);
+  }
+
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool can100 = g_prefill_path != 1 && p->mkv > 0 && prefill_sm100_supported(p);
+  // (the tcgen05 kernels take no additive bias)
+  const bool can100 = g_prefill_path != 1 && p->mkv > 0 && p->bias == nullptr && prefill_sm100_supported(p);
   if (g_prefill_path >= 2 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
   if (can100) return prefill_sm100_launch(p, st);
   return prefill_generic_launch(p, st);

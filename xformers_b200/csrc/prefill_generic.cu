@@ -103,6 +103,19 @@ __global__ void __launch_bounds__(kGenThreads) prefill_generic_kernel(const __gr
   for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int i0 = m0 + warp * 16 + r, i1 = i0 + 8;  // local query indices of this thread's rows
+  // additive bias: rows of this thread's two query rows (dense batches only), or null
+  const uint8_t* bias_row[2] = {nullptr, nullptr};
+  const int bias_esz = p.bias_dtype == XFB200_F32 ? 4 : 2;
+  if (p.bias != nullptr) {
+    const int64_t base = int64_t(b) * p.bias_stride_b + int64_t(g) * p.bias_stride_g + int64_t(h) * p.bias_stride_h;
+    if (i0 < qlen) bias_row[0] = reinterpret_cast<const uint8_t*>(p.bias) + (base + int64_t(i0) * p.bias_stride_m) * bias_esz;
+    if (i1 < qlen) bias_row[1] = reinterpret_cast<const uint8_t*>(p.bias) + (base + int64_t(i1) * p.bias_stride_m) * bias_esz;
+  }
+  auto load_bias = [&](const uint8_t* row, int col) -> float {
+    if (p.bias_dtype == XFB200_F32) return reinterpret_cast<const float*>(row)[col];
+    if (p.bias_dtype == XFB200_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(row)[col]);
+    return __half2float(reinterpret_cast<const __half*>(row)[col]);
+  };
 
   for (int n0 = n_lo; n0 < n_hi; n0 += kGenBN) {
     __syncthreads();  // previous tile fully consumed
@@ -128,7 +141,7 @@ __global__ void __launch_bounds__(kGenThreads) prefill_generic_kernel(const __gr
       }
     }
 
-    // mask + online softmax
+    // additive bias + mask + online softmax
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < kGenBN / 8; ++j)
@@ -139,7 +152,11 @@ __global__ void __launch_bounds__(kGenThreads) prefill_generic_kernel(const __gr
         bool vis = col < klen;
         if (causal) vis = vis && col <= i + shift;
         if (p.window_left >= 0) vis = vis && col >= i + shift - p.window_left;
-        const float x = vis ? s[j][e] * ga.scale_log2 : -INFINITY;
+        float x = -INFINITY;
+        if (vis) {
+          x = s[j][e] * ga.scale_log2;
+          if (bias_row[e >> 1] != nullptr) x = fmaf(load_bias(bias_row[e >> 1], col), 1.4426950408889634f, x);
+        }
         s[j][e] = x;
         mx[e >> 1] = fmaxf(mx[e >> 1], x);
       }

@@ -129,8 +129,8 @@ class LocalAttentionFromBottomRightMask(AttentionBias):
 
 
 class LowerTriangularMaskWithTensorBias(LowerTriangularMask):
-    """Causal mask plus an additive tensor.  Kept for ``materialize`` parity
-    (tests/test_mem_eff_attention.py:1431-1449); no kernel here takes it."""
+    """Causal mask plus an additive tensor ``[B, (G,) H, Mq, Mkv]``
+    (tests/test_mem_eff_attention.py:1431-1449); runs on the mma.sync prefill kernel."""
 
     HOLDS_DENSE_TENSOR = True
 

@@ -28,6 +28,7 @@ from .attn_bias import (
     LowerTriangularFromBottomRightMask,
     LowerTriangularMask,
     LowerTriangularMaskLocalAttention,
+    LowerTriangularMaskWithTensorBias,
 )
 from .common import AttentionFwOpBase, Context, Inputs, check_lastdim_alignment_stride1
 
@@ -43,11 +44,22 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None or t.numel() == 0 else t.data_ptr()
 
 
+def _bias_tensor(bias: Any) -> Optional[torch.Tensor]:
+    """The additive tensor of a bias, if it carries one."""
+    if isinstance(bias, torch.Tensor):
+        return bias
+    if isinstance(bias, LowerTriangularMaskWithTensorBias):
+        return bias._bias
+    return None
+
+
 def _mask_of(bias: Any) -> Tuple[int, int]:
     """(mask_type, window_left) of a bias object."""
     if bias is None or type(bias) in (BlockDiagonalMask, BlockDiagonalPaddedKeysMask, BlockDiagonalGappyKeysMask):
         return _lib.MASK_NONE, -1
-    if type(bias) in (LowerTriangularMask, BlockDiagonalCausalMask):
+    if isinstance(bias, torch.Tensor):
+        return _lib.MASK_NONE, -1
+    if type(bias) in (LowerTriangularMask, BlockDiagonalCausalMask, LowerTriangularMaskWithTensorBias):
         return _lib.MASK_CAUSAL_TOP_LEFT, -1
     if type(bias) in (
         LowerTriangularFromBottomRightMask,
@@ -85,6 +97,8 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
         BlockDiagonalGappyKeysMask,
         BlockDiagonalCausalWithOffsetGappyKeysMask,
+        torch.Tensor,
+        LowerTriangularMaskWithTensorBias,
     )
     SUPPORTS_DROPOUT = False
     SUPPORTS_CUSTOM_SCALE = True
@@ -122,8 +136,26 @@ class FwOp(AttentionFwOpBase):
             pass  # handled by the mma.sync kernel
         if d.output_dtype is not None and d.output_dtype not in _DTYPE_CODE:
             reasons.append(f"output_dtype={d.output_dtype}")
-        if isinstance(d.attn_bias, torch.Tensor):
-            reasons.append("additive tensor biases are not supported")
+        bt = _bias_tensor(d.attn_bias)
+        if bt is not None:
+            q5 = d.get_qkv_in_bmghk()[0]
+            want = tuple(q5.shape[:1]) + tuple(q5.shape[2:4]) + (q5.shape[1], d.key.shape[1])
+            if bt.ndim == 5:
+                shape5 = tuple(bt.shape)
+            elif bt.ndim == 4:
+                shape5 = tuple(bt.shape[:1]) + (1,) + tuple(bt.shape[1:])
+            elif bt.ndim == 3:  # BMK inputs before they are brought to BMHK
+                shape5 = tuple(bt.shape[:1]) + (1, 1) + tuple(bt.shape[1:])
+            else:
+                shape5 = None
+            if shape5 != want:
+                reasons.append(f"additive bias of shape {tuple(bt.shape)}: expected [B, (G,) H, Mq, Mkv] = {want}")
+            elif bt.stride(-1) != 1:
+                reasons.append("additive bias needs unit stride on its last axis")
+            if bt.dtype not in _DTYPE_CODE:
+                reasons.append(f"additive bias dtype {bt.dtype}")
+            if cls.KERNEL_PATH >= 2:
+                reasons.append("additive biases run on the mma.sync kernel only")
         return reasons
 
     @classmethod
@@ -171,6 +203,11 @@ class FwOp(AttentionFwOpBase):
                 p.q_strides, p.k_strides, p.v_strides, p.o_strides = _strides4(q), _strides4(k), _strides4(v), _strides4(out)
                 if lse is not None:
                     p.lse_stride_b, p.lse_stride_g, p.lse_stride_h = lse.stride(0), lse.stride(1), lse.stride(2)
+                bt = _bias_tensor(bias)
+                if bt is not None:
+                    b5 = bt if bt.ndim == 5 else bt.unsqueeze(1)  # [B, G, H, Mq, Mkv]
+                    p.bias, p.bias_dtype = b5.data_ptr(), _DTYPE_CODE[b5.dtype]
+                    p.bias_stride_b, p.bias_stride_g, p.bias_stride_h, p.bias_stride_m = b5.stride(0), b5.stride(1), b5.stride(2), b5.stride(3)
                 p.mask_type, p.kv_offset, p.window_left = mask_type, kv_offset, window_left
                 p.scale = inp.scale_float
                 lib = _lib.load()
