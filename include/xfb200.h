@@ -244,6 +244,52 @@ typedef struct {
 
 XFB200_API int xfb200_merge_attentions(const xfb200_merge_params* p, void* stream);
 
+/* ------------------------------------------------------------ rope_padded
+ * Rotary embeddings and KV-cache emplacement for a concatenated batch whose
+ * caches are laid out as BlockDiagonalCausalWithOffsetPaddedKeysMask describes
+ * (xformers/ops/rope_padded.py:16-36, kernel semantics
+ * xformers/ops/_triton/rope_padded_kernels.py:13-229): for query token t of
+ * sequence b (the queries of a sequence are its LAST keys),
+ *   cache row = seqstart_k[b] + seqlen_k[b] - (seqstart_q[b+1] - t),
+ *   position  = seqpos[t], or row - seqstart_k[b] (+ first_seqpos[b]),
+ *   angle_j   = position * theta^(-2j/dim) / linear_scale   (optionally rescaled per wavelength),
+ * q rows are rotated into out_q, k rows rotated into cache_k[row], v rows copied
+ * into cache_v[row].  Pairs are (2j, 2j+1) when adjacents != 0, else (j, j + dim/2).
+ * Strides are in elements; every row has unit stride along dim. */
+typedef struct {
+  const void* xq;      /* [tokens, groups, q_heads, dim] */
+  const void* xk;      /* [tokens, groups, kv_heads, dim] */
+  const void* xv;      /* [tokens, groups, kv_heads, dim] */
+  void* out_q;         /* like xq */
+  void* cache_k;       /* [cache rows, groups, kv_heads, dim], modified in place */
+  void* cache_v;
+  const int32_t* seqstart_q; /* [batch + 1] */
+  const int32_t* seqstart_k; /* [batch + 1] */
+  const int32_t* seqlen_k;   /* [batch] */
+  const void* first_seqpos; /* NULL or [batch], int32 or int64 (seqpos_i64) */
+  const void* seqpos;       /* NULL or [tokens], int32 or int64 (seqpos_i64) */
+  int64_t seqpos_stride;    /* in elements, of whichever of the two is given */
+  int32_t dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32, of all six tensors */
+  int32_t batch;
+  int32_t max_q_per_seq;
+  int32_t q_heads, kv_heads, groups, dim;
+  int32_t adjacents;
+  int32_t use_dynamic_scaling;
+  int32_t internal_f64; /* angles in double precision */
+  int32_t seqpos_i64;   /* first_seqpos / seqpos hold int64 */
+  float theta, linear_scale;
+  float dynamic_old_context_len, dynamic_scale_factor, dynamic_low_freq_factor, dynamic_high_freq_factor;
+  int64_t xq_m, xq_g, xq_h;
+  int64_t xk_m, xk_g, xk_h;
+  int64_t xv_m, xv_g, xv_h;
+  int64_t oq_m, oq_g, oq_h;
+  int64_t ck_m, ck_g, ck_h;
+  int64_t cv_m, cv_g, cv_h;
+} xfb200_rope_params;
+
+XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);
+
+
 /* ---- misc ---------------------------------------------------------------------- */
 XFB200_API int xfb200_abi_version(void);
 XFB200_API const char* xfb200_last_error(void);

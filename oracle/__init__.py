@@ -38,3 +38,4 @@ from .fp8 import (  # noqa: F401
 from .paged import gather_paged, scatter_to_pages, physical_rows  # noqa: F401
 from .merge import merge_attentions_ref  # noqa: F401
 from .splitk import ref_attention_splitk  # noqa: F401
+from .rope import rope_frequencies, rope_rotate, rope_padded as rope_padded_ref  # noqa: F401

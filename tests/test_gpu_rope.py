@@ -1,0 +1,174 @@
+"""rope_padded on the GPU against the CPU oracle, in the shape of the
+reference's own tests (tests/test_rope_padded.py:155-344): ragged batches in a
+padded cache, 4-D and 5-D inputs, odd head sizes, both pair layouts, linear and
+wavelength-dependent scaling, shifted and explicit positions, and untouched
+cache rows staying bit-identical."""
+
+import pytest
+import torch
+
+import oracle
+from xformers_b200.ops import fmha, rope_padded
+
+pytestmark = pytest.mark.gpu
+
+# tolerances of tests/test_rope_padded.py:148-152, plus f16 (same mantissa class as its f32 atol)
+ATOL_RTOL = {torch.bfloat16: (5e-3, 8e-3), torch.float16: (5e-3, 1e-3), torch.float32: (5e-3, 1e-5)}
+
+
+def _case(q_seqlen, kv_seqlen, padding, *, heads=10, kv_heads=2, dim=128, groups=None, dtype=torch.bfloat16, seed=0,
+          expand_kv=False, cache_noise=True):
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    M, B = sum(q_seqlen), len(q_seqlen)
+    mid = () if groups is None else (groups,)
+    xq = torch.randn((1, M) + mid + (heads, dim), generator=g).to(dtype)
+    if expand_kv:
+        xk = torch.randn((1, M) + mid + (1, dim), generator=g).to(dtype).expand((1, M) + mid + (kv_heads, dim))
+        xv = torch.randn((1, M) + mid + (1, dim), generator=g).to(dtype).expand((1, M) + mid + (kv_heads, dim))
+        ck = torch.randn((1, B * padding) + mid + (1, dim), generator=g).to(dtype).expand((1, B * padding) + mid + (kv_heads, dim))
+        cv = torch.randn((1, B * padding) + mid + (1, dim), generator=g).to(dtype).expand((1, B * padding) + mid + (kv_heads, dim))
+    else:
+        xk = torch.randn((1, M) + mid + (kv_heads, dim), generator=g).to(dtype)
+        xv = torch.randn((1, M) + mid + (kv_heads, dim), generator=g).to(dtype)
+        shape = (1, B * padding) + mid + (kv_heads, dim)
+        ck = torch.randn(shape, generator=g).to(dtype) if cache_noise else torch.zeros(shape, dtype=dtype)
+        cv = torch.randn(shape, generator=g).to(dtype) if cache_noise else torch.zeros(shape, dtype=dtype)
+    bias = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(
+        q_seqlen=list(q_seqlen), kv_padding=padding, kv_seqlen=list(kv_seqlen))
+    return dict(xq=xq, xk=xk, xv=xv, ck=ck, cv=cv, bias=bias.to(dev), starts=[b * padding for b in range(B)], dev=dev)
+
+
+def _run_and_check(c, q_seqlen, kv_seqlen, *, first_seqpos=None, seqpos=None, internal_dtype="", tol=None, **kw):
+    dev = c["dev"]
+
+    def put(t):  # an expanded (stride 0) head axis stays expanded on the device
+        if t.stride(-2) == 0 and t.shape[-2] > 1:
+            return t[..., :1, :].to(dev).expand(t.shape)
+        return t.to(dev)
+
+    xq, xk, xv, ck, cv = (put(c[n]) for n in ("xq", "xk", "xv", "ck", "cv"))
+    fs = None if first_seqpos is None else torch.tensor(first_seqpos, device=dev)
+    sp = None if seqpos is None else torch.tensor(seqpos, device=dev)
+    out = rope_padded(xq, xk, xv, ck, cv, c["bias"], first_seqpos=fs, seqpos=sp, internal_dtype=internal_dtype, **kw)
+    want_q, want_k, want_v = oracle.rope_padded_ref(
+        c["xq"], c["xk"], c["xv"], c["ck"], c["cv"], q_seqlen, c["starts"], kv_seqlen, first_seqpos=first_seqpos, seqpos=seqpos, **kw)
+    atol, rtol = tol or ATOL_RTOL[xq.dtype]
+    torch.testing.assert_close(out.cpu().float(), want_q.float(), atol=atol, rtol=rtol)
+    torch.testing.assert_close(ck.cpu().float(), want_k.float(), atol=atol, rtol=rtol)
+    assert torch.equal(cv.cpu(), want_v)  # values are copied, untouched rows keep their bits
+    # rows that no token writes are bit-identical in cache_k as well
+    written = torch.zeros(c["ck"].shape[1], dtype=torch.bool)
+    for b, (ql, kl) in enumerate(zip(q_seqlen, kv_seqlen)):
+        written[c["starts"][b] + kl - ql: c["starts"][b] + kl] = True
+    assert torch.equal(ck.cpu()[0, ~written], c["ck"][0, ~written])
+    return out
+
+
+@pytest.mark.parametrize("adjacents", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("dim,padding", [(100, 87), (4098, 87), (128, 18300)])
+@pytest.mark.parametrize("groups", [None, 1, 3])
+def test_consistency(adjacents, dtype, dim, padding, groups):
+    # tests/test_rope_padded.py:155-283
+    nq = [2, 1, 1]
+    cache_lens = [27, padding - 5, padding // 2]
+    c = _case(nq, cache_lens, padding, dim=dim, groups=groups, dtype=dtype, seed=dim + padding)
+    _run_and_check(c, nq, cache_lens, adjacents=adjacents)
+
+
+@pytest.mark.parametrize("adjacents", [True, False])
+@pytest.mark.parametrize("kw", [
+    dict(linear_scale=4.0),
+    dict(theta=500000.0),
+    dict(use_dynamic_scaling=True),
+    dict(use_dynamic_scaling=True, theta=500000.0, dynamic_old_context_len=4096.0, dynamic_scale_factor=8.0,
+         dynamic_low_freq_factor=2.0, dynamic_high_freq_factor=16.0, linear_scale=2.0),
+])
+def test_scalings(adjacents, kw):
+    nq, cache_lens, padding = [2, 1, 1, 5], [27, 9000, 4500, 8192], 9001
+    c = _case(nq, cache_lens, padding, dim=128, dtype=torch.bfloat16, seed=7)
+    _run_and_check(c, nq, cache_lens, adjacents=adjacents, **kw)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("internal_dtype", ["", "f32", "f64"])
+def test_internal_dtype(dtype, internal_dtype):
+    nq, cache_lens, padding = [3, 1], [100000, 77777], 100000
+    c = _case(nq, cache_lens, padding, heads=4, kv_heads=1, dim=64, dtype=dtype, seed=3)
+    # float64 angles: only the final rounding differs; float32 angles at position 1e5 carry ~4e-3 of angle error
+    tol = ((1e-6, 1e-6) if dtype == torch.float32 else (1e-6, 8e-3)) if internal_dtype == "f64" else (2e-2, 8e-3)
+    _run_and_check(c, nq, cache_lens, internal_dtype=internal_dtype, tol=tol)
+
+
+@pytest.mark.parametrize("adjacents", [True, False])
+@pytest.mark.parametrize("seqlen", [1, 511, 2049])
+def test_prefill(adjacents, seqlen):
+    # tests/test_rope_padded.py:286-299: one sequence, cache length == query length
+    c = _case([seqlen], [seqlen], seqlen + 1, heads=4, kv_heads=2, dim=256, dtype=torch.float32, seed=seqlen)
+    _run_and_check(c, [seqlen], [seqlen], adjacents=adjacents)
+
+
+def test_positions():
+    # tests/test_rope_padded.py:302-344
+    seqlen = 512
+    c = _case([seqlen], [seqlen], seqlen, heads=2, kv_heads=2, dim=32, dtype=torch.float32, seed=1)
+    _run_and_check(c, [seqlen], [seqlen], first_seqpos=[4])
+    custom = list(range(seqlen))
+    custom[231], custom[423] = 934, 134
+    _run_and_check(c, [seqlen], [seqlen], seqpos=custom)
+    # int32 positions are accepted as well
+    dev = c["dev"]
+    ck, cv = c["ck"].to(dev), c["cv"].to(dev)
+    a = rope_padded(c["xq"].to(dev), c["xk"].to(dev), c["xv"].to(dev), ck, cv, c["bias"], seqpos=torch.tensor(custom, device=dev, dtype=torch.int32))
+    b = rope_padded(c["xq"].to(dev), c["xk"].to(dev), c["xv"].to(dev), ck, cv, c["bias"], seqpos=torch.tensor(custom, device=dev))
+    assert torch.equal(a, b)
+
+
+def test_ragged_batch_with_empty_sequence_and_out_q():
+    nq, cache_lens, padding = [4, 0, 1, 7], [4, 10, 33, 64], 64
+    c = _case(nq, cache_lens, padding, heads=8, kv_heads=8, dim=64, dtype=torch.bfloat16, seed=11)
+    out = _run_and_check(c, nq, cache_lens)
+    # out_q given (no-grad mode), with room between tokens: strided rows
+    dev = c["dev"]
+    wide = torch.zeros(1, sum(nq), 8, 96, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        got = rope_padded(c["xq"].to(dev), c["xk"].to(dev), c["xv"].to(dev), c["ck"].to(dev), c["cv"].to(dev), c["bias"], out_q=wide[..., :64])
+    assert got.data_ptr() == wide.data_ptr() and torch.equal(got, out) and not wide[..., 64:].any()
+
+
+def test_unaligned_rows_take_the_scalar_path():
+    nq, cache_lens, padding = [2, 3], [9, 3], 16
+    c = _case(nq, cache_lens, padding, heads=3, kv_heads=1, dim=64, dtype=torch.bfloat16, seed=5)
+    dev = c["dev"]
+    # rows that start one element off a 16-byte boundary
+    pad = torch.zeros(1, 5, 3, 65, dtype=torch.bfloat16, device=dev)
+    pad[..., 1:] = c["xq"].to(dev)
+    ck, cv = c["ck"].to(dev), c["cv"].to(dev)
+    got = rope_padded(pad[..., 1:], c["xk"].to(dev), c["xv"].to(dev), ck, cv, c["bias"])
+    want_q, want_k, _ = oracle.rope_padded_ref(c["xq"], c["xk"], c["xv"], c["ck"], c["cv"], nq, c["starts"], cache_lens)
+    torch.testing.assert_close(got.cpu().float(), want_q.float(), atol=5e-3, rtol=8e-3)
+    torch.testing.assert_close(ck.cpu().float(), want_k.float(), atol=5e-3, rtol=8e-3)
+
+
+def test_single_kv_head_given_expanded():
+    # xformers/ops/rope_padded.py:121-129: stride 0 over the kv heads means one real head
+    nq, cache_lens, padding = [1, 1, 2], [5, 40, 17], 40
+    c = _case(nq, cache_lens, padding, heads=8, kv_heads=4, dim=128, groups=2, dtype=torch.bfloat16, seed=13, expand_kv=True)
+    _run_and_check(c, nq, cache_lens)
+
+
+def test_feeds_decode_attention():
+    # the stated purpose (xformers/ops/rope_padded.py:47-53): out_q, cache_k, cache_v go straight into attention
+    nq, cache_lens, padding = [1, 1, 1], [100, 257, 31], 512
+    c = _case(nq, cache_lens, padding, heads=8, kv_heads=1, dim=128, dtype=torch.bfloat16, seed=17)
+    dev = c["dev"]
+    ck, cv = c["ck"].to(dev), c["cv"].to(dev)
+    out_q = rope_padded(c["xq"].to(dev), c["xk"].to(dev), c["xv"].to(dev), ck, cv, c["bias"])
+    attn = fmha.memory_efficient_attention_forward(out_q, ck.expand(-1, -1, 8, -1), cv.expand(-1, -1, 8, -1), c["bias"])
+    want_q, want_k, want_v = oracle.rope_padded_ref(c["xq"], c["xk"], c["xv"], c["ck"], c["cv"], nq, c["starts"], cache_lens)
+    for b in range(3):
+        kk = want_k[0, b * padding: b * padding + cache_lens[b], 0].float()
+        vv = want_v[0, b * padding: b * padding + cache_lens[b], 0].float()
+        p = torch.softmax(want_q[0, b].float() @ kk.T * 128**-0.5, -1)
+        torch.testing.assert_close(attn[0, b].cpu().float(), p @ vv, atol=2e-2, rtol=2e-2)

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "xfb200_decode_forward",
     "xfb200_decode_forward_static_scratch",
     "xfb200_merge_attentions",
+    "xfb200_rope_padded",
 )
 
 
@@ -162,6 +163,22 @@ class MergeParams(C.Structure):
     ]
 
 
+class RopeParams(C.Structure):
+    _fields_ = (
+        [(n, C.c_void_p) for n in ("xq", "xk", "xv", "out_q", "cache_k", "cache_v", "seqstart_q", "seqstart_k", "seqlen_k", "first_seqpos", "seqpos")]
+        + [("seqpos_stride", C.c_int64)]
+        + [
+            (n, C.c_int32)
+            for n in ("dtype", "batch", "max_q_per_seq", "q_heads", "kv_heads", "groups", "dim", "adjacents", "use_dynamic_scaling", "internal_f64", "seqpos_i64")
+        ]
+        + [
+            (n, C.c_float)
+            for n in ("theta", "linear_scale", "dynamic_old_context_len", "dynamic_scale_factor", "dynamic_low_freq_factor", "dynamic_high_freq_factor")
+        ]
+        + [(f"{t}_{a}", C.c_int64) for t in ("xq", "xk", "xv", "oq", "ck", "cv") for a in "mgh"]
+    )
+
+
 def library_path() -> Path:
     override = os.environ.get("XFB200_LIBRARY")
     if override:
@@ -203,6 +220,8 @@ def load() -> C.CDLL:
     lib.xfb200_decode_forward_static_scratch.restype = C.c_int
     lib.xfb200_merge_attentions.argtypes = [C.POINTER(MergeParams), C.c_void_p]
     lib.xfb200_merge_attentions.restype = C.c_int
+    lib.xfb200_rope_padded.argtypes = [C.POINTER(RopeParams), C.c_void_p]
+    lib.xfb200_rope_padded.restype = C.c_int
     if lib.xfb200_abi_version() != ABI_VERSION:
         raise RuntimeError(f"{path}: ABI version {lib.xfb200_abi_version()} != {ABI_VERSION}")
     _LIB = lib

@@ -26,6 +26,7 @@ SOURCES = [
     "prefill_sm100_m256.cu",
     "prefill_sm100_s64.cu",
     "prefill_api.cu",
+    "rope_padded.cu",
 ]
 HEADERS = ["internal.h", "ptx.cuh", "prefill_sm100.h", "../../include/xfb200.h"]
 NVCC_FLAGS = [

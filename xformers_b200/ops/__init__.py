@@ -2,6 +2,7 @@
 (xformers/ops/__init__.py:9-25)."""
 
 from . import fmha  # noqa: F401
+from .rope_padded import rope_padded  # noqa: F401
 from .fmha import (  # noqa: F401
     AttentionBias,
     AttentionOpBase,
