@@ -67,7 +67,7 @@ def _run_and_check(c, q_seqlen, kv_seqlen, *, first_seqpos=None, seqpos=None, in
 
 @pytest.mark.parametrize("adjacents", [True, False])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
-@pytest.mark.parametrize("dim,padding", [(100, 87), (4098, 87), (128, 18300)])
+@pytest.mark.parametrize("dim,padding", [(100, 87), (4098, 87), (128, 18300), (96, 87), (4096, 40)])
 @pytest.mark.parametrize("groups", [None, 1, 3])
 def test_consistency(adjacents, dtype, dim, padding, groups):
     # tests/test_rope_padded.py:155-283

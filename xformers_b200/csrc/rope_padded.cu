@@ -12,6 +12,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
+
 #include "internal.h"
 
 namespace xfb {
@@ -77,140 +79,163 @@ struct RopeVec {
   }
 };
 
-// source and destination of row `row` (q rows, then k rows, then v rows) of one token
+// source and destination of row `row` (q rows, then k rows, then v rows) of the
+// token at row `qpos` of the inputs and row `cache_pos` of the caches
 template <typename T>
 __device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, int qpos, int cache_pos, const T*& src, T*& dst, bool& rotate) {
-  const int head = row / p.groups, g = row - head * p.groups;
-  rotate = true;
-  if (head < p.q_heads) {
-    src = reinterpret_cast<const T*>(p.xq) + int64_t(qpos) * p.xq_m + int64_t(g) * p.xq_g + int64_t(head) * p.xq_h;
-    dst = reinterpret_cast<T*>(p.out_q) + int64_t(qpos) * p.oq_m + int64_t(g) * p.oq_g + int64_t(head) * p.oq_h;
-  } else if (head < p.q_heads + p.kv_heads) {
-    const int hk = head - p.q_heads;
-    src = reinterpret_cast<const T*>(p.xk) + int64_t(qpos) * p.xk_m + int64_t(g) * p.xk_g + int64_t(hk) * p.xk_h;
-    dst = reinterpret_cast<T*>(p.cache_k) + int64_t(cache_pos) * p.ck_m + int64_t(g) * p.ck_g + int64_t(hk) * p.ck_h;
-  } else {
-    const int hv = head - p.q_heads - p.kv_heads;
-    src = reinterpret_cast<const T*>(p.xv) + int64_t(qpos) * p.xv_m + int64_t(g) * p.xv_g + int64_t(hv) * p.xv_h;
-    dst = reinterpret_cast<T*>(p.cache_v) + int64_t(cache_pos) * p.cv_m + int64_t(g) * p.cv_g + int64_t(hv) * p.cv_h;
-    rotate = false;
-  }
+  int head = row, g = 0;
+  if (p.groups != 1) head = row / p.groups, g = row - head * p.groups;
+  const int kind = (head >= p.q_heads) + (head >= p.q_heads + p.kv_heads);  // 0 q, 1 k, 2 v
+  head -= kind == 0 ? 0 : (kind == 1 ? p.q_heads : p.q_heads + p.kv_heads);
+  const void* sbase = kind == 0 ? p.xq : (kind == 1 ? p.xk : p.xv);
+  void* dbase = kind == 0 ? p.out_q : (kind == 1 ? p.cache_k : p.cache_v);
+  const int64_t s_m = kind == 0 ? p.xq_m : (kind == 1 ? p.xk_m : p.xv_m);
+  const int64_t s_g = kind == 0 ? p.xq_g : (kind == 1 ? p.xk_g : p.xv_g);
+  const int64_t s_h = kind == 0 ? p.xq_h : (kind == 1 ? p.xk_h : p.xv_h);
+  const int64_t d_m = kind == 0 ? p.oq_m : (kind == 1 ? p.ck_m : p.cv_m);
+  const int64_t d_g = kind == 0 ? p.oq_g : (kind == 1 ? p.ck_g : p.cv_g);
+  const int64_t d_h = kind == 0 ? p.oq_h : (kind == 1 ? p.ck_h : p.cv_h);
+  src = reinterpret_cast<const T*>(sbase) + qpos * s_m + g * s_g + head * s_h;
+  dst = reinterpret_cast<T*>(dbase) + (kind == 0 ? qpos : cache_pos) * d_m + g * d_g + head * d_h;
+  rotate = kind != 2;
 }
 
-// kVec: every row starts on a 16-byte boundary and dim (dim / 2 for split halves)
-// is a whole number of 16-byte vectors.  Shared memory: the token's table of
-// (cos, sin) per pair, computed once and used by all of the token's rows.
-template <typename T, bool kF64, bool kVec>
-__global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel(const __grid_constant__ xfb200_rope_params p) {
+// kVec: every row starts on a 16-byte boundary and dim is a whole number of
+// pairs of 16-byte vectors.  A CTA owns up to p.tok_per_cta
+// consecutive tokens of one sequence, so the frequencies (a double-precision
+// power each) are formed once per CTA and the dependent loads of the sequence
+// bookkeeping are paid once.  Shared memory: (cos, sin) per (token, pair).
+template <typename T, bool kF64, bool kVec, bool kAdj>
+__global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel(const __grid_constant__ xfb200_rope_params p, const int tok_per_cta) {
   extern __shared__ float2 cs_table[];
-  // blockIdx.x = query inside the sequence, blockIdx.y = sequence
+  // blockIdx.x = group of queries inside the sequence, blockIdx.y = sequence
   const int b = blockIdx.y;
   const int q1 = p.seqstart_q[b + 1];
-  const int qpos = p.seqstart_q[b] + int(blockIdx.x);
-  if (qpos >= q1) return;
+  const int first = p.seqstart_q[b] + int(blockIdx.x) * tok_per_cta;
+  if (first >= q1) return;
+  const int ntok = min(tok_per_cta, q1 - first);
   const int cache_start = p.seqstart_k[b];
-  const int cache_pos = cache_start + p.seqlen_k[b] - (q1 - qpos);  // the queries are the last keys of the sequence
+  // the queries are the last keys of the sequence: token `first + t` goes to row cache_first + t
+  const int cache_first = cache_start + p.seqlen_k[b] - (q1 - first);
   auto position = [&](const void* base, int64_t i) -> long long {
     return p.seqpos_i64 ? reinterpret_cast<const long long*>(base)[i * p.seqpos_stride]
                         : reinterpret_cast<const int*>(base)[i * p.seqpos_stride];
   };
-  long long seq_pos;
-  if (p.seqpos != nullptr)
-    seq_pos = position(p.seqpos, qpos);
-  else
-    seq_pos = (cache_pos - cache_start) + (p.first_seqpos != nullptr ? position(p.first_seqpos, b) : 0);
+  const long long pos_first = (cache_first - cache_start) + (p.first_seqpos != nullptr ? position(p.first_seqpos, b) : 0);
 
   const int pairs = p.dim / 2;
   const int rows = (p.q_heads + 2 * p.kv_heads) * p.groups;
+  // The frequency and its product with the position are formed in double
+  // precision and reduced to [-pi, pi] there: the library is compiled with
+  // fast-math, whose single-precision power, sine and cosine are only good on
+  // a small range.  kF64 also takes the sine and cosine in double precision.
   for (int j = threadIdx.x; j < pairs; j += kRopeThreads) {
-    // The frequency and the product with the position are formed in double
-    // precision and reduced to [-pi, pi] there: the library is compiled with
-    // fast-math, whose single-precision power, sine and cosine are only good on
-    // a small range.  kF64 also takes the sine and cosine in double precision.
-    const double ang = double(seq_pos) * rope_freq<double>(p, j) / double(p.linear_scale);
-    float sn, cs;
-    if constexpr (kF64) {
-      sn = float(sin(ang)), cs = float(cos(ang));
-    } else {
-      const double two_pi = 6.283185307179586476925286766559;
-      const float r = float(ang - two_pi * rint(ang / two_pi));
-      __sincosf(r, &sn, &cs);
+    const double freq = rope_freq<double>(p, j) / double(p.linear_scale);
+    for (int t = 0; t < ntok; ++t) {
+      const long long seq_pos = p.seqpos != nullptr ? position(p.seqpos, first + t) : pos_first + t;
+      const double ang = double(seq_pos) * freq;
+      float sn, cs;
+      if constexpr (kF64) {
+        sn = float(sin(ang)), cs = float(cos(ang));
+      } else {
+        const double two_pi = 6.283185307179586476925286766559;
+        const float r = float(ang - two_pi * rint(ang * (1.0 / two_pi)));
+        __sincosf(r, &sn, &cs);
+      }
+      cs_table[t * pairs + j] = make_float2(cs, sn);
     }
-    cs_table[j] = make_float2(cs, sn);
   }
   __syncthreads();
 
   if constexpr (kVec) {
     constexpr int E = RopeVec<T>::kElems;
-    // an item is one vector of a row (adjacent pairs) or the two vectors holding
-    // E real parts and their E imaginary parts (split halves)
-    const int per_row = p.adjacents ? p.dim / E : pairs / E;
-    const int items = rows * per_row;
-    for (int it0 = threadIdx.x; it0 < items; it0 += kRopeThreads * kRopeUnroll) {
-      uint4 xw[kRopeUnroll], yw[kRopeUnroll];
-      T* dst[kRopeUnroll];
-      bool rot[kRopeUnroll];
-      int vec[kRopeUnroll];
+    // An item is E pairs of a row in two vectors, one in each half of the row:
+    // E/2 pairs each (adjacent pairs), or E real parts and their E imaginary
+    // parts (split halves).
+    // A thread keeps its column (item index inside the row) and walks down the
+    // rows of the CTA's tokens, `nslots` rows apart, (token, row) advanced
+    // without a division.
+        constexpr int kUnroll = 2;
+    const int per_row = pairs / E;
+    const int lanes = min(per_row, kRopeThreads);
+    const int nslots = kRopeThreads / lanes;
+    const int vx = threadIdx.x % lanes, slot = threadIdx.x / lanes;
+    if (slot >= nslots) return;
+    for (int v = vx; v < per_row; v += lanes) {
+      const int x_off = v * E, y_off = pairs + x_off;  // the same column of the row's two halves: both loads of a warp are contiguous
+      int t = 0, row = slot;
+      while (row >= rows) row -= rows, ++t;
+      while (t < ntok) {
+        uint4 xw[kUnroll], yw[kUnroll];
+        T* dst[kUnroll];
+        int tab[kUnroll];  // first (cos, sin) entry of the item, -1: copy only, -2: no item
 #pragma unroll
-      for (int u = 0; u < kRopeUnroll; ++u) {
-        const int it = it0 + u * kRopeThreads;
-        if (it < items) {
-          const int row = it / per_row;
-          vec[u] = it - row * per_row;
-          const T* src;
-          rope_row<T>(p, row, qpos, cache_pos, src, dst[u], rot[u]);
-          dst[u] += vec[u] * E;
-          xw[u] = RopeVec<T>::load(src + vec[u] * E);
-          if (!p.adjacents) yw[u] = RopeVec<T>::load(src + pairs + vec[u] * E);
+        for (int u = 0; u < kUnroll; ++u) {
+          tab[u] = -2;
+          if (t < ntok) {
+            const T* src;
+            bool rotate;
+            rope_row<T>(p, row, first + t, cache_first + t, src, dst[u], rotate);
+            dst[u] += x_off;
+            xw[u] = RopeVec<T>::load(src + x_off);
+            yw[u] = RopeVec<T>::load(src + y_off);
+            tab[u] = rotate ? t * pairs + (kAdj ? v * (E / 2) : v * E) : -1;
+            row += nslots;
+            while (row >= rows) row -= rows, ++t;
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < kRopeUnroll; ++u) {
-        const int it = it0 + u * kRopeThreads;
-        if (it < items) {
-          if (rot[u]) {
-            float x[E], y[E];
-            RopeVec<T>::unpack(xw[u], x);
-            if (p.adjacents) {
-#pragma unroll
-              for (int i = 0; i < E / 2; ++i) {
-                const float2 t = cs_table[vec[u] * (E / 2) + i];
-                const float re = x[2 * i], im = x[2 * i + 1];
-                x[2 * i] = re * t.x - im * t.y;
-                x[2 * i + 1] = im * t.x + re * t.y;
-              }
-            } else {
+        for (int u = 0; u < kUnroll; ++u) {
+          if (tab[u] != -2) {
+            if (tab[u] >= 0) {
+              float x[E], y[E];
+              RopeVec<T>::unpack(xw[u], x);
               RopeVec<T>::unpack(yw[u], y);
+              if constexpr (kAdj) {
 #pragma unroll
-              for (int i = 0; i < E; ++i) {
-                const float2 t = cs_table[vec[u] * E + i];
-                const float re = x[i], im = y[i];
-                x[i] = re * t.x - im * t.y;
-                y[i] = im * t.x + re * t.y;
+                for (int i = 0; i < E / 2; ++i) {
+                  const float2 w = cs_table[tab[u] + i], z = cs_table[tab[u] + pairs / 2 + i];
+                  const float re = x[2 * i], im = x[2 * i + 1];
+                  x[2 * i] = re * w.x - im * w.y;
+                  x[2 * i + 1] = im * w.x + re * w.y;
+                  const float re2 = y[2 * i], im2 = y[2 * i + 1];
+                  y[2 * i] = re2 * z.x - im2 * z.y;
+                  y[2 * i + 1] = im2 * z.x + re2 * z.y;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                  const float2 w = cs_table[tab[u] + i];
+                  const float re = x[i], im = y[i];
+                  x[i] = re * w.x - im * w.y;
+                  y[i] = im * w.x + re * w.y;
+                }
               }
+              xw[u] = RopeVec<T>::pack(x);
               yw[u] = RopeVec<T>::pack(y);
             }
-            xw[u] = RopeVec<T>::pack(x);
+            RopeVec<T>::store(dst[u], xw[u]);
+            RopeVec<T>::store(dst[u] + (y_off - x_off), yw[u]);
           }
-          RopeVec<T>::store(dst[u], xw[u]);
-          if (!p.adjacents) RopeVec<T>::store(dst[u] + pairs, yw[u]);
         }
       }
     }
   } else {
-    const int items = rows * pairs;
+    const int per_tok = rows * pairs;
+    const int items = ntok * per_tok;
     for (int it = threadIdx.x; it < items; it += kRopeThreads) {
-      const int row = it / pairs, j = it - row * pairs;
+      const int t = it / per_tok, rem = it - t * per_tok;
+      const int row = rem / pairs, j = rem - row * pairs;
       const T* src;
       T* dst;
       bool rotate;
-      rope_row<T>(p, row, qpos, cache_pos, src, dst, rotate);
-      const int c_re = p.adjacents ? 2 * j : j;
-      const int c_im = p.adjacents ? 2 * j + 1 : j + pairs;
-      const float2 t = cs_table[j];
+      rope_row<T>(p, row, first + t, cache_first + t, src, dst, rotate);
+      const int c_re = kAdj ? 2 * j : j;
+      const int c_im = kAdj ? 2 * j + 1 : j + pairs;
+      const float2 w = cs_table[t * pairs + j];
       const float re = RopeIo<T>::ld(src + c_re), im = RopeIo<T>::ld(src + c_im);
-      RopeIo<T>::st(dst + c_re, rotate ? re * t.x - im * t.y : re);
-      RopeIo<T>::st(dst + c_im, rotate ? im * t.x + re * t.y : im);
+      RopeIo<T>::st(dst + c_re, rotate ? re * w.x - im * w.y : re);
+      RopeIo<T>::st(dst + c_im, rotate ? im * w.x + re * w.y : im);
     }
   }
 }
@@ -221,22 +246,35 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
   auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
   const int64_t strides[] = {p.xq_m, p.xq_g, p.xq_h, p.xk_m, p.xk_g, p.xk_h, p.xv_m, p.xv_g, p.xv_h,
                              p.oq_m, p.oq_g, p.oq_h, p.ck_m, p.ck_g, p.ck_h, p.cv_m, p.cv_g, p.cv_h};
-  bool vec = (p.adjacents ? p.dim % E == 0 : (p.dim / 2) % E == 0) && aligned(p.xq) && aligned(p.xk) && aligned(p.xv) &&
+  bool vec = p.dim % (2 * E) == 0 && aligned(p.xq) && aligned(p.xk) && aligned(p.xv) &&
              aligned(p.out_q) && aligned(p.cache_k) && aligned(p.cache_v);
   for (int64_t s : strides) vec = vec && s % E == 0;
-  const size_t smem = size_t(p.dim / 2) * sizeof(float2);
+  const int pairs = p.dim / 2;
+  // Tokens per CTA: about 128 KB of rows, while the (cos, sin) table stays within
+  // 16 KB and the grid keeps a few CTAs per SM slot.
+  const int64_t tok_bytes = int64_t(p.q_heads + 2 * p.kv_heads) * p.groups * p.dim * int64_t(sizeof(T));
+  const int64_t by_grid = int64_t(p.max_q_per_seq) * p.batch / (int64_t(sm_count()) * 16);
+  const int tok_per_cta = int(std::max<int64_t>(1, std::min<int64_t>({(128 * 1024 + tok_bytes - 1) / tok_bytes, 2048 / pairs, p.max_q_per_seq, by_grid})));
+  const size_t smem = size_t(tok_per_cta) * pairs * sizeof(float2);
   if (smem > 200 * 1024) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: dim %d too large", p.dim);
-  dim3 grid(unsigned(p.max_q_per_seq), unsigned(p.batch), 1);
+  dim3 grid(unsigned((p.max_q_per_seq + tok_per_cta - 1) / tok_per_cta), unsigned(p.batch), 1);
   auto go = [&](auto kernel) -> int {
     if (smem > 48 * 1024) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
       if (e != cudaSuccess) return cuda_fail("rope_padded: shared memory", e);
     }
-    kernel<<<grid, kRopeThreads, smem, st>>>(p);
+    kernel<<<grid, kRopeThreads, smem, st>>>(p, tok_per_cta);
     return check_launch("rope_padded_kernel");
   };
-  if (p.internal_f64) return vec ? go(rope_padded_kernel<T, true, true>) : go(rope_padded_kernel<T, true, false>);
-  return vec ? go(rope_padded_kernel<T, false, true>) : go(rope_padded_kernel<T, false, false>);
+#define XFB_ROPE(F64, VEC)                                                                   \
+  return p.adjacents ? go(rope_padded_kernel<T, F64, VEC, true>) : go(rope_padded_kernel<T, F64, VEC, false>)
+  if (p.internal_f64) {
+    if (vec) XFB_ROPE(true, true);
+    XFB_ROPE(true, false);
+  }
+  if (vec) XFB_ROPE(false, true);
+  XFB_ROPE(false, false);
+#undef XFB_ROPE
 }
 
 }  // namespace xfb
