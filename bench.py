@@ -57,7 +57,7 @@ CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 # under profiles/: bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
 NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
-               "decode_fp8": (613.01e6 + 14.01e6) / 505.51e6}
+               "decode_fp8": (613.01e6 + 14.01e6) / 505.51e6, "rope": (100.70e6 + 55.24e6) / 201.33e6}
 
 
 def causal_flops(B, M, H, D):
@@ -304,7 +304,7 @@ def main():
     ap.add_argument("--skip-extras", action="store_true", help="headline only (no decode / varlen / long-context / CPU legs)")
     ap.add_argument("--e2e-mode", default="pipelined", choices=["pipelined", "serial"],
                     help="e2e leg: overlap upload / kernel / read-back of neighbouring steps, or run them back to back")
-    ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,decode_fp8,varlen,long,cpu")
+    ap.add_argument("--only", default="", help="comma list of legs to run: prefill,e2e,decode_bf16,decode_int4,decode_fp8,rope,varlen,long,cpu")
     ap.add_argument("--small", action="store_true",
                     help="profiling case: one batch of the headline configuration (128 MB of tensors, still larger than L2) and 16 decode sequences; not a bench value")
     args = ap.parse_args()
@@ -329,7 +329,7 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "decode_fp8", "varlen", "long", "cpu"}
+    legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "decode_fp8", "rope", "varlen", "long", "cpu"}
     if args.skip_extras:
         legs &= {"prefill", "e2e"}
     peaks = load_peaks()
@@ -481,6 +481,35 @@ def main():
                                                "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 16-sequence case)", "of": peaks["source"]},
                                   "workload": "as decode_bf16 with a row-wise fp8 cache (128 B + one scale/shift word per token and head)"}
         del dq, dk, dv, dbias, kss, vss, inp
+        torch.cuda.empty_cache()
+    barrier()
+
+    # ------------------------------ rope_padded: prefill into a padded cache (rank 0)
+    if "rope" in legs and rank == 0:
+        r_seqs, r_len, r_hq, r_hkv, r_pad = (2, 4096, 32, 8, 4160) if args.small else (8, 4096, 32, 8, 4160)
+        gd = torch.Generator(device=dev).manual_seed(0)
+        rq = torch.randn(1, r_seqs * r_len, r_hq, 128, generator=gd, device=dev, dtype=torch.bfloat16)
+        rk = torch.randn(1, r_seqs * r_len, r_hkv, 128, generator=gd, device=dev, dtype=torch.bfloat16)
+        rv = torch.randn(1, r_seqs * r_len, r_hkv, 128, generator=gd, device=dev, dtype=torch.bfloat16)
+        rck = torch.zeros(1, r_seqs * r_pad, r_hkv, 128, device=dev, dtype=torch.bfloat16)
+        rcv = torch.zeros_like(rck)
+        rout = torch.empty_like(rq)
+        rbias = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=[r_len] * r_seqs, kv_padding=r_pad, kv_seqlen=[r_len + 17] * r_seqs).to(dev)
+
+        def rope_step():
+            with torch.no_grad():
+                xops.rope_padded(rq, rk, rv, rck, rcv, rbias, out_q=rout)
+
+        r_steps = max(5, min(args.steps, 30))
+        ms, win = event_time_ms(rope_step, r_steps, 3)
+        windows.append(win)
+        rbytes = 2 * rq.numel() * 2 + 2 * (rk.numel() + rv.numel()) * 2  # every row read once and written once
+        gbs = rbytes / (ms / r_steps * 1e-3) / 1e9
+        out_line["rope_padded"] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / r_steps, "bytes_per_step": rbytes,
+                                   "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                                                "traffic": NCU_TRAFFIC["rope"] * rbytes, "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 2-sequence case)", "of": peaks["source"]},
+                                   "workload": f"{r_seqs} seqs x {r_len} new tokens into slots of {r_pad} rows, Hq={r_hq} Hkv={r_hkv} D=128 bf16, adjacent pairs; {rbytes >> 20} MiB per step, larger than L2"}
+        del rq, rk, rv, rck, rcv, rout
         torch.cuda.empty_cache()
     barrier()
 
