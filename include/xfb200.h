@@ -285,6 +285,14 @@ typedef struct {
   int64_t oq_m, oq_g, oq_h;
   int64_t ck_m, ck_g, ck_h;
   int64_t cv_m, cv_g, cv_h;
+  /* Paged caches (an extension: the reference's rope_padded writes flat caches only).  NULL, or
+   * [batch, pages per sequence]: key t of sequence b lives in row
+   * block_tables[b, t / page_size] * page_size + t % page_size of cache_k / cache_v, and
+   * seqstart_k is not used for addressing. */
+  const int32_t* block_tables;
+  int64_t block_tables_stride; /* elements between the rows of two sequences */
+  int32_t page_size;
+  int32_t reserved;
 } xfb200_rope_params;
 
 XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);

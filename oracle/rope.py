@@ -80,24 +80,29 @@ def rope_padded(
     seqpos: Optional[Sequence[int]] = None,
     linear_scale: float = 1.0,
     adjacents: bool = True,
+    block_tables: Optional[Sequence[Sequence[int]]] = None,
+    page_size: int = 0,
     **freq_kwargs,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """``xq/xk/xv [1, M, (G,) H, dim]``, caches ``[1, rows, (G,) Hkv, dim]``.
     Returns (out_q, new cache_k, new cache_v); the inputs are not modified.
     The queries of sequence b are its last ``q_seqlen[b]`` keys: token i of them
-    goes to cache row ``kv_seqstart[b] + kv_seqlen[b] - q_seqlen[b] + i``."""
+    goes to cache row ``kv_seqstart[b] + kv_seqlen[b] - q_seqlen[b] + i``; with
+    ``block_tables`` key t of sequence b is instead row
+    ``block_tables[b][t // page_size] * page_size + t % page_size`` of a page pool
+    (the paged layout of oracle/paged.py)."""
     assert first_seqpos is None or seqpos is None
     freqs = rope_frequencies(xq.shape[-1], **freq_kwargs)
     rows, pos = [], []
     t = 0
     for b, (ql, ks, kl) in enumerate(zip(q_seqlen, kv_seqstart, kv_seqlen)):
         for i in range(ql):
-            row = ks + kl - ql + i
-            rows.append(row)
+            key = kl - ql + i
+            rows.append(ks + key if block_tables is None else int(block_tables[b][key // page_size]) * page_size + key % page_size)
             if seqpos is not None:
                 pos.append(int(seqpos[t]))
             else:
-                pos.append(row - ks + (int(first_seqpos[b]) if first_seqpos is not None else 0))
+                pos.append(key + (int(first_seqpos[b]) if first_seqpos is not None else 0))
             t += 1
     assert t == xq.shape[1]
     rows_t, pos_t = torch.tensor(rows, dtype=torch.long), torch.tensor(pos, dtype=torch.long)

@@ -172,3 +172,43 @@ def test_feeds_decode_attention():
         vv = want_v[0, b * padding: b * padding + cache_lens[b], 0].float()
         p = torch.softmax(want_q[0, b].float() @ kk.T * 128**-0.5, -1)
         torch.testing.assert_close(attn[0, b].cpu().float(), p @ vv, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("page_size", [16, 256])
+@pytest.mark.parametrize("groups", [None, 2])
+def test_paged_cache(page_size, groups):
+    # beyond the reference: the caches are page pools reached through block_tables
+    nq, cache_lens = [5, 1, 40, 1], [21, 300, 40, 1]
+    max_pages = (max(cache_lens) + page_size - 1) // page_size
+    B = len(nq)
+    g = torch.Generator().manual_seed(page_size)
+    tables = torch.randperm(B * max_pages + 3, generator=g)[: B * max_pages].int().view(B, max_pages)
+    pool_rows = (B * max_pages + 3) * page_size
+    dev = torch.device("cuda")
+    mid = () if groups is None else (groups,)
+    M, Hq, Hkv, D = sum(nq), 8, 2, 128
+    xq = torch.randn((1, M) + mid + (Hq, D), generator=g).bfloat16()
+    xk = torch.randn((1, M) + mid + (Hkv, D), generator=g).bfloat16()
+    xv = torch.randn((1, M) + mid + (Hkv, D), generator=g).bfloat16()
+    ck = torch.randn((1, pool_rows) + mid + (Hkv, D), generator=g).bfloat16()
+    cv = torch.randn((1, pool_rows) + mid + (Hkv, D), generator=g).bfloat16()
+    bias = fmha.attn_bias.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(nq, cache_lens, tables, page_size).to(dev)
+    ckd, cvd = ck.to(dev), cv.to(dev)
+    out = rope_padded(xq.to(dev), xk.to(dev), xv.to(dev), ckd, cvd, bias)
+    want_q, want_k, want_v = oracle.rope_padded_ref(xq, xk, xv, ck, cv, nq, [0] * B, cache_lens, block_tables=tables.tolist(), page_size=page_size)
+    torch.testing.assert_close(out.cpu().float(), want_q.float(), atol=5e-3, rtol=8e-3)
+    torch.testing.assert_close(ckd.cpu().float(), want_k.float(), atol=5e-3, rtol=8e-3)
+    assert torch.equal(cvd.cpu(), want_v)
+    changed = (ckd.cpu() != ck).flatten(2).any(-1)[0]
+    assert int(changed.sum()) <= M  # only the rows of the new tokens were touched
+    if groups is None:
+        # and the paged decode operator reads what was written: last query of each sequence
+        qlast = out[:, [4, 5, 45, 46]].reshape(1, B, Hkv, Hq // Hkv, D)
+        dbias = fmha.attn_bias.PagedBlockDiagonalPaddedKeysMask.from_seqlens([1] * B, cache_lens, tables, page_size).to(dev)
+        attn = fmha.memory_efficient_attention_forward(
+            qlast, ckd.unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1), cvd.unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1), dbias,
+            op=fmha.triton_splitk.FwOp)
+        ref, _ = oracle.ref_attention_with_lse(
+            qlast.float().cpu(), want_k.float().unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1),
+            want_v.float().unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1), dbias.to("cpu"))
+        torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)

@@ -88,3 +88,21 @@ def test_cache_rows_and_positions():
     assert torch.equal(nk2[0, untouched], ck[0, untouched])
     oq3, _, _ = oracle.rope_padded_ref(xq, xk, xv, ck, cv, q_seqlen, starts, kv_seqlen, seqpos=[9, 8, 7, 6, 5, 4])
     torch.testing.assert_close(oq3[0], rope_rotate(xq[0], torch.tensor([9, 8, 7, 6, 5, 4]), f))
+
+
+def test_paged_rows():
+    # key t of sequence b -> row block_tables[b][t // page] * page + t % page
+    q_seqlen, kv_seqlen, page = [3, 1], [6, 9], 4
+    tables = [[5, 2, 0], [1, 3, 4]]
+    g = torch.Generator().manual_seed(1)
+    xq, xk, xv = (torch.randn(1, 4, 2, 8, generator=g) for _ in range(3))
+    ck, cv = torch.randn(1, 24, 2, 8, generator=g), torch.randn(1, 24, 2, 8, generator=g)
+    oq, nk, nv = oracle.rope_padded_ref(xq, xk, xv, ck, cv, q_seqlen, [0, 0], kv_seqlen, block_tables=tables, page_size=page)
+    rows = [5 * 4 + 3, 2 * 4 + 0, 2 * 4 + 1, 4 * 4 + 0]  # keys 3, 4, 5 of sequence 0; key 8 of sequence 1
+    pos = torch.tensor([3, 4, 5, 8])
+    f = rope_frequencies(8)
+    torch.testing.assert_close(nk[0, rows], rope_rotate(xk[0], pos, f))
+    assert torch.equal(nv[0, rows], xv[0])
+    untouched = [r for r in range(24) if r not in rows]
+    assert torch.equal(nk[0, untouched], ck[0, untouched]) and torch.equal(nv[0, untouched], cv[0, untouched])
+    torch.testing.assert_close(oq[0], rope_rotate(xq[0], pos, f))

@@ -57,6 +57,7 @@ __device__ __forceinline__ F rope_freq(const xfb200_rope_params& p, int j) {
 }
 
 constexpr int kRopeThreads = 256;
+constexpr int kRopeMaxTok = 64;  // most tokens one CTA takes
 constexpr int kRopeUnroll = 4;
 
 // 16-byte vectors of T, kept as raw words between the load and the arithmetic
@@ -108,6 +109,7 @@ __device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, i
 template <typename T, bool kF64, bool kVec, bool kAdj>
 __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel(const __grid_constant__ xfb200_rope_params p, const int tok_per_cta) {
   extern __shared__ float2 cs_table[];
+  __shared__ int cache_rows[kRopeMaxTok];  // cache row of each of the CTA's tokens
   // blockIdx.x = group of queries inside the sequence, blockIdx.y = sequence
   const int b = blockIdx.y;
   const int q1 = p.seqstart_q[b + 1];
@@ -115,13 +117,20 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
   if (first >= q1) return;
   const int ntok = min(tok_per_cta, q1 - first);
   const int cache_start = p.seqstart_k[b];
-  // the queries are the last keys of the sequence: token `first + t` goes to row cache_first + t
-  const int cache_first = cache_start + p.seqlen_k[b] - (q1 - first);
+  // the queries are the last keys of the sequence: token `first + t` is key slot_first + t of its slot,
+  // which is row cache_start + slot_first + t of a flat cache, or goes through the page table
+  const int slot_first = p.seqlen_k[b] - (q1 - first);
+  if (int(threadIdx.x) < ntok) {
+    const int pos = slot_first + int(threadIdx.x);
+    cache_rows[threadIdx.x] = p.block_tables != nullptr
+                                  ? p.block_tables[int64_t(b) * p.block_tables_stride + pos / p.page_size] * p.page_size + pos % p.page_size
+                                  : cache_start + pos;
+  }
   auto position = [&](const void* base, int64_t i) -> long long {
     return p.seqpos_i64 ? reinterpret_cast<const long long*>(base)[i * p.seqpos_stride]
                         : reinterpret_cast<const int*>(base)[i * p.seqpos_stride];
   };
-  const long long pos_first = (cache_first - cache_start) + (p.first_seqpos != nullptr ? position(p.first_seqpos, b) : 0);
+  const long long pos_first = slot_first + (p.first_seqpos != nullptr ? position(p.first_seqpos, b) : 0);
 
   const int pairs = p.dim / 2;
   const int rows = (p.q_heads + 2 * p.kv_heads) * p.groups;
@@ -175,7 +184,7 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
           if (t < ntok) {
             const T* src;
             bool rotate;
-            rope_row<T>(p, row, first + t, cache_first + t, src, dst[u], rotate);
+            rope_row<T>(p, row, first + t, cache_rows[t], src, dst[u], rotate);
             dst[u] += x_off;
             xw[u] = RopeVec<T>::load(src + x_off);
             yw[u] = RopeVec<T>::load(src + y_off);
@@ -229,7 +238,7 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
       const T* src;
       T* dst;
       bool rotate;
-      rope_row<T>(p, row, first + t, cache_first + t, src, dst, rotate);
+      rope_row<T>(p, row, first + t, cache_rows[t], src, dst, rotate);
       const int c_re = kAdj ? 2 * j : j;
       const int c_im = kAdj ? 2 * j + 1 : j + pairs;
       const float2 w = cs_table[t * pairs + j];
@@ -254,7 +263,7 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
   // 16 KB and the grid keeps a few CTAs per SM slot.
   const int64_t tok_bytes = int64_t(p.q_heads + 2 * p.kv_heads) * p.groups * p.dim * int64_t(sizeof(T));
   const int64_t by_grid = int64_t(p.max_q_per_seq) * p.batch / (int64_t(sm_count()) * 16);
-  const int tok_per_cta = int(std::max<int64_t>(1, std::min<int64_t>({(128 * 1024 + tok_bytes - 1) / tok_bytes, 2048 / pairs, p.max_q_per_seq, by_grid})));
+  const int tok_per_cta = int(std::max<int64_t>(1, std::min<int64_t>({(128 * 1024 + tok_bytes - 1) / tok_bytes, 2048 / pairs, p.max_q_per_seq, by_grid, kRopeMaxTok})));
   const size_t smem = size_t(tok_per_cta) * pairs * sizeof(float2);
   if (smem > 200 * 1024) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: dim %d too large", p.dim);
   dim3 grid(unsigned((p.max_q_per_seq + tok_per_cta - 1) / tok_per_cta), unsigned(p.batch), 1);
@@ -289,6 +298,7 @@ extern "C" int xfb200_rope_padded(const xfb200_rope_params* p, void* stream) {
   if (!p->xq || !p->xk || !p->xv || !p->out_q || !p->cache_k || !p->cache_v || !p->seqstart_q || !p->seqstart_k || !p->seqlen_k)
     return set_error(XFB200_E_INVALID, "rope_padded: null tensor pointer");
   if (p->first_seqpos != nullptr && p->seqpos != nullptr) return set_error(XFB200_E_INVALID, "rope_padded: seqpos and first_seqpos may not both be given");
+  if (p->block_tables != nullptr && p->page_size < 1) return set_error(XFB200_E_INVALID, "rope_padded: page_size %d with a page table", p->page_size);
   if (!(p->linear_scale != 0.f)) return set_error(XFB200_E_INVALID, "rope_padded: linear_scale must not be 0");
   if (p->batch > 65535) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: more than 65535 sequences");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

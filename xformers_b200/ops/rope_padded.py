@@ -8,12 +8,12 @@ this function."""
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Tuple
+from typing import Optional, Tuple, Union
 
 import torch
 
 from .. import _lib
-from .fmha.attn_bias import BlockDiagonalCausalWithOffsetPaddedKeysMask
+from .fmha.attn_bias import BlockDiagonalCausalWithOffsetPaddedKeysMask, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask
 
 _DTYPES = {torch.bfloat16: _lib.BF16, torch.float16: _lib.F16, torch.float32: _lib.F32}
 
@@ -30,7 +30,7 @@ def rope_padded(
     xv: torch.Tensor,
     cache_k: torch.Tensor,
     cache_v: torch.Tensor,
-    attn_bias: BlockDiagonalCausalWithOffsetPaddedKeysMask,
+    attn_bias: Union[BlockDiagonalCausalWithOffsetPaddedKeysMask, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask],
     *,
     theta: float = 10000.0,
     linear_scale: float = 1.0,
@@ -59,13 +59,24 @@ def rope_padded(
     ``linear_scale`` divides positions; ``use_dynamic_scaling`` rescales
     frequencies per wavelength; ``internal_dtype`` "" / "f32" computes angles in
     float32, "f64" in float64.  Errors follow xformers/ops/rope_padded.py:97-233.
+
+    Beyond the reference: with a ``PagedBlockDiagonalCausalWithOffsetPaddedKeysMask``
+    the caches are page pools ``[1, pages * page_size, (G,) Hkv, D]`` and key t of
+    sequence b is written to row ``block_tables[b, t // page_size] * page_size +
+    t % page_size``, the layout the paged decode operator reads.
     """
     if torch.is_grad_enabled() and (
         xq.requires_grad or xk.requires_grad or xv.requires_grad or cache_k.requires_grad or cache_v.requires_grad or out_q is not None
     ):
         raise ValueError("Gradients not supported.")
     n_total_queries = attn_bias.q_seqinfo.seqstart_py[-1]
-    cache_length = attn_bias.k_seqinfo.seqstart_py[-1]
+    paged = isinstance(attn_bias, PagedBlockDiagonalCausalWithOffsetPaddedKeysMask)
+    if paged:
+        if cache_k.ndim < 2 or cache_k.shape[1] % attn_bias.page_size:
+            raise ValueError(f"unexpected cache_k shape {tuple(cache_k.shape)}: rows must be a whole number of pages of {attn_bias.page_size}")
+        cache_length = cache_k.shape[1]
+    else:
+        cache_length = attn_bias.k_seqinfo.seqstart_py[-1]
     ndim = xq.ndim
     if ndim not in [4, 5]:
         raise ValueError("Unexpected xq dimension")
@@ -154,6 +165,11 @@ def rope_padded(
     p.oq_m, p.oq_g, p.oq_h = _strides3(out_q, ndim)
     p.ck_m, p.ck_g, p.ck_h = _strides3(cache_k, ndim)
     p.cv_m, p.cv_g, p.cv_h = _strides3(cache_v, ndim)
+    if paged:
+        tables = attn_bias.block_tables
+        if tables.device != device or tables.dtype != torch.int32 or tables.ndim != 2 or tables.shape[0] != logical_bsz or tables.stride(1) != 1:
+            raise ValueError("`attn_bias.block_tables` must be an int32 [batch, pages] tensor with unit inner stride on the same device as the other inputs")
+        p.block_tables, p.block_tables_stride, p.page_size = tables.data_ptr(), tables.stride(0), attn_bias.page_size
     with torch.cuda.device(device):
         rc = _lib.load().xfb200_rope_padded(C.byref(p), C.c_void_p(torch.cuda.current_stream(device).cuda_stream))
     _lib.check(rc, "rope_padded")
