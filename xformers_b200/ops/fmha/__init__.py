@@ -148,3 +148,6 @@ def memory_efficient_attention(*args, **kwargs):
         "memory_efficient_attention with autograd (backward pass) is outside this library; "
         "use memory_efficient_attention_forward"
     )
+
+
+from . import torch_library  # noqa: E402,F401  (defines torch.ops.xformers_b200.memory_efficient_attention_forward[_with_bias])
