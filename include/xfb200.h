@@ -163,7 +163,11 @@ typedef struct {
   int32_t mask_type; /* NONE or CAUSAL_BOTTOM_RIGHT (w.r.t. seqlen_k[b]) */
   float scale;
   int32_t out_dtype;
-  int32_t reserved;
+  /* XFB200_KV_FP8_ROWWISE: number of consecutive int32 that may be read at every (token, kv head)
+   * entry of k_scale_shift / v_scale_shift, the word itself first (the reference's helper lays the
+   * word out once per query head of the group, tests/utils.py:175-188).  0 or 1: only the word.
+   * With 4 or more the kernel fetches the words with tiled copies.  Other formats: 0. */
+  int32_t ss_words;
   /* XFB200_KV_FP8_ROWWISE only (xformers/ops/fmha/triton_splitk.py:28, InputsFp8; tests/utils.py:311-340):
    * k/v are int32 words of four e4m3 values, x = fp8 * scale + shift with one
    * (fp16 scale | fp16 shift << 16) word per token and kv head; strides in words. */

@@ -129,3 +129,27 @@ def test_fp8_nan_bytes_in_padding_do_not_leak():
     out1, lse1 = run(kw2, vw2, kss2, vss2)
     assert not out1.isnan().any() and not lse1.isnan().any()
     assert torch.equal(out0, out1) and torch.equal(lse0, lse1)
+
+
+@gpu
+@pytest.mark.parametrize("Hkv,G", [(2, 8), (1, 4), (8, 2)])
+def test_scale_shift_layouts_agree(Hkv, G):
+    """The scale/shift words may be laid out once per query head of the group
+    (tests/utils.py:175-188; fetched by tiled copies when a group has at least 4
+    heads) or given expanded with stride 0 (fetched word by word): same bits out."""
+    require_cuda()
+    B, Mkv = 3, 512
+    q, kw, vw, kss, vss, _, _ = _fp8_case(B, Mkv, Hkv, G, torch.bfloat16, seed=9)
+    lens = [512, 77, 300]
+    bias = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=[1] * B, kv_seqlen=lens, kv_padding=Mkv, device="cuda")
+    outs = []
+    for contiguous in (True, False):
+        ks, vs = _expand(kss.cuda(), G), _expand(vss.cuda(), G)
+        if contiguous:
+            ks, vs = ks.contiguous(), vs.contiguous()
+        assert (ks.stride(3) == 1) == contiguous or G == 1
+        inp = S.InputsFp8(query=q.cuda(), key=_expand(kw.cuda(), G), value=_expand(vw.cuda(), G), attn_bias=bias,
+                          k_fp8_scale_shift=ks, v_fp8_scale_shift=vs)
+        out, ctx = fmha._memory_efficient_attention_forward_requires_grad(inp, op=S.FwOp)
+        outs.append((out, ctx.lse))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])

@@ -122,7 +122,7 @@ class DecodeParams(C.Structure):
         ("mask_type", C.c_int32),
         ("scale", C.c_float),
         ("out_dtype", C.c_int32),
-        ("reserved", C.c_int32),
+        ("ss_words", C.c_int32),
         ("k_scale_shift", C.c_void_p),
         ("v_scale_shift", C.c_void_p),
         ("ks_stride_m", C.c_int64),

@@ -33,6 +33,8 @@ constexpr int kDecChunkAlign = 128;  // chunk size granularity in tokens (= larg
 struct DecodeArgs {
   // copy_mode 3 only: the K and V caches as 3-D tensors {64 elements, token rows, 128-byte column groups}
   CUtensorMap tm_k, tm_v;
+  // fp8 with ss_tma: the scale/shift words as 3-D int32 tensors {4 words, kv heads, token rows}
+  CUtensorMap tm_kss, tm_vss;
   const void* q;
   const void* k;
   const void* v;
@@ -58,6 +60,8 @@ struct DecodeArgs {
   const int32_t* k_ss; // fp8: scale/shift words of K and V, strides in words
   const int32_t* v_ss;
   int64_t kss_m, kss_g, vss_m, vss_g;
+  int32_t ss_tma;      // fp8: the scale/shift words come by tiled copies of 16 bytes per (token, head), the word first
+  int32_t ss_bytes;    // fp8: bytes of the scale/shift words of K (or V) in a stage
   int32_t copy_group;  // tokens per bulk copy (int4 only, mode 0)
   int32_t stages;         // depth of the shared-memory ring
   int32_t q_first_stage;  // stages >= this one hold the staged Q until q_done
@@ -145,7 +149,7 @@ constexpr int kDecMaxStages = 12;
 template <int kFmt>
 struct DecOccupancy {
   static constexpr int kCtasPerSm = kFmt == kFmtInt4 ? 2 : kFmt == kFmtFp8 ? XFB_FP8_CTAS : 1;
-  static constexpr int kRingBudget = kCtasPerSm == 2 ? 106 * 1024 : 212 * 1024;
+  static constexpr int kRingBudget = kCtasPerSm == 2 ? 108 * 1024 : 212 * 1024;
 };
 
 // What a consumer warp needs to know about its CTA.
@@ -1117,8 +1121,10 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
     }
     const uint8_t* kst = w.stage_base + st * w.stage_bytes;
     const uint8_t* vst = kst + w.kv_bytes;
-    const uint32_t* ssk = reinterpret_cast<const uint32_t*>(kst + 2 * w.kv_bytes) + hw * w.tok_per_stage;
-    const uint32_t* ssv = ssk + hb * w.tok_per_stage;
+    // scale/shift words: [head][token] after the 4-byte copies, [token][head][4 words] after the tiled ones
+    const uint32_t* ssk = reinterpret_cast<const uint32_t*>(kst + 2 * w.kv_bytes) + (a.ss_tma ? hw * 4 : hw * w.tok_per_stage);
+    const uint32_t* ssv = ssk + a.ss_bytes / 4;
+    const int ss_step = a.ss_tma ? hb * 4 : 1;  // words from one token to the next
 #pragma unroll 1
     for (int sp = 0; sp < kSps; ++sp) {
       const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
@@ -1150,7 +1156,8 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
       }
 
       // ------------------ scale/shift of tokens r, r+8; mask; online softmax
-      const uint32_t kw0 = ssk[tok0 + r], kw1 = ssk[tok0 + r + 8], vw0 = ssv[tok0 + r], vw1 = ssv[tok0 + r + 8];
+      const uint32_t kw0 = ssk[(tok0 + r) * ss_step], kw1 = ssk[(tok0 + r + 8) * ss_step];
+      const uint32_t vw0 = ssv[(tok0 + r) * ss_step], vw1 = ssv[(tok0 + r + 8) * ss_step];
       const float ksc0 = half_bits_to_float(kw0 & 0xFFFFu), ksh0 = half_bits_to_float(kw0 >> 16);
       const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
       float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
@@ -1418,13 +1425,20 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
         if (lane == 0) {
           const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
           const uint32_t box_bytes = uint32_t(a.box_tok) * hb * kHeadBytes;
-          mbar_expect_tx(&full_bar[st], uint32_t(nbox) * box_bytes * 2u);
+          const bool ss_tma = kFp8 && a.ss_tma;
+          const uint32_t box_ss = uint32_t(a.box_tok) * hb * 16u;  // 16 bytes per (token, head)
+          mbar_expect_tx(&full_bar[st], uint32_t(nbox) * (box_bytes + (ss_tma ? box_ss : 0u)) * 2u);
           for (int bx = 0; bx < nbox; ++bx) {
             const int64_t row = row_of(t0 + bx * a.box_tok);
             // third coordinate: 128-byte column group (16-bit cache) or kv head (fp8: a head is one 128-byte row)
             const int c2 = kFp8 ? head0 : head0 * (D / 64);
             tma_load_3d(ks + bx * box_bytes, &a.tm_k, &full_bar[st], 0, int(row), c2);
             tma_load_3d(vs + bx * box_bytes, &a.tm_v, &full_bar[st], 0, int(row), c2);
+            if (ss_tma) {
+              uint8_t* ss = ks + 2 * kv_bytes;
+              tma_load_3d(ss + bx * box_ss, &a.tm_kss, &full_bar[st], 0, head0, int(row));
+              tma_load_3d(ss + a.ss_bytes + bx * box_ss, &a.tm_vss, &full_bar[st], 0, head0, int(row));
+            }
           }
         }
         if constexpr (kFp8) {
@@ -1436,7 +1450,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
           // copy warp never waits for this data itself.
           uint32_t* ssk = reinterpret_cast<uint32_t*>(ks + 2 * kv_bytes);
           uint32_t* ssv = ssk + hb * TOK;
-          for (int i = lane; i < nvalid * hb; i += 32) {
+          for (int i = lane; i < (a.ss_tma ? 0 : nvalid * hb); i += 32) {
             const int tok = i / hb, hh = i % hb;  // heads fastest: neighbouring lanes read neighbouring words
             const int64_t row = row_of(t0 + tok);
             cp_async_4(ssk + hh * TOK + tok, a.k_ss + row * a.kss_m + (head0 + hh) * a.kss_g);
@@ -1685,7 +1699,8 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   const int kv_bytes = kFmt == kFmtFp8      ? Stage::tokens(a_in.hb) * a_in.hb * D
                        : a_in.copy_mode == 3 ? Stage::tokens(a_in.hb) * a_in.hb * D * 2
                                              : Stage::kv_bytes(a_in.hb);
-  const size_t stage_bytes = 2 * size_t(kv_bytes) + 2 * size_t(Stage::ss_bytes(a_in.hb));
+  const int ss_bytes = Stage::ss_bytes(a_in.hb) * (a_in.ss_tma ? 4 : 1);
+  const size_t stage_bytes = 2 * size_t(kv_bytes) + 2 * size_t(ss_bytes);
   const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
   int stages = int(DecOccupancy<kFmt>::kRingBudget / stage_bytes);
@@ -1697,6 +1712,7 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   a.q_first_stage = stages - q_stages;
   a.kv_bytes = kv_bytes;
   a.stage_bytes = int(stage_bytes);
+  a.ss_bytes = ss_bytes;
   const size_t ring = stages * stage_bytes + 1024;  // the kernel aligns the ring to 1024 B
   const size_t smem = ring > cmb ? ring : cmb;
   auto kern = decode_splitk_kernel<D, MT, kFmt, kBf16, NG>;
@@ -1884,6 +1900,31 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
         a.copy_mode = 3;
         a.box_tok = box;
       }
+    }
+  }
+
+  a.ss_tma = 0;
+  if (fp8 && a.copy_mode == 3 && p->ss_words >= 4) {
+    // The caller vouches for at least 4 consecutive int32 at every (token, kv head)
+    // entry of the scale/shift tensors (the word and its replicas for the query
+    // heads of the group): 16 bytes per entry can then come by tiled copies, one
+    // per tensor and run of tokens, instead of one 4-byte copy per word.
+    auto ok16 = [](const void* ptr, int64_t m, int64_t g, int heads) {
+      return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && m % 4 == 0 && m > 0 && (heads == 1 || (g % 4 == 0 && g > 0));
+    };
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc != nullptr && ok16(a.k_ss, a.kss_m, a.kss_g, p->kv_heads) && ok16(a.v_ss, a.vss_m, a.vss_g, p->kv_heads)) {
+      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : gappy ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t dims[3] = {4, cuuint64_t(p->kv_heads), rows};
+      const cuuint32_t bx[3] = {4, cuuint32_t(hb), cuuint32_t(a.box_tok)};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const cuuint64_t ks[2] = {cuuint64_t(p->kv_heads == 1 ? 4 : a.kss_g) * 4, cuuint64_t(a.kss_m) * 4};
+      const cuuint64_t vs[2] = {cuuint64_t(p->kv_heads == 1 ? 4 : a.vss_g) * 4, cuuint64_t(a.vss_m) * 4};
+      const CUresult rk = enc(&a.tm_kss, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(a.k_ss), dims, ks, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      const CUresult rv = enc(&a.tm_vss, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(a.v_ss), dims, vs, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (rk == CUDA_SUCCESS && rv == CUDA_SUCCESS) a.ss_tma = 1;
     }
   }
 

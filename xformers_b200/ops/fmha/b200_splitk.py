@@ -212,6 +212,8 @@ class FwOp(AttentionFwOpBase):
                 p.k_stride_g, p.v_stride_g = k.stride(2), v.stride(2)
                 if fp8:
                     p.ks_stride_g, p.vs_stride_g = kss.stride(2), vss.stride(2)
+                    # the word is laid out once per query head of the group: H consecutive int32 per entry
+                    p.ss_words = H if kss.stride(3) == 1 and vss.stride(3) == 1 else 1
                 p.o_stride_g, p.o_stride_h = out.stride(2), out.stride(3)
                 lse_g, lse_h = (lse.stride(0), lse.stride(1)) if lse is not None else (0, 0)
             else:
