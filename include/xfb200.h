@@ -181,6 +181,11 @@ typedef struct {
    * then bounds seqlen_k[b]. */
   const int32_t* kv_seqstart;
   int64_t kv_rows;
+  /* Local attention for one query per sequence (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+   * PagedBlockDiagonalCausalLocalPaddedKeysMask, fmha/attn_bias.py:29,43): 0, or the number of keys the
+   * query sees, the last window_size of its sequence.  Needs mq == 1 and the bottom-right causal mask. */
+  int32_t window_size;
+  int32_t reserved;
 } xfb200_decode_params;
 
 XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t kv_heads, int32_t q_per_kv, int32_t head_dim,

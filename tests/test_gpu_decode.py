@@ -333,3 +333,93 @@ def test_decode_respects_current_stream_and_custom_scale():
     assert out.dtype == torch.float32
     ro, _ = oracle.ref_attention_with_lse(q.float().cpu(), k_ref, v_ref, bias.to("cpu"), scale=0.05)
     assert (out.cpu() - ro).abs().max() <= ATOL_O[dtype]
+
+
+@gpu
+@pytest.mark.parametrize("fmt", ["bf16", "int4", "fp8"])
+@pytest.mark.parametrize("split_k", [None, 1, 3])
+@pytest.mark.parametrize("window", [1, 100, 640, 5000])
+@pytest.mark.parametrize("kv_heads,group", [(8, 8), (1, 4)])
+def test_local_window_one_query(kv_heads, group, window, split_k, fmt):
+    """BlockDiagonalCausalLocalAttentionPaddedKeysMask and its paged form
+    (bias list of tests/test_mem_eff_attention.py:283,395) with one query per
+    sequence: the query sees the last `window` keys of its sequence, i.e. the
+    sequence starts later; the same keys behind a block table give the same bits."""
+    require_cuda()
+    dtype, D, B, max_t, page = torch.bfloat16, 128, 4, 1536, 64
+    g = torch.Generator().manual_seed(window)
+    lens = [max_t, 1, 700, 99]
+    q = torch.randn(1, B, kv_heads, group, D, generator=g).to(dtype).cuda()
+    kf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
+    vf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
+    expand = lambda t: t.expand(-1, -1, -1, group, -1)
+    pad_bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([1] * B, max_t, lens, window, device="cuda")
+    if fmt == "fp8":
+        from oracle import fp8 as ofp8
+
+        flat = lambda t: t.to(dtype).float().reshape(-1, D)
+        (kq, ksc, ksh), (vq, vsc, vsh) = ofp8.quantize_fp8_asymmetric(flat(kf)), ofp8.quantize_fp8_asymmetric(flat(vf))
+        kss_w, vss_w = ofp8.combine_scale_shift(ksc, ksh), ofp8.combine_scale_shift(vsc, vsh)
+        # what the kernel sees after the fp16 rounding of scale and shift
+        (ksc, ksh), (vsc, vsh) = ofp8.split_scale_shift(kss_w), ofp8.split_scale_shift(vss_w)
+        k_ref = ofp8.dequantize_fp8_asymmetric(kq, ksc, ksh).reshape(kf.shape)
+        v_ref = ofp8.dequantize_fp8_asymmetric(vq, vsc, vsh).reshape(vf.shape)
+        k_pad = ofp8.pack_fp8_words(kq).reshape(1, B * max_t, kv_heads, 1, D // 4)
+        v_pad = ofp8.pack_fp8_words(vq).reshape(1, B * max_t, kv_heads, 1, D // 4)
+        kss, vss = kss_w.reshape(1, B * max_t, kv_heads, 1), vss_w.reshape(1, B * max_t, kv_heads, 1)
+    elif fmt == "int4":
+        k_pad, v_pad = oracle.quantize_kv_int4(kf), oracle.quantize_kv_int4(vf)
+        k_ref, v_ref = oracle.dequantize_kv_int4(k_pad), oracle.dequantize_kv_int4(v_pad)
+    else:
+        k_pad, v_pad = kf.to(dtype), vf.to(dtype)
+        k_ref, v_ref = k_pad.float(), v_pad.float()
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), expand(k_ref), expand(v_ref), pad_bias.to("cpu"))
+    op = S.FwOp if split_k is None else type("Op", (S.FwOp,), {"SPLIT_K": split_k})
+
+    def run(kc, vc, bias):
+        if fmt == "fp8":
+            inp = S.InputsFp8(query=q, key=expand(kc.cuda()), value=expand(vc.cuda()), attn_bias=bias,
+                              k_fp8_scale_shift=kss.cuda().expand(-1, -1, -1, group).contiguous(),
+                              v_fp8_scale_shift=vss.cuda().expand(-1, -1, -1, group).contiguous())
+            out, ctx = fmha._memory_efficient_attention_forward_requires_grad(inp, op=op)
+            return out, ctx.lse
+        return fmha.memory_efficient_attention_forward_requires_grad(q, expand(kc.cuda()), expand(vc.cuda()), bias, op=op)
+
+    out_pad, lse_pad = run(k_pad, v_pad, pad_bias)
+    assert_o_lse(out_pad, lse_pad, ro, rl, dtype, f"window {window} {fmt}")
+    # the plain causal mask with a window that covers everything is the same computation
+    if window >= max_t:
+        full = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens([1] * B, max_t, lens, device="cuda")
+        out_f, lse_f = run(k_pad, v_pad, full)
+        assert torch.equal(out_pad, out_f) and torch.equal(lse_pad, lse_f)
+    if fmt == "fp8":
+        paged = pad_bias.make_paged(torch.arange(B * (max_t // page), dtype=torch.int32).view(B, -1).cuda(), page, ab.PagedBlockDiagonalCausalLocalPaddedKeysMask)
+        inp = S.InputsFp8(query=q, key=expand(k_pad.cuda()), value=expand(v_pad.cuda()), attn_bias=paged, k_fp8_scale_shift=kss.cuda().expand(-1, -1, -1, group).contiguous(),
+                          v_fp8_scale_shift=vss.cuda().expand(-1, -1, -1, group).contiguous())
+        assert any("window" in r for r in S.FwOp.not_supported_reasons(inp))
+        return
+    pages_per_seq = max_t // page
+    n_pages = B * pages_per_seq
+    perm = torch.randperm(n_pages, generator=g).int().view(B, pages_per_seq)
+    k_pg = oracle.scatter_to_pages(k_pad, perm, page, [max_t] * B, max_t, n_pages)
+    v_pg = oracle.scatter_to_pages(v_pad, perm, page, [max_t] * B, max_t, n_pages)
+    bias = pad_bias.make_paged(perm.cuda(), page, ab.PagedBlockDiagonalCausalLocalPaddedKeysMask)
+    assert bias._window_size == window
+    out, lse = run(k_pg, v_pg, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, f"paged window {window} {fmt}")
+    # and the paged bias materialises to the same visible keys as the flat one (physical rows)
+    m = bias.to("cpu").materialize((B, n_pages * page)) == 0
+    assert int(m.sum()) == sum(min(n, window) for n in lens)
+
+
+@gpu
+def test_local_window_needs_one_query():
+    require_cuda()
+    q = torch.randn(1, 4, 2, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 2 * 64, 2, 128, device="cuda", dtype=torch.bfloat16)
+    bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([2, 2], 64, [10, 20], 4, device="cuda")
+    assert any("one query per sequence" in r for r in S.FwOp.not_supported_reasons(fmha.Inputs(q, k, k, bias)))
+    # the dispatcher still finds an operator for it (the prefill operator takes windows with several queries)
+    out = fmha.memory_efficient_attention_forward(q, k, k, bias)
+    ro, _ = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), k.float().cpu(), bias.to("cpu"))
+    assert (out.float().cpu() - ro).abs().max() <= 2e-2

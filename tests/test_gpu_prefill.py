@@ -176,6 +176,44 @@ def test_padded_keys_prefill_and_nan_padding(op):
         assert torch.equal(out, out_n) and torch.equal(lse, lse_n)
     _status_ok()
 
+@gpu
+@pytest.mark.parametrize("window", [1, 3, 64, 200])
+@pytest.mark.parametrize("op", KERNELS + [P.FwOp_Tcgen05_M256])
+def test_causal_local_padded_keys_and_bottom_right_local(op, window):
+    """The window forms of the bottom-right causal masks
+    (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+    LowerTriangularFromBottomRightLocalAttentionMask; bias list of
+    tests/test_mem_eff_attention.py:283,389): every query sees at most `window` keys."""
+    require_cuda()
+    dtype = torch.bfloat16
+    n_heads, d, padding = 2, 128, 384
+    k_seqlen = [5, 300, 131, 1, 384, 64]
+    q_seqlen = [4, 130, 131, 1, 7, 64]
+    g = torch.Generator().manual_seed(window)
+    q = torch.randn(1, sum(q_seqlen), n_heads, d, generator=g).to(dtype).cuda()
+    k = torch.randn(1, len(k_seqlen) * padding, n_heads, d, generator=g).to(dtype).cuda()
+    v = torch.randn(1, len(k_seqlen) * padding, n_heads, d, generator=g).to(dtype).cuda()
+    bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local(q_seqlen, padding, k_seqlen, window, device="cuda")
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, "causal local padded keys")
+    # NaN beyond the sequences must not leak
+    kn, vn = k.clone(), v.clone()
+    for b, n in enumerate(k_seqlen):
+        kn[0, b * padding + n : (b + 1) * padding] = float("nan")
+        vn[0, b * padding + n : (b + 1) * padding] = float("nan")
+    out_n, lse_n = fmha.memory_efficient_attention_forward_requires_grad(q, kn, vn, bias, op=op)
+    assert torch.equal(out, out_n) and torch.equal(lse, lse_n)
+
+    qd = torch.randn(2, 200, n_heads, d, generator=g).to(dtype).cuda()
+    kd = torch.randn(2, 333, n_heads, d, generator=g).to(dtype).cuda()
+    vd = torch.randn(2, 333, n_heads, d, generator=g).to(dtype).cuda()
+    b2 = ab.LowerTriangularFromBottomRightLocalAttentionMask(window)
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(qd, kd, vd, b2, op=op)
+    ro, rl = ref(qd, kd, vd, b2)
+    assert_o_lse(out, lse, ro, rl, dtype, "bottom-right local")
+    _status_ok()
+
 
 @gpu
 @pytest.mark.parametrize("op", KERNELS)

@@ -331,3 +331,27 @@ def test_gappy_keys_mask_materialize():
     pv = (paged.materialize((3, 8)) == 0).int().tolist()
     # sequence 0: logical rows 1, 2 of its table [1, 0] -> physical rows 5, 6; sequence 1: rows 0..2 of table [0, 1] -> 0, 1, 2
     assert pv == [[0, 0, 0, 0, 0, 1, 1, 0], [1, 1, 1, 0, 0, 0, 0, 0], [1, 1, 1, 0, 0, 0, 0, 0]]
+
+
+def test_causal_local_padded_keys_and_bottom_right_local_materialize():
+    """Hand-built masks of the window forms: query i of a block of ql queries sees
+    key t iff i + kl - ql - window < t <= i + kl - ql."""
+    from xformers_b200.ops.fmha import attn_bias as ab
+
+    bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([2, 1], 4, [4, 2], 2)
+    m = bias.materialize((3, 8)) == 0
+    want = torch.tensor([
+        [0, 1, 1, 0, 0, 0, 0, 0],   # sequence 0, query 0 of 2, 4 keys: diagonal at key 2, window 2 -> keys 1, 2
+        [0, 0, 1, 1, 0, 0, 0, 0],   # query 1: keys 2, 3
+        [0, 0, 0, 0, 1, 1, 0, 0],   # sequence 1 (slot 4..7, 2 keys): its only query sees keys 0, 1 of the slot
+    ], dtype=torch.bool)
+    assert torch.equal(m, want)
+    with pytest.raises(ValueError):
+        ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([1], 4, [1], 0)
+
+    m = ab.LowerTriangularFromBottomRightLocalAttentionMask(2).materialize((2, 5)) == 0
+    want = torch.tensor([[0, 0, 1, 1, 0], [0, 0, 0, 1, 1]], dtype=torch.bool)
+    assert torch.equal(m, want)
+    # window >= number of keys: the plain bottom-right causal mask
+    full = ab.LowerTriangularFromBottomRightLocalAttentionMask(99).materialize((3, 5))
+    assert torch.equal(full, ab.LowerTriangularFromBottomRightMask().materialize((3, 5)))

@@ -131,6 +131,8 @@ class DecodeParams(C.Structure):
         ("vs_stride_g", C.c_int64),
         ("kv_seqstart", C.c_void_p),
         ("kv_rows", C.c_int64),
+        ("window_size", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

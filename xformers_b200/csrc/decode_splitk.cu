@@ -72,6 +72,7 @@ struct DecodeArgs {
   int32_t causal;
   int32_t out_dtype;
   float scale_log2;
+  int32_t window_size;  // 0: none; else (mq == 1 only) the query sees its sequence's last window_size keys
 };
 
 template <bool kBf16>
@@ -1335,7 +1336,10 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
   constexpr int kSps = Stage::kSubTiles;
   const int TOK = 16 * wph * kSps;
 
-  const int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
+  int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
+  // a window (one query per sequence) is a sequence that starts win_skip keys later
+  const int win_skip = a.window_size > 0 ? max(kv_len - a.window_size, 0) : 0;
+  kv_len -= win_skip;
   const int chunk_lo = split * a.chunk_tokens;
   const int chunk_hi = min(chunk_lo + a.chunk_tokens, kv_len);
   if (chunk_lo >= chunk_hi) {
@@ -1391,8 +1395,8 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
     // so that a lane waits for that load once per page instead of once per stage
     int cached_page = -1;
     int64_t cached_base = 0;
-    const int64_t kv_base = a.kv_start != nullptr ? int64_t(a.kv_start[b]) : int64_t(b) * a.kv_padding;  // padded / gappy cache
-    const int t_shift = (a.block_tables != nullptr && a.kv_start != nullptr) ? a.kv_start[b] : 0;       // paged gappy cache
+    const int64_t kv_base = (a.kv_start != nullptr ? int64_t(a.kv_start[b]) : int64_t(b) * a.kv_padding) + win_skip;  // padded / gappy cache
+    const int t_shift = ((a.block_tables != nullptr && a.kv_start != nullptr) ? a.kv_start[b] : 0) + win_skip;       // paged gappy cache
     auto row_of = [&](int t_rel) -> int64_t {
       if (a.block_tables == nullptr) return kv_base + t_rel;
       const int t = t_rel + t_shift;
@@ -1613,7 +1617,8 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const __grid_constant
   const int row = int(gw % R);
   const int head = int((gw / R) % a.kv_heads);
   const int b = int(gw / (int64_t(R) * a.kv_heads));
-  const int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
+  int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
+  if (a.window_size > 0) kv_len = min(kv_len, a.window_size);
   const int nsplit = min(a.split_k, (kv_len + a.chunk_tokens - 1) / a.chunk_tokens);
 
   float mx = -INFINITY;
@@ -1794,7 +1799,8 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   a.batch = p->batch, a.mq = p->mq, a.kv_heads = p->kv_heads, a.q_per_kv = p->q_per_kv;
   a.kv_padding = p->kv_padding, a.page_size = p->page_size, a.bt_stride = p->block_table_stride;
   a.split_k = p->split_k;
-  a.chunk_tokens = decode_chunk_tokens(p->kv_padding, p->split_k);
+  // with a window no sequence has more than window_size keys to read: the chunks divide that
+  a.chunk_tokens = decode_chunk_tokens(p->window_size > 0 && p->window_size < p->kv_padding ? p->window_size : p->kv_padding, p->split_k);
   a.rows = R, a.row_blocks = row_blocks;
   a.q_sm = p->q_stride_m, a.q_sg = p->q_stride_g, a.q_sh = p->q_stride_h;
   a.k_sm = p->k_stride_m, a.k_sg = p->k_stride_g, a.v_sm = p->v_stride_m, a.v_sg = p->v_stride_g;
@@ -1828,6 +1834,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   auto al16 = [&](int64_t elems) { return (elems * elem) % 16 == 0; };
   const bool base_al = (reinterpret_cast<uintptr_t>(p->k) % 16 == 0) && (reinterpret_cast<uintptr_t>(p->v) % 16 == 0);
   a.copy_group = 1;
+  const bool moved_start = p->kv_seqstart != nullptr || p->window_size > 0;  // a sequence's first key is not the first row of its slot
   if (!base_al) {
     a.copy_mode = 2;
   } else if (heads_contig && al16(p->k_stride_m) && al16(p->v_stride_m) && al16(int64_t(hb) * head_elems) &&
@@ -1838,7 +1845,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     // tokens of a page (or of the padded row) follow one another in memory,
     // copy runs of up to 64 tokens at once.
     // (not for gappy caches: a run could cross a page, or the end of the tensor)
-    if (int4 && p->kv_seqstart == nullptr && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
+    if (int4 && !moved_start && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems && p->v_stride_m == p->k_stride_m) {
       const int span = p->block_tables ? p->page_size : p->kv_padding;
       // a run must fit the stage it is copied into (a power of two of tokens)
       const int stage_tokens = p->head_dim == 128 ? DecStage<128, kFmtInt4>::tokens(hb) : DecStage<64, kFmtInt4>::tokens(hb);
@@ -1848,7 +1855,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     }
   } else if (al16(p->k_stride_m) && al16(p->v_stride_m) && al16(a.k_sg) && al16(a.v_sg) && al16(head_elems)) {
     a.copy_mode = 1;
-  } else if (int4 && p->kv_seqstart == nullptr && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
+  } else if (int4 && !moved_start && heads_contig && head_blocks == 1 && p->k_stride_m == int64_t(hb) * head_elems &&
              p->v_stride_m == p->k_stride_m) {
     // tokens are contiguous: copy groups of 2 or 4 tokens so that each copy is a multiple of 16 B
     int g = 2;
@@ -1866,8 +1873,13 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
   if (fp8 && a.copy_mode != 0) return set_error(XFB200_E_UNSUPPORTED, "decode: the heads of an fp8 cache row must be contiguous");
   a.box_tok = 16;
-  const bool gappy = p->kv_seqstart != nullptr;
-  if (gappy && p->block_tables == nullptr && p->kv_rows <= 0)
+  a.window_size = p->window_size;
+  if (p->window_size < 0) return set_error(XFB200_E_INVALID, "decode: window_size %d", p->window_size);
+  if (p->window_size > 0 && (p->mq != 1 || p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT))
+    return set_error(XFB200_E_UNSUPPORTED, "decode: a window needs one query per sequence and the bottom-right causal mask");
+  // a window moves the first key of a sequence like a gappy start does
+  const bool gappy = p->kv_seqstart != nullptr || p->window_size > 0;
+  if (gappy && p->block_tables == nullptr && p->kv_seqstart != nullptr && p->kv_rows <= 0)
     return set_error(XFB200_E_INVALID, "decode: a gappy cache needs kv_rows, the number of key rows of the tensor");
   // (a run of a paged gappy cache may start anywhere inside a page: per-token copies there)
   if (!int4 && a.copy_mode == 0 && !(gappy && p->block_tables != nullptr) &&
@@ -1883,7 +1895,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     if (box >= (fp8 ? 16 : 8) && enc != nullptr) {
       // token rows: all of a padded cache (rows past the end read as zero); a paged
       // pool's size is not part of the call, and a copy never leaves its page
-      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : gappy ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : p->kv_seqstart != nullptr ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
       // 16-bit cache: {64 elements, token rows, 128-byte column groups}; fp8: {128 bytes, token rows, kv heads}
       const cuuint64_t dims[3] = {cuuint64_t(fp8 ? 128 : 64), rows, fp8 ? cuuint64_t(p->kv_heads) : cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
       const cuuint32_t bx[3] = {cuuint32_t(fp8 ? 128 : 64), cuuint32_t(box), cuuint32_t(fp8 ? hb : hb * (p->head_dim / 64))};
@@ -1914,7 +1926,7 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     };
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc != nullptr && ok16(a.k_ss, a.kss_m, a.kss_g, p->kv_heads) && ok16(a.v_ss, a.vss_m, a.vss_g, p->kv_heads)) {
-      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : gappy ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : p->kv_seqstart != nullptr ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
       const cuuint64_t dims[3] = {4, cuuint64_t(p->kv_heads), rows};
       const cuuint32_t bx[3] = {4, cuuint32_t(hb), cuuint32_t(a.box_tok)};
       const cuuint32_t estr[3] = {1, 1, 1};

@@ -110,6 +110,24 @@ class LowerTriangularFromBottomRightMask(AttentionBias):
 
 
 @dataclass
+class LowerTriangularFromBottomRightLocalAttentionMask(LowerTriangularFromBottomRightMask):
+    """Bottom-right causal mask that also hides keys more than ``_window_size - 1``
+    positions left of the diagonal: each query sees at most ``_window_size`` keys
+    (xformers/ops/fmha/attn_bias.py:42; listed as a bottom-right mask in
+    tests/test_mem_eff_attention.py:384-396)."""
+
+    _window_size: int = 0
+
+    def __post_init__(self) -> None:
+        if self._window_size <= 0:
+            raise ValueError(f"Expected `window_size > 0`, but window_size={self._window_size}")
+
+    def materialize(self, shape, dtype=torch.float32, device="cpu") -> torch.Tensor:
+        vis = _band(shape[-2], shape[-1], device, shift=shape[-1] - shape[-2], window_left=self._window_size - 1)
+        return _additive(vis, dtype).expand(*shape)
+
+
+@dataclass
 class LocalAttentionFromBottomRightMask(AttentionBias):
     """Bottom-right aligned band (tests/test_mem_eff_attention.py:2389-2399)."""
 
@@ -512,7 +530,8 @@ class BlockDiagonalPaddedKeysMask(AttentionBias):
         )
         # share the device tensor so that in-place length updates stay visible
         k_info.seqlen = self.k_seqinfo.seqlen
-        return paged_type(q_seqinfo=self.q_seqinfo, k_seqinfo=k_info, block_tables=block_tables, page_size=page_size)
+        extra = {"_window_size": self._window_size} if hasattr(self, "_window_size") else {}
+        return paged_type(q_seqinfo=self.q_seqinfo, k_seqinfo=k_info, block_tables=block_tables, page_size=page_size, **extra)
 
 
 @dataclass
@@ -521,6 +540,34 @@ class BlockDiagonalCausalWithOffsetPaddedKeysMask(BlockDiagonalPaddedKeysMask):
     of a block of ql queries sees key t iff ``t <= i + kv_seqlen[b] - ql``."""
 
     _CAUSAL: ClassVar[bool] = True
+
+
+@dataclass
+class BlockDiagonalCausalLocalAttentionPaddedKeysMask(BlockDiagonalPaddedKeysMask):
+    """:class:`BlockDiagonalCausalWithOffsetPaddedKeysMask` with a window: query
+    i of a block of ql queries sees key t of its sequence iff ``t <= i +
+    kv_seqlen[b] - ql`` and ``t > i + kv_seqlen[b] - ql - _window_size``
+    (xformers/ops/fmha/attn_bias.py:29; tests/test_mem_eff_attention.py:283)."""
+
+    _window_size: int = 0
+
+    def to(self, device):
+        return type(self)(q_seqinfo=self.q_seqinfo.to(device), k_seqinfo=self.k_seqinfo.to(device), _window_size=self._window_size)
+
+    def _block(self, ql: int, kl: int, device) -> torch.Tensor:
+        return _band(ql, kl, device, shift=kl - ql, window_left=self._window_size - 1)
+
+    @classmethod
+    def from_seqlens_local(cls, q_seqlen: Sequence[int], kv_padding: int, kv_seqlen: Sequence[int], window_size: int, *, device=None):
+        if window_size <= 0:
+            raise ValueError(f"Expected `window_size > 0`, but window_size={window_size}")
+        if len(q_seqlen) != len(kv_seqlen):
+            raise ValueError("q_seqlen and kv_seqlen must describe the same number of sequences")
+        return cls(
+            q_seqinfo=_SeqLenInfo.from_seqlens(q_seqlen, device=device),
+            k_seqinfo=_PaddedSeqLenInfo.from_seqlens_padded(kv_seqlen, kv_padding, device=device),
+            _window_size=window_size,
+        )
 
 
 @dataclass
@@ -622,6 +669,41 @@ class PagedBlockDiagonalPaddedKeysMask(AttentionBias):
 @dataclass
 class PagedBlockDiagonalCausalWithOffsetPaddedKeysMask(PagedBlockDiagonalPaddedKeysMask):
     _UNPAGED_TYPE: ClassVar[Type[BlockDiagonalPaddedKeysMask]] = BlockDiagonalCausalWithOffsetPaddedKeysMask
+
+
+@dataclass
+class PagedBlockDiagonalCausalLocalPaddedKeysMask(PagedBlockDiagonalPaddedKeysMask):
+    """:class:`BlockDiagonalCausalLocalAttentionPaddedKeysMask` behind a block table
+    (xformers/ops/fmha/attn_bias.py:43; tests/test_mem_eff_attention.py:395)."""
+
+    _window_size: int = 0
+
+    _UNPAGED_TYPE: ClassVar[Type[BlockDiagonalPaddedKeysMask]] = BlockDiagonalCausalLocalAttentionPaddedKeysMask
+
+    def to(self, device):
+        return type(self)(
+            q_seqinfo=self.q_seqinfo.to(device), k_seqinfo=self.k_seqinfo.to(device),
+            block_tables=self.block_tables.to(device), page_size=self.page_size, _window_size=self._window_size,
+        )
+
+    def materialize(self, shape, dtype=torch.float32, device="cpu") -> torch.Tensor:
+        """Mask over *physical* key rows: shape[-1] = num_pages * page_size."""
+        out = torch.full((self.q_seqinfo.seqstart_py[-1], shape[-1]), -math.inf, dtype=dtype, device=device)
+        bt = self.block_tables.to(device).long()
+        for b, ((qs, qe), n) in enumerate(zip(self.q_seqinfo.intervals(), self.k_seqinfo.seqlen_py)):
+            t = torch.arange(n, device=device)
+            rows = bt[b, t // self.page_size] * self.page_size + t % self.page_size
+            vis = _band(qe - qs, n, device, shift=n - (qe - qs), window_left=self._window_size - 1)
+            out[qs:qe, rows] = _additive(vis, dtype)
+        return out.expand(*shape)
+
+    @classmethod
+    def from_seqlens_local(cls, q_seqlen: Sequence[int], kv_seqlen: Sequence[int], block_tables: torch.Tensor, page_size: int,
+                           window_size: int, *, device=None):
+        if window_size <= 0:
+            raise ValueError(f"Expected `window_size > 0`, but window_size={window_size}")
+        base = PagedBlockDiagonalPaddedKeysMask.from_seqlens(q_seqlen, kv_seqlen, block_tables, page_size, device=device)
+        return cls(q_seqinfo=base.q_seqinfo, k_seqinfo=base.k_seqinfo, block_tables=block_tables, page_size=page_size, _window_size=window_size)
 
 
 @dataclass

@@ -19,6 +19,8 @@ from .attn_bias import (
     BlockDiagonalCausalFromBottomRightMask,
     BlockDiagonalCausalLocalAttentionFromBottomRightMask,
     BlockDiagonalCausalLocalAttentionMask,
+    BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+    LowerTriangularFromBottomRightLocalAttentionMask,
     BlockDiagonalCausalMask,
     BlockDiagonalCausalWithOffsetGappyKeysMask,
     BlockDiagonalCausalWithOffsetPaddedKeysMask,
@@ -70,7 +72,11 @@ def _mask_of(bias: Any) -> Tuple[int, int]:
         return _lib.MASK_CAUSAL_BOTTOM_RIGHT, -1
     if type(bias) in (LowerTriangularMaskLocalAttention, BlockDiagonalCausalLocalAttentionMask):
         return _lib.MASK_CAUSAL_TOP_LEFT, bias._window_size - 1
-    if type(bias) is BlockDiagonalCausalLocalAttentionFromBottomRightMask:
+    if type(bias) in (
+        BlockDiagonalCausalLocalAttentionFromBottomRightMask,
+        BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+        LowerTriangularFromBottomRightLocalAttentionMask,
+    ):
         return _lib.MASK_CAUSAL_BOTTOM_RIGHT, bias._window_size - 1
     raise NotImplementedError(f"bias {type(bias)}")
 
@@ -95,6 +101,8 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalLocalAttentionFromBottomRightMask,
         BlockDiagonalPaddedKeysMask,
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
+        BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+        LowerTriangularFromBottomRightLocalAttentionMask,
         BlockDiagonalGappyKeysMask,
         BlockDiagonalCausalWithOffsetGappyKeysMask,
         torch.Tensor,

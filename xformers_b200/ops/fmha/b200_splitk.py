@@ -20,6 +20,8 @@ import torch
 
 from ... import _lib
 from .attn_bias import (
+    BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+    PagedBlockDiagonalCausalLocalPaddedKeysMask,
     BlockDiagonalCausalWithOffsetGappyKeysMask,
     BlockDiagonalCausalWithOffsetPaddedKeysMask,
     BlockDiagonalGappyKeysMask,
@@ -49,6 +51,9 @@ def _geometry(inp: Inputs):
     return q, k, v, broadcast
 
 
+_LOCAL_BIASES = (BlockDiagonalCausalLocalAttentionPaddedKeysMask, PagedBlockDiagonalCausalLocalPaddedKeysMask)
+
+
 class FwOp(AttentionFwOpBase):
     """Flash-decoding on sm_100a.  ``SPLIT_K = None`` picks the split count."""
 
@@ -67,6 +72,8 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalWithOffsetGappyKeysMask,
         PagedBlockDiagonalGappyKeysMask,
         PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
+        BlockDiagonalCausalLocalAttentionPaddedKeysMask,  # one query per sequence
+        PagedBlockDiagonalCausalLocalPaddedKeysMask,
     )
     SUPPORTS_DROPOUT = False
     SUPPORTS_CUSTOM_SCALE = True
@@ -134,6 +141,11 @@ class FwOp(AttentionFwOpBase):
             mq = qs.max_seqlen
             if B != 1:
                 reasons.append("padded/paged biases need batch 1")
+            if isinstance(bias, _LOCAL_BIASES):
+                if mq != 1:
+                    reasons.append("local attention is supported for one query per sequence (use the prefill operator for more)")
+                if fp8 and isinstance(bias, PagedBlockDiagonalPaddedKeysMask):
+                    reasons.append("a paged fp8 cache cannot be read through a window")
         else:
             mq = Mq
             if B > 1 and (q.stride(0) != Mq * q.stride(1) or k.stride(0) != k.shape[1] * k.stride(1) or v.stride(0) != v.shape[1] * v.stride(1)):
@@ -256,15 +268,18 @@ class FwOp(AttentionFwOpBase):
                         PagedBlockDiagonalCausalWithOffsetPaddedKeysMask,
                         BlockDiagonalCausalWithOffsetGappyKeysMask,
                         PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
-                    ),
+                    )
+                    + _LOCAL_BIASES,
                 ):
                     p.mask_type = _lib.MASK_CAUSAL_BOTTOM_RIGHT
+                if isinstance(bias, _LOCAL_BIASES):
+                    p.window_size = bias._window_size
             else:
                 p.batch, p.mq = B, Mq
                 p.seqlen_k = None
                 p.kv_padding = k.shape[1]
             row_bytes = D if fp8 else (D // 8 + cls.NUM_GROUPS) * 4 if quantized else D * 2
-            p.split_k = cls.get_split_k(p.batch, p.kv_padding, p.kv_heads, row_bytes)
+            p.split_k = cls.get_split_k(p.batch, min(p.kv_padding, p.window_size) if p.window_size else p.kv_padding, p.kv_heads, row_bytes)
             lib = _lib.load()
             nbytes = lib.xfb200_decode_scratch_bytes(p.batch, p.mq, p.kv_heads, p.q_per_kv, D, p.split_k)
             scratch = torch.empty((nbytes,), dtype=torch.uint8, device=q.device) if nbytes else None
