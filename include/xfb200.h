@@ -301,7 +301,11 @@ typedef struct {
   const int32_t* block_tables;
   int64_t block_tables_stride; /* elements between the rows of two sequences */
   int32_t page_size;
-  int32_t reserved;
+  /* 0: cache_k / cache_v have the dtype of the inputs.  1 (an extension as well): they are int4
+   * row-wise caches of int32 rows, 1 + dim / 8 words with one quantisation group
+   * (XFB200_KV_INT4_ROWWISE as the decode operator reads it); ck_* / cv_* strides count int32
+   * words.  Needs bf16 / f16 inputs, dim a power of two in [32, 512], 16-byte aligned input rows. */
+  int32_t cache_format;
 } xfb200_rope_params;
 
 XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);

@@ -212,3 +212,76 @@ def test_paged_cache(page_size, groups):
             qlast.float().cpu(), want_k.float().unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1),
             want_v.float().unsqueeze(3).expand(-1, -1, -1, Hq // Hkv, -1), dbias.to("cpu"))
         torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("adjacents", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dim", [64, 128, 256])
+@pytest.mark.parametrize("paged", [False, True])
+def test_int4_cache_quantised_on_write(paged, dim, dtype, adjacents):
+    """Beyond the reference: cache_k / cache_v are int4 row-wise caches
+    (benchmarks/benchmark_attn_decoding.py:38-72).  Values are copies, so their
+    rows must equal the oracle's quantiser bit for bit; rotated keys may differ
+    from the float64 oracle by one rounding of the 16-bit value, i.e. by at most
+    one quantisation step after dequantising.  Untouched rows keep their bits."""
+    nq, cache_lens, page = [3, 1, 17], [40, 300, 17], 64
+    B, Hq, Hkv = len(nq), 8, 2
+    g = torch.Generator().manual_seed(dim + int(paged))
+    M = sum(nq)
+    xq = torch.randn(1, M, Hq, dim, generator=g).to(dtype)
+    xk = torch.randn(1, M, Hkv, dim, generator=g).to(dtype)
+    xv = torch.randn(1, M, Hkv, dim, generator=g).to(dtype)
+    dev = torch.device("cuda")
+    if paged:
+        max_pages = 5
+        tables = torch.randperm(B * max_pages, generator=g).int().view(B, max_pages)
+        rows_total, starts = B * max_pages * page, [0] * B
+        bias = fmha.attn_bias.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(nq, cache_lens, tables, page).to(dev)
+        extra = dict(block_tables=tables.tolist(), page_size=page)
+    else:
+        padding = 320
+        rows_total, starts = B * padding, [b * padding for b in range(B)]
+        bias = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=nq, kv_padding=padding, kv_seqlen=cache_lens).to(dev)
+        extra = {}
+    old_k = torch.randint(-2**31, 2**31 - 1, (1, rows_total, Hkv, 1 + dim // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    old_v = torch.randint(-2**31, 2**31 - 1, (1, rows_total, Hkv, 1 + dim // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    ck, cv = old_k.to(dev), old_v.to(dev)
+    out = rope_padded(xq.to(dev), xk.to(dev), xv.to(dev), ck, cv, bias, adjacents=adjacents)
+    # the oracle's pipeline: rope into a 16-bit cache, then quantise the written rows
+    z = torch.zeros(1, rows_total, Hkv, dim, dtype=dtype)
+    want_q, want_k, want_v = oracle.rope_padded_ref(xq, xk, xv, z, z, nq, starts, cache_lens, adjacents=adjacents, **extra)
+    torch.testing.assert_close(out.cpu().float(), want_q.float(), atol=5e-3, rtol=8e-3)
+    written = (want_v[0] != 0).flatten(1).any(-1) | (want_k[0] != 0).flatten(1).any(-1)
+    assert int(written.sum()) == M
+    assert torch.equal(ck.cpu()[0, ~written], old_k[0, ~written]) and torch.equal(cv.cpu()[0, ~written], old_v[0, ~written])
+    assert torch.equal(cv.cpu()[0, written], oracle.quantize_kv_int4(want_v[0, written]))
+    got_k = oracle.dequantize_kv_int4(ck.cpu()[0, written])
+    ref_rows = want_k[0, written].float()
+    step = (ref_rows.amax(-1, keepdim=True) - ref_rows.amin(-1, keepdim=True)) / 15
+    # half a step of quantisation error, plus one step where the 16-bit rounding of the rotated value fell the other way
+    assert ((got_k - ref_rows).abs() <= 1.6 * step + 1e-2).all()
+    assert ((got_k - ref_rows).abs() <= 0.51 * step + 1e-2).float().mean() > 0.97
+
+
+def test_int4_cache_feeds_decode():
+    """rope_padded -> int4 paged cache -> split-K decode, against attention on the
+    dequantised oracle cache."""
+    nq, cache_lens, page, D, Hkv, G = [1, 1, 1], [100, 257, 31], 64, 128, 2, 4
+    B = 3
+    g = torch.Generator().manual_seed(5)
+    dev = torch.device("cuda")
+    tables = torch.randperm(B * 5, generator=g).int().view(B, 5)
+    rows_total = B * 5 * page
+    # a cache whose earlier keys are already there (quantised), then one new token per sequence
+    base_k, base_v = torch.randn(1, rows_total, Hkv, D, generator=g).bfloat16(), torch.randn(1, rows_total, Hkv, D, generator=g).bfloat16()
+    ck, cv = oracle.quantize_kv_int4(base_k).to(dev), oracle.quantize_kv_int4(base_v).to(dev)
+    xq = torch.randn(1, B, Hkv * G, D, generator=g).bfloat16()
+    xk, xv = torch.randn(1, B, Hkv, D, generator=g).bfloat16(), torch.randn(1, B, Hkv, D, generator=g).bfloat16()
+    bias = fmha.attn_bias.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(nq, cache_lens, tables, page).to(dev)
+    out_q = rope_padded(xq.to(dev), xk.to(dev), xv.to(dev), ck, cv, bias)
+    q5 = out_q.view(1, B, Hkv, G, D)
+    attn = fmha.memory_efficient_attention_forward(q5, ck.unsqueeze(3).expand(-1, -1, -1, G, -1), cv.unsqueeze(3).expand(-1, -1, -1, G, -1), bias,
+                                                   op=fmha.triton_splitk.FwOp)
+    k_deq, v_deq = oracle.dequantize_kv_int4(ck.cpu()), oracle.dequantize_kv_int4(cv.cpu())
+    ref, _ = oracle.ref_attention_with_lse(q5.float().cpu(), k_deq.unsqueeze(3).expand(-1, -1, -1, G, -1), v_deq.unsqueeze(3).expand(-1, -1, -1, G, -1), bias.to("cpu"))
+    torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)

@@ -178,7 +178,7 @@ class RopeParams(C.Structure):
             for n in ("theta", "linear_scale", "dynamic_old_context_len", "dynamic_scale_factor", "dynamic_low_freq_factor", "dynamic_high_freq_factor")
         ]
         + [(f"{t}_{a}", C.c_int64) for t in ("xq", "xk", "xv", "oq", "ck", "cv") for a in "mgh"]
-        + [("block_tables", C.c_void_p), ("block_tables_stride", C.c_int64), ("page_size", C.c_int32), ("reserved", C.c_int32)]
+        + [("block_tables", C.c_void_p), ("block_tables_stride", C.c_int64), ("page_size", C.c_int32), ("cache_format", C.c_int32)]
     )
 
 

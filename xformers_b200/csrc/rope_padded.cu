@@ -82,8 +82,9 @@ struct RopeVec {
 
 // source and destination of row `row` (q rows, then k rows, then v rows) of the
 // token at row `qpos` of the inputs and row `cache_pos` of the caches
-template <typename T>
-__device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, int qpos, int cache_pos, const T*& src, T*& dst, bool& rotate) {
+// (an int4 cache has int32 rows: its strides count words)
+template <typename T, bool kQuant = false>
+__device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, int qpos, int cache_pos, const T*& src, T*& dst, bool& rotate, int* kind_out = nullptr) {
   int head = row, g = 0;
   if (p.groups != 1) head = row / p.groups, g = row - head * p.groups;
   const int kind = (head >= p.q_heads) + (head >= p.q_heads + p.kv_heads);  // 0 q, 1 k, 2 v
@@ -97,7 +98,12 @@ __device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, i
   const int64_t d_g = kind == 0 ? p.oq_g : (kind == 1 ? p.ck_g : p.cv_g);
   const int64_t d_h = kind == 0 ? p.oq_h : (kind == 1 ? p.ck_h : p.cv_h);
   src = reinterpret_cast<const T*>(sbase) + qpos * s_m + g * s_g + head * s_h;
-  dst = reinterpret_cast<T*>(dbase) + (kind == 0 ? qpos : cache_pos) * d_m + g * d_g + head * d_h;
+  const int64_t d_off = (kind == 0 ? qpos : cache_pos) * d_m + g * d_g + head * d_h;
+  if (kQuant && kind != 0)
+    dst = reinterpret_cast<T*>(reinterpret_cast<int32_t*>(dbase) + d_off);
+  else
+    dst = reinterpret_cast<T*>(dbase) + d_off;
+  if (kind_out != nullptr) *kind_out = kind;
   rotate = kind != 2;
 }
 
@@ -106,7 +112,13 @@ __device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, i
 // consecutive tokens of one sequence, so the frequencies (a double-precision
 // power each) are formed once per CTA and the dependent loads of the sequence
 // bookkeeping are paid once.  Shared memory: (cos, sin) per (token, pair).
-template <typename T, bool kF64, bool kVec, bool kAdj>
+// kQuant (vector path, 16-bit T): cache_k / cache_v are int4 row-wise caches, a row
+// = one (fp16 scale | fp16 shift << 16) word and dim / 8 words of nibbles, element
+// e of a word at bits [4e, 4e + 4) (benchmarks/benchmark_attn_decoding.py:38-72):
+// scale = (max - min) / 15 and shift = min of the row, both rounded to fp16,
+// nibble = trunc((x - shift) / scale + 0.5).  The rotated keys are rounded to T
+// first, as if a 16-bit cache had been written and quantised afterwards.
+template <typename T, bool kF64, bool kVec, bool kAdj, bool kQuant = false>
 __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel(const __grid_constant__ xfb200_rope_params p, const int tok_per_cta) {
   extern __shared__ float2 cs_table[];
   __shared__ int cache_rows[kRopeMaxTok];  // cache row of each of the CTA's tokens
@@ -177,6 +189,7 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
       while (t < ntok) {
         uint4 xw[kUnroll], yw[kUnroll];
         T* dst[kUnroll];
+        bool to_int4[kUnroll];
         int tab[kUnroll];  // first (cos, sin) entry of the item, -1: copy only, -2: no item
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -184,8 +197,9 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
           if (t < ntok) {
             const T* src;
             bool rotate;
-            rope_row<T>(p, row, first + t, cache_rows[t], src, dst[u], rotate);
-            dst[u] += x_off;
+            int kind;
+            rope_row<T, kQuant>(p, row, first + t, cache_rows[t], src, dst[u], rotate, &kind);
+            to_int4[u] = kQuant && kind != 0;
             xw[u] = RopeVec<T>::load(src + x_off);
             yw[u] = RopeVec<T>::load(src + y_off);
             tab[u] = rotate ? t * pairs + (kAdj ? v * (E / 2) : v * E) : -1;
@@ -196,10 +210,12 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
           if (tab[u] != -2) {
-            if (tab[u] >= 0) {
-              float x[E], y[E];
+            float x[E], y[E];
+            if (tab[u] >= 0 || to_int4[u]) {
               RopeVec<T>::unpack(xw[u], x);
               RopeVec<T>::unpack(yw[u], y);
+            }
+            if (tab[u] >= 0) {
               if constexpr (kAdj) {
 #pragma unroll
                 for (int i = 0; i < E / 2; ++i) {
@@ -223,8 +239,45 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
               xw[u] = RopeVec<T>::pack(x);
               yw[u] = RopeVec<T>::pack(y);
             }
-            RopeVec<T>::store(dst[u], xw[u]);
-            RopeVec<T>::store(dst[u] + (y_off - x_off), yw[u]);
+            if constexpr (kQuant) {
+              if (to_int4[u]) {
+                if (tab[u] >= 0) {  // the values a 16-bit cache would hold
+                  RopeVec<T>::unpack(xw[u], x);
+                  RopeVec<T>::unpack(yw[u], y);
+                }
+                float mn = x[0], mx = x[0];
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                  mn = fminf(mn, fminf(x[i], y[i]));
+                  mx = fmaxf(mx, fmaxf(x[i], y[i]));
+                }
+                // the `lanes` threads of a row are neighbours in their warp and reach this point together
+                const unsigned gmask = (lanes >= 32 ? 0xffffffffu : ((1u << lanes) - 1u)) << ((threadIdx.x & 31) & ~(lanes - 1));
+                for (int o = 1; o < lanes; o <<= 1) {
+                  mn = fminf(mn, __shfl_xor_sync(gmask, mn, o));
+                  mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, o));
+                }
+                const __half scale_h = __float2half_rn(__fdiv_rn(mx - mn, 15.f)), shift_h = __float2half_rn(mn);
+                const float sc = __half2float(scale_h), sh = __half2float(shift_h);
+                auto nibbles = [&](const float (&z)[E]) {
+                  uint32_t w = 0;
+#pragma unroll
+                  for (int i = 0; i < E; ++i) {
+                    const float qf = __fadd_rn(__fdiv_rn(__fsub_rn(z[i], sh), sc), 0.5f);
+                    const uint32_t qi = qf > 0.f ? uint32_t(qf) : 0u;  // truncation; NaN (a constant row: 0 / 0) gives 0
+                    w |= (qi & 0xFu) << (4 * i);
+                  }
+                  return w;
+                };
+                int32_t* drow = reinterpret_cast<int32_t*>(dst[u]);
+                drow[1 + v] = int32_t(nibbles(x));
+                drow[1 + per_row + v] = int32_t(nibbles(y));
+                if (v == 0) drow[0] = int32_t(uint32_t(__half_as_ushort(scale_h)) | (uint32_t(__half_as_ushort(shift_h)) << 16));
+                continue;
+              }
+            }
+            RopeVec<T>::store(dst[u] + x_off, xw[u]);
+            RopeVec<T>::store(dst[u] + y_off, yw[u]);
           }
         }
       }
@@ -255,9 +308,10 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
   auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
   const int64_t strides[] = {p.xq_m, p.xq_g, p.xq_h, p.xk_m, p.xk_g, p.xk_h, p.xv_m, p.xv_g, p.xv_h,
                              p.oq_m, p.oq_g, p.oq_h, p.ck_m, p.ck_g, p.ck_h, p.cv_m, p.cv_g, p.cv_h};
-  bool vec = p.dim % (2 * E) == 0 && aligned(p.xq) && aligned(p.xk) && aligned(p.xv) &&
-             aligned(p.out_q) && aligned(p.cache_k) && aligned(p.cache_v);
-  for (int64_t s : strides) vec = vec && s % E == 0;
+  const bool quant = p.cache_format == 1;  // int32 rows, written word by word: no vector alignment needed
+  bool vec = p.dim % (2 * E) == 0 && aligned(p.xq) && aligned(p.xk) && aligned(p.xv) && aligned(p.out_q) &&
+             (quant || (aligned(p.cache_k) && aligned(p.cache_v)));
+  for (int i = 0; i < 18; ++i) vec = vec && ((quant && i >= 12) || strides[i] % E == 0);
   const int pairs = p.dim / 2;
   // Tokens per CTA: about 128 KB of rows, while the (cos, sin) table stays within
   // 16 KB and the grid keeps a few CTAs per SM slot.
@@ -275,6 +329,18 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
     kernel<<<grid, kRopeThreads, smem, st>>>(p, tok_per_cta);
     return check_launch("rope_padded_kernel");
   };
+  if (p.cache_format == 1) {
+    // int4 caches: the vector path with a row's threads inside one warp, 16-bit inputs
+    const int per_row = pairs / E;
+    if constexpr (sizeof(T) != 2) {
+      return set_error(XFB200_E_UNSUPPORTED, "rope_padded: an int4 cache needs bf16 or f16 inputs");
+    } else {
+      if (!vec || per_row > 32 || (per_row & (per_row - 1)) != 0)
+        return set_error(XFB200_E_UNSUPPORTED, "rope_padded: an int4 cache needs dim 32, 64, 128, 256 or 512 and 16-byte aligned input rows");
+      if (p.internal_f64) return p.adjacents ? go(rope_padded_kernel<T, true, true, true, true>) : go(rope_padded_kernel<T, true, true, false, true>);
+      return p.adjacents ? go(rope_padded_kernel<T, false, true, true, true>) : go(rope_padded_kernel<T, false, true, false, true>);
+    }
+  }
 #define XFB_ROPE(F64, VEC)                                                                   \
   return p.adjacents ? go(rope_padded_kernel<T, F64, VEC, true>) : go(rope_padded_kernel<T, F64, VEC, false>)
   if (p.internal_f64) {
@@ -298,6 +364,7 @@ extern "C" int xfb200_rope_padded(const xfb200_rope_params* p, void* stream) {
   if (!p->xq || !p->xk || !p->xv || !p->out_q || !p->cache_k || !p->cache_v || !p->seqstart_q || !p->seqstart_k || !p->seqlen_k)
     return set_error(XFB200_E_INVALID, "rope_padded: null tensor pointer");
   if (p->first_seqpos != nullptr && p->seqpos != nullptr) return set_error(XFB200_E_INVALID, "rope_padded: seqpos and first_seqpos may not both be given");
+  if (p->cache_format != 0 && p->cache_format != 1) return set_error(XFB200_E_INVALID, "rope_padded: cache_format %d", p->cache_format);
   if (p->block_tables != nullptr && p->page_size < 1) return set_error(XFB200_E_INVALID, "rope_padded: page_size %d with a page table", p->page_size);
   if (!(p->linear_scale != 0.f)) return set_error(XFB200_E_INVALID, "rope_padded: linear_scale must not be 0");
   if (p->batch > 65535) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: more than 65535 sequences");

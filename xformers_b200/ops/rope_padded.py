@@ -63,7 +63,10 @@ def rope_padded(
     Beyond the reference: with a ``PagedBlockDiagonalCausalWithOffsetPaddedKeysMask``
     the caches are page pools ``[1, pages * page_size, (G,) Hkv, D]`` and key t of
     sequence b is written to row ``block_tables[b, t // page_size] * page_size +
-    t % page_size``, the layout the paged decode operator reads.
+    t % page_size``, the layout the paged decode operator reads; and int32 caches
+    ``[..., 1 + D // 8]`` are int4 row-wise caches (one quantisation group,
+    benchmarks/benchmark_attn_decoding.py:38-72): the rotated keys and the values
+    are quantised as they are written (bf16 / f16 inputs).
     """
     if torch.is_grad_enabled() and (
         xq.requires_grad or xk.requires_grad or xv.requires_grad or cache_k.requires_grad or cache_v.requires_grad or out_q is not None
@@ -94,7 +97,9 @@ def rope_padded(
     mid = (n_groups,) if ndim == 5 else ()
     assert q_len == n_total_queries
     want_x = (1, n_total_queries) + mid + (expected_kv_heads, dim)
-    want_cache = (1, cache_length) + mid + (expected_cache_heads, dim)
+    # int32 caches are int4 row-wise caches with one quantisation group: a scale/shift word and dim / 8 words of nibbles
+    int4_cache = cache_k.dtype == torch.int32
+    want_cache = (1, cache_length) + mid + (expected_cache_heads, 1 + dim // 8 if int4_cache else dim)
     if tuple(xk.shape) != want_x:
         raise ValueError(f"unexpected k shape {tuple(xk.shape)}: expected {want_x}")
     if tuple(xv.shape) != want_x:
@@ -138,8 +143,12 @@ def rope_padded(
     if device.type != "cuda":
         raise ValueError(f"rope_padded needs CUDA tensors, got device={device}")
     tensors = (xq, xk, xv, cache_k, cache_v, out_q)
-    if xq.dtype not in _DTYPES or any(t.dtype != xq.dtype for t in tensors):
-        raise ValueError(f"rope_padded: tensors must share one dtype of bf16 / f16 / f32, got {[t.dtype for t in tensors]}")
+    if xq.dtype not in _DTYPES or any(t.dtype != xq.dtype for t in (xk, xv, out_q)):
+        raise ValueError(f"rope_padded: xq, xk, xv and out_q must share one dtype of bf16 / f16 / f32, got {[t.dtype for t in tensors]}")
+    if cache_v.dtype != cache_k.dtype or cache_k.dtype not in (xq.dtype, torch.int32):
+        raise ValueError(f"rope_padded: the caches must have the dtype of the inputs or be int32 (int4 row-wise), got {cache_k.dtype}, {cache_v.dtype}")
+    if int4_cache and (xq.dtype == torch.float32 or dim % 8):
+        raise ValueError("rope_padded: an int4 cache needs bf16 / f16 inputs and dim a multiple of 8")
     if any(t.device != device for t in tensors) or (positions is not None and positions.device != device):
         raise ValueError("rope_padded: all tensors must be on one device")
     for t in (seqstartq, seqstartk, seqlenk):
@@ -156,6 +165,7 @@ def rope_padded(
     p.batch, p.max_q_per_seq = logical_bsz, attn_bias.q_seqinfo.max_seqlen
     p.q_heads, p.kv_heads, p.groups, p.dim = n_q_heads, n_kv_heads, n_groups, dim
     p.adjacents, p.use_dynamic_scaling, p.internal_f64 = int(adjacents), int(use_dynamic_scaling), int(internal_dtype == "f64")
+    p.cache_format = int(int4_cache)
     p.theta, p.linear_scale = theta, linear_scale
     p.dynamic_old_context_len, p.dynamic_scale_factor = dynamic_old_context_len, dynamic_scale_factor
     p.dynamic_low_freq_factor, p.dynamic_high_freq_factor = dynamic_low_freq_factor, dynamic_high_freq_factor
