@@ -423,3 +423,31 @@ def test_local_window_needs_one_query():
     out = fmha.memory_efficient_attention_forward(q, k, k, bias)
     ro, _ = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), k.float().cpu(), bias.to("cpu"))
     assert (out.float().cpu() - ro).abs().max() <= 2e-2
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,Mkv,H,K", [(1, 2**16, 3, 128), (5, 53, 4, 64), (7, 51, 4, 256), (3, 51, 2, 512)])
+@pytest.mark.parametrize("op", [S.FwOp, None])
+def test_mqa_decoding(op, dtype, B, Mkv, H, K):
+    """tests/test_mem_eff_attention.py:2276-2313: one query, one kv head expanded
+    over H query heads, inputs scaled by 3.  An operator that does not take the
+    shape says so (the reference skips then); the dispatcher finds one for every
+    head size the library covers."""
+    require_cuda()
+    g = torch.Generator(device="cuda").manual_seed(K + B)
+    q = torch.randn(B, 1, H, K, generator=g, device="cuda", dtype=dtype) * 3
+    k = (torch.randn(B, Mkv, 1, K, generator=g, device="cuda", dtype=dtype) * 3).expand(-1, -1, H, -1)
+    v = (torch.randn(B, Mkv, 1, K, generator=g, device="cuda", dtype=dtype) * 3).expand(-1, -1, H, -1)
+    if op is not None:
+        reasons = op.not_supported_reasons(fmha.Inputs(q, k, v))
+        assert bool(reasons) == (K not in (64, 128)), reasons
+        if reasons:
+            pytest.skip("; ".join(reasons))
+    elif K > 256:
+        with pytest.raises(NotImplementedError):
+            fmha.memory_efficient_attention_forward(q, k, v)
+        return
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, op=op)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), None)
+    assert_o_lse(out, lse, ro, rl, dtype, f"mqa decoding K={K}", o_scale=3.0)
