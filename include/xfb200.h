@@ -301,11 +301,19 @@ typedef struct {
   const int32_t* block_tables;
   int64_t block_tables_stride; /* elements between the rows of two sequences */
   int32_t page_size;
-  /* 0: cache_k / cache_v have the dtype of the inputs.  1 (an extension as well): they are int4
+  /* 0: cache_k / cache_v have the dtype of the inputs.  2: see below.  1 (an extension as well): they are int4
    * row-wise caches of int32 rows, 1 + dim / 8 words with one quantisation group
    * (XFB200_KV_INT4_ROWWISE as the decode operator reads it); ck_* / cv_* strides count int32
    * words.  Needs bf16 / f16 inputs, dim a power of two in [32, 512], 16-byte aligned input rows. */
   int32_t cache_format;
+  /* cache_format 2 (an extension as well): fp8 row-wise caches (XFB200_KV_FP8_ROWWISE): cache_k /
+   * cache_v are int32 rows of dim / 4 words (strides in words, rows 8-byte aligned) and every written
+   * row gets its (fp16 scale | fp16 shift << 16) word in these tensors, [cache rows, groups, kv_heads]
+   * with strides in words.  shift = mean of the row, scale = max |x - shift| / 448. */
+  void* k_scale_shift;
+  void* v_scale_shift;
+  int64_t kss_m, kss_g, kss_h;
+  int64_t vss_m, vss_g, vss_h;
 } xfb200_rope_params;
 
 XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);

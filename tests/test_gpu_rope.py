@@ -285,3 +285,92 @@ def test_int4_cache_feeds_decode():
     k_deq, v_deq = oracle.dequantize_kv_int4(ck.cpu()), oracle.dequantize_kv_int4(cv.cpu())
     ref, _ = oracle.ref_attention_with_lse(q5.float().cpu(), k_deq.unsqueeze(3).expand(-1, -1, -1, G, -1), v_deq.unsqueeze(3).expand(-1, -1, -1, G, -1), bias.to("cpu"))
     torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("adjacents", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dim", [64, 128])
+@pytest.mark.parametrize("paged", [False, True])
+def test_fp8_cache_quantised_on_write(paged, dim, dtype, adjacents):
+    """Beyond the reference: cache_k / cache_v are fp8 row-wise caches (InputsFp8,
+    tests/utils.py:134-222).  The format is defined by its dequantiser, x = fp8 *
+    scale + shift: the written rows must dequantise to the oracle's rotated keys
+    and to the values within the e4m3 rounding of x - shift (3 mantissa bits) plus
+    the fp16 rounding of the shift; other rows and scale words keep their bits."""
+    from oracle import fp8 as ofp8
+
+    nq, cache_lens, page = [3, 1, 17], [40, 300, 17], 64
+    B, Hq, Hkv = len(nq), 8, 2
+    g = torch.Generator().manual_seed(dim + int(paged))
+    M = sum(nq)
+    xq = torch.randn(1, M, Hq, dim, generator=g).to(dtype)
+    xk = (torch.randn(1, M, Hkv, dim, generator=g) + 0.5).to(dtype)
+    xv = (torch.randn(1, M, Hkv, dim, generator=g) * 2 - 1).to(dtype)
+    dev = torch.device("cuda")
+    if paged:
+        tables = torch.randperm(B * 5, generator=g).int().view(B, 5)
+        rows_total, starts = B * 5 * page, [0] * B
+        bias = fmha.attn_bias.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(nq, cache_lens, tables, page).to(dev)
+        extra = dict(block_tables=tables.tolist(), page_size=page)
+    else:
+        padding = 320
+        rows_total, starts = B * padding, [b * padding for b in range(B)]
+        bias = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=nq, kv_padding=padding, kv_seqlen=cache_lens).to(dev)
+        extra = {}
+    rnd = lambda *shape: torch.randint(-2**31, 2**31 - 1, shape, generator=g, dtype=torch.int64).to(torch.int32)
+    old_k, old_v = rnd(1, rows_total, Hkv, dim // 4), rnd(1, rows_total, Hkv, dim // 4)
+    old_ks, old_vs = rnd(1, rows_total, Hkv), rnd(1, rows_total, Hkv)
+    ck, cv, ks, vs = old_k.to(dev), old_v.to(dev), old_ks.to(dev), old_vs.to(dev)
+    out = rope_padded(xq.to(dev), xk.to(dev), xv.to(dev), ck, cv, bias, adjacents=adjacents, cache_k_scale_shift=ks, cache_v_scale_shift=vs)
+    z = torch.zeros(1, rows_total, Hkv, dim, dtype=dtype)
+    want_q, want_k, want_v = oracle.rope_padded_ref(xq, xk, xv, z, z, nq, starts, cache_lens, adjacents=adjacents, **extra)
+    torch.testing.assert_close(out.cpu().float(), want_q.float(), atol=5e-3, rtol=8e-3)
+    written = (want_v[0] != 0).flatten(1).any(-1)
+    assert int(written.sum()) == M
+    for got, got_ss, old, old_ss, want in ((ck, ks, old_k, old_ks, want_k), (cv, vs, old_v, old_vs, want_v)):
+        got, got_ss = got.cpu(), got_ss.cpu()
+        assert torch.equal(got[0, ~written], old[0, ~written]) and torch.equal(got_ss[0, ~written], old_ss[0, ~written])
+        scale, shift = ofp8.split_scale_shift(got_ss[0, written])
+        vals = ofp8.unpack_fp8_words(got[0, written]).float()
+        deq = vals * scale.float()[..., None] + shift.float()[..., None]
+        ref = want[0, written].float()
+        # the stored shift is the row mean up to its fp16 rounding, the scale maps the largest |x - shift| to about 448
+        assert ((shift.float() - ref.mean(-1)).abs() <= 2e-3 * ref.mean(-1).abs() + 1e-2).all()
+        assert (vals.abs().amax(-1) >= 416).all() and (vals.abs().amax(-1) <= 448).all()
+        c = ref - shift.float()[..., None]
+        assert ((deq - ref).abs() <= c.abs() * 2**-4 + 2e-2).all()
+        assert ((deq - ref).abs().mean() <= 0.03 * c.abs().mean() + 2e-3)
+
+
+def test_fp8_cache_feeds_decode():
+    """rope_padded -> fp8 cache -> split-K decode, against attention on the
+    dequantised cache."""
+    from oracle import fp8 as ofp8
+
+    nq, cache_lens, padding, D, Hkv, G = [1, 1, 1], [100, 257, 31], 320, 128, 2, 4
+    B = 3
+    g = torch.Generator().manual_seed(6)
+    dev = torch.device("cuda")
+    rows_total = B * padding
+    # earlier keys written by an earlier call (a prefill of the whole slots), then one new token per sequence
+    pre = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=[padding] * B, kv_padding=padding, kv_seqlen=[padding] * B).to(dev)
+    ck = torch.zeros(1, rows_total, Hkv, D // 4, dtype=torch.int32, device=dev)
+    cv, ks, vs = torch.zeros_like(ck), torch.zeros(1, rows_total, Hkv, dtype=torch.int32, device=dev), torch.zeros(1, rows_total, Hkv, dtype=torch.int32, device=dev)
+    big = lambda h: torch.randn(1, rows_total, h, D, generator=g).bfloat16().to(dev)
+    rope_padded(big(Hkv * G), big(Hkv), big(Hkv), ck, cv, pre, cache_k_scale_shift=ks, cache_v_scale_shift=vs)
+    xq = torch.randn(1, B, Hkv * G, D, generator=g).bfloat16()
+    xk, xv = torch.randn(1, B, Hkv, D, generator=g).bfloat16(), torch.randn(1, B, Hkv, D, generator=g).bfloat16()
+    bias = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=nq, kv_padding=padding, kv_seqlen=cache_lens).to(dev)
+    out_q = rope_padded(xq.to(dev), xk.to(dev), xv.to(dev), ck, cv, bias, cache_k_scale_shift=ks, cache_v_scale_shift=vs)
+    q5 = out_q.view(1, B, Hkv, G, D)
+    ex = lambda t: t.unsqueeze(3).expand(-1, -1, -1, G, -1)
+    inp = fmha.triton_splitk.InputsFp8(query=q5, key=ex(ck), value=ex(cv), attn_bias=bias,
+                                       k_fp8_scale_shift=ks.unsqueeze(3).expand(-1, -1, -1, G), v_fp8_scale_shift=vs.unsqueeze(3).expand(-1, -1, -1, G))
+    attn = fmha._memory_efficient_attention_forward(inp, op=fmha.triton_splitk.FwOp)
+
+    def deq(words, ss):
+        scale, shift = ofp8.split_scale_shift(ss.cpu())
+        return ofp8.unpack_fp8_words(words.cpu()).float() * scale.float()[..., None] + shift.float()[..., None]
+
+    ref, _ = oracle.ref_attention_with_lse(q5.float().cpu(), ex(deq(ck, ks)), ex(deq(cv, vs)), bias.to("cpu"))
+    torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)

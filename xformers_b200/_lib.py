@@ -179,6 +179,8 @@ class RopeParams(C.Structure):
         ]
         + [(f"{t}_{a}", C.c_int64) for t in ("xq", "xk", "xv", "oq", "ck", "cv") for a in "mgh"]
         + [("block_tables", C.c_void_p), ("block_tables_stride", C.c_int64), ("page_size", C.c_int32), ("cache_format", C.c_int32)]
+        + [("k_scale_shift", C.c_void_p), ("v_scale_shift", C.c_void_p)]
+        + [(f"{t}_{a}", C.c_int64) for t in ("kss", "vss") for a in "mgh"]
     )
 
 

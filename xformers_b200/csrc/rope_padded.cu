@@ -83,14 +83,18 @@ struct RopeVec {
 // source and destination of row `row` (q rows, then k rows, then v rows) of the
 // token at row `qpos` of the inputs and row `cache_pos` of the caches
 // (an int4 cache has int32 rows: its strides count words)
-template <typename T, bool kQuant = false>
-__device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, int qpos, int cache_pos, const T*& src, T*& dst, bool& rotate, int* kind_out = nullptr) {
+template <typename T, int kQuant = 0>
+__device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, int qpos, int cache_pos, const T*& src, T*& dst, bool& rotate, int* kind_out = nullptr,
+                                         int32_t** ss_out = nullptr) {
   int head = row, g = 0;
   if (p.groups != 1) head = row / p.groups, g = row - head * p.groups;
   const int kind = (head >= p.q_heads) + (head >= p.q_heads + p.kv_heads);  // 0 q, 1 k, 2 v
   head -= kind == 0 ? 0 : (kind == 1 ? p.q_heads : p.q_heads + p.kv_heads);
   const void* sbase = kind == 0 ? p.xq : (kind == 1 ? p.xk : p.xv);
   void* dbase = kind == 0 ? p.out_q : (kind == 1 ? p.cache_k : p.cache_v);
+  if (ss_out != nullptr && kind != 0)  // fp8 caches: where this row's scale/shift word goes
+    *ss_out = reinterpret_cast<int32_t*>(kind == 1 ? p.k_scale_shift : p.v_scale_shift) + int64_t(cache_pos) * (kind == 1 ? p.kss_m : p.vss_m) +
+              int64_t(g) * (kind == 1 ? p.kss_g : p.vss_g) + int64_t(head) * (kind == 1 ? p.kss_h : p.vss_h);
   const int64_t s_m = kind == 0 ? p.xq_m : (kind == 1 ? p.xk_m : p.xv_m);
   const int64_t s_g = kind == 0 ? p.xq_g : (kind == 1 ? p.xk_g : p.xv_g);
   const int64_t s_h = kind == 0 ? p.xq_h : (kind == 1 ? p.xk_h : p.xv_h);
@@ -118,7 +122,12 @@ __device__ __forceinline__ void rope_row(const xfb200_rope_params& p, int row, i
 // scale = (max - min) / 15 and shift = min of the row, both rounded to fp16,
 // nibble = trunc((x - shift) / scale + 0.5).  The rotated keys are rounded to T
 // first, as if a 16-bit cache had been written and quantised afterwards.
-template <typename T, bool kF64, bool kVec, bool kAdj, bool kQuant = false>
+// kQuant == 2: fp8 row-wise caches (XFB200_KV_FP8_ROWWISE): int32 rows of dim / 4
+// words of four e4m3 values and one (fp16 scale | fp16 shift << 16) word per row in
+// a tensor of its own, x ~ fp8 * scale + shift.  shift = the row's mean, scale =
+// max |x - shift| / 448, both rounded to fp16 before they are used, values rounded
+// to nearest with saturation.
+template <typename T, bool kF64, bool kVec, bool kAdj, int kQuant = 0>
 __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel(const __grid_constant__ xfb200_rope_params p, const int tok_per_cta) {
   extern __shared__ float2 cs_table[];
   __shared__ int cache_rows[kRopeMaxTok];  // cache row of each of the CTA's tokens
@@ -189,7 +198,8 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
       while (t < ntok) {
         uint4 xw[kUnroll], yw[kUnroll];
         T* dst[kUnroll];
-        bool to_int4[kUnroll];
+        bool to_int4[kUnroll];  // the row goes to a quantised cache
+        int32_t* ss_dst[kUnroll];
         int tab[kUnroll];  // first (cos, sin) entry of the item, -1: copy only, -2: no item
 #pragma unroll
         for (int u = 0; u < kUnroll; ++u) {
@@ -198,8 +208,8 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
             const T* src;
             bool rotate;
             int kind;
-            rope_row<T, kQuant>(p, row, first + t, cache_rows[t], src, dst[u], rotate, &kind);
-            to_int4[u] = kQuant && kind != 0;
+            rope_row<T, kQuant>(p, row, first + t, cache_rows[t], src, dst[u], rotate, &kind, kQuant == 2 ? &ss_dst[u] : nullptr);
+            to_int4[u] = kQuant != 0 && kind != 0;
             xw[u] = RopeVec<T>::load(src + x_off);
             yw[u] = RopeVec<T>::load(src + y_off);
             tab[u] = rotate ? t * pairs + (kAdj ? v * (E / 2) : v * E) : -1;
@@ -253,6 +263,36 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
                 }
                 // the `lanes` threads of a row are neighbours in their warp and reach this point together
                 const unsigned gmask = (lanes >= 32 ? 0xffffffffu : ((1u << lanes) - 1u)) << ((threadIdx.x & 31) & ~(lanes - 1));
+                if constexpr (kQuant == 2) {
+                  float sum = 0.f;
+#pragma unroll
+                  for (int i = 0; i < E; ++i) sum += x[i] + y[i];
+                  for (int o = 1; o < lanes; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
+                  const __half shift_h = __float2half_rn(__fdiv_rn(sum, float(p.dim)));
+                  const float sh = __half2float(shift_h);
+                  float amax = 0.f;
+#pragma unroll
+                  for (int i = 0; i < E; ++i) {
+                    x[i] -= sh, y[i] -= sh;
+                    amax = fmaxf(amax, fmaxf(fabsf(x[i]), fabsf(y[i])));
+                  }
+                  for (int o = 1; o < lanes; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+                  __half scale_h = __float2half_rn(__fdiv_rn(amax, 448.f));
+                  if (__half2float(scale_h) == 0.f) scale_h = __float2half_rn(1.f);  // a constant row: every value is 0 * 1 + shift
+                  const float inv = __fdiv_rn(1.f, __half2float(scale_h));
+                  auto e4m3x4 = [&](float a0, float a1, float a2, float a3) {
+                    uint32_t lo, hi;
+                    asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(lo) : "f"(a0 * inv), "f"(a1 * inv));
+                    asm("{\n\t.reg .b16 t;\n\tcvt.rn.satfinite.e4m3x2.f32 t, %2, %1;\n\tcvt.u32.u16 %0, t;\n\t}" : "=r"(hi) : "f"(a2 * inv), "f"(a3 * inv));
+                    return lo | (hi << 16);
+                  };
+                  int32_t* drow = reinterpret_cast<int32_t*>(dst[u]);
+                  // x holds the elements [8 v, 8 v + 8) of the row, y the same of its second half: two words each
+                  *reinterpret_cast<uint2*>(drow + 2 * v) = make_uint2(e4m3x4(x[0], x[1], x[2], x[3]), e4m3x4(x[4], x[5], x[6], x[7]));
+                  *reinterpret_cast<uint2*>(drow + 2 * per_row + 2 * v) = make_uint2(e4m3x4(y[0], y[1], y[2], y[3]), e4m3x4(y[4], y[5], y[6], y[7]));
+                  if (v == 0) *ss_dst[u] = int32_t(uint32_t(__half_as_ushort(scale_h)) | (uint32_t(__half_as_ushort(shift_h)) << 16));
+                  continue;
+                }
                 for (int o = 1; o < lanes; o <<= 1) {
                   mn = fminf(mn, __shfl_xor_sync(gmask, mn, o));
                   mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, o));
@@ -308,7 +348,7 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
   auto aligned = [](const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; };
   const int64_t strides[] = {p.xq_m, p.xq_g, p.xq_h, p.xk_m, p.xk_g, p.xk_h, p.xv_m, p.xv_g, p.xv_h,
                              p.oq_m, p.oq_g, p.oq_h, p.ck_m, p.ck_g, p.ck_h, p.cv_m, p.cv_g, p.cv_h};
-  const bool quant = p.cache_format == 1;  // int32 rows, written word by word: no vector alignment needed
+  const bool quant = p.cache_format != 0;  // int32 rows, written word by word (fp8: 8 bytes at a time, checked below)
   bool vec = p.dim % (2 * E) == 0 && aligned(p.xq) && aligned(p.xk) && aligned(p.xv) && aligned(p.out_q) &&
              (quant || (aligned(p.cache_k) && aligned(p.cache_v)));
   for (int i = 0; i < 18; ++i) vec = vec && ((quant && i >= 12) || strides[i] % E == 0);
@@ -329,6 +369,17 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
     kernel<<<grid, kRopeThreads, smem, st>>>(p, tok_per_cta);
     return check_launch("rope_padded_kernel");
   };
+  if (p.cache_format == 2) {
+    const int per_row = pairs / E;
+    if constexpr (sizeof(T) != 2) {
+      return set_error(XFB200_E_UNSUPPORTED, "rope_padded: an fp8 cache needs bf16 or f16 inputs");
+    } else {
+      if (!vec || per_row > 32 || (per_row & (per_row - 1)) != 0)
+        return set_error(XFB200_E_UNSUPPORTED, "rope_padded: an fp8 cache needs dim 32, 64, 128, 256 or 512 and 16-byte aligned input rows");
+      if (p.internal_f64) return p.adjacents ? go(rope_padded_kernel<T, true, true, true, 2>) : go(rope_padded_kernel<T, true, true, false, 2>);
+      return p.adjacents ? go(rope_padded_kernel<T, false, true, true, 2>) : go(rope_padded_kernel<T, false, true, false, 2>);
+    }
+  }
   if (p.cache_format == 1) {
     // int4 caches: the vector path with a row's threads inside one warp, 16-bit inputs
     const int per_row = pairs / E;
@@ -337,8 +388,8 @@ int launch_rope(const xfb200_rope_params& p, cudaStream_t st) {
     } else {
       if (!vec || per_row > 32 || (per_row & (per_row - 1)) != 0)
         return set_error(XFB200_E_UNSUPPORTED, "rope_padded: an int4 cache needs dim 32, 64, 128, 256 or 512 and 16-byte aligned input rows");
-      if (p.internal_f64) return p.adjacents ? go(rope_padded_kernel<T, true, true, true, true>) : go(rope_padded_kernel<T, true, true, false, true>);
-      return p.adjacents ? go(rope_padded_kernel<T, false, true, true, true>) : go(rope_padded_kernel<T, false, true, false, true>);
+      if (p.internal_f64) return p.adjacents ? go(rope_padded_kernel<T, true, true, true, 1>) : go(rope_padded_kernel<T, true, true, false, 1>);
+      return p.adjacents ? go(rope_padded_kernel<T, false, true, true, 1>) : go(rope_padded_kernel<T, false, true, false, 1>);
     }
   }
 #define XFB_ROPE(F64, VEC)                                                                   \
@@ -364,7 +415,14 @@ extern "C" int xfb200_rope_padded(const xfb200_rope_params* p, void* stream) {
   if (!p->xq || !p->xk || !p->xv || !p->out_q || !p->cache_k || !p->cache_v || !p->seqstart_q || !p->seqstart_k || !p->seqlen_k)
     return set_error(XFB200_E_INVALID, "rope_padded: null tensor pointer");
   if (p->first_seqpos != nullptr && p->seqpos != nullptr) return set_error(XFB200_E_INVALID, "rope_padded: seqpos and first_seqpos may not both be given");
-  if (p->cache_format != 0 && p->cache_format != 1) return set_error(XFB200_E_INVALID, "rope_padded: cache_format %d", p->cache_format);
+  if (p->cache_format < 0 || p->cache_format > 2) return set_error(XFB200_E_INVALID, "rope_padded: cache_format %d", p->cache_format);
+  if (p->cache_format == 2) {
+    if (p->k_scale_shift == nullptr || p->v_scale_shift == nullptr) return set_error(XFB200_E_INVALID, "rope_padded: an fp8 cache needs its scale/shift tensors");
+    const int64_t st[] = {p->ck_m, p->ck_g, p->ck_h, p->cv_m, p->cv_g, p->cv_h};
+    bool ok = (reinterpret_cast<uintptr_t>(p->cache_k) & 7) == 0 && (reinterpret_cast<uintptr_t>(p->cache_v) & 7) == 0;
+    for (int64_t s : st) ok = ok && s % 2 == 0;
+    if (!ok) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: fp8 cache rows must be 8-byte aligned");
+  }
   if (p->block_tables != nullptr && p->page_size < 1) return set_error(XFB200_E_INVALID, "rope_padded: page_size %d with a page table", p->page_size);
   if (!(p->linear_scale != 0.f)) return set_error(XFB200_E_INVALID, "rope_padded: linear_scale must not be 0");
   if (p->batch > 65535) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: more than 65535 sequences");

@@ -44,6 +44,8 @@ def rope_padded(
     seqpos: Optional[torch.Tensor] = None,
     adjacents: bool = True,
     internal_dtype: str = "",
+    cache_k_scale_shift: Optional[torch.Tensor] = None,
+    cache_v_scale_shift: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Rotate ``xq`` into ``out_q`` (returned), rotate ``xk`` into its rows of
     ``cache_k`` and copy ``xv`` into the same rows of ``cache_v`` (both caches
@@ -66,7 +68,12 @@ def rope_padded(
     t % page_size``, the layout the paged decode operator reads; and int32 caches
     ``[..., 1 + D // 8]`` are int4 row-wise caches (one quantisation group,
     benchmarks/benchmark_attn_decoding.py:38-72): the rotated keys and the values
-    are quantised as they are written (bf16 / f16 inputs).
+    are quantised as they are written (bf16 / f16 inputs).  With
+    ``cache_k_scale_shift`` / ``cache_v_scale_shift`` (int32, the caches' shape
+    without the last axis) int32 caches ``[..., D // 4]`` are fp8 row-wise caches
+    (``InputsFp8``, tests/utils.py:134-222): four e4m3 values per word, ``x ~ fp8 *
+    scale + shift`` with the row's (fp16 scale | fp16 shift << 16) word written to
+    those tensors (shift = row mean, scale = max |x - shift| / 448).
     """
     if torch.is_grad_enabled() and (
         xq.requires_grad or xk.requires_grad or xv.requires_grad or cache_k.requires_grad or cache_v.requires_grad or out_q is not None
@@ -98,8 +105,9 @@ def rope_padded(
     assert q_len == n_total_queries
     want_x = (1, n_total_queries) + mid + (expected_kv_heads, dim)
     # int32 caches are int4 row-wise caches with one quantisation group: a scale/shift word and dim / 8 words of nibbles
-    int4_cache = cache_k.dtype == torch.int32
-    want_cache = (1, cache_length) + mid + (expected_cache_heads, 1 + dim // 8 if int4_cache else dim)
+    fp8_cache = cache_k_scale_shift is not None or cache_v_scale_shift is not None
+    int4_cache = cache_k.dtype == torch.int32 and not fp8_cache
+    want_cache = (1, cache_length) + mid + (expected_cache_heads, dim // 4 if fp8_cache else 1 + dim // 8 if int4_cache else dim)
     if tuple(xk.shape) != want_x:
         raise ValueError(f"unexpected k shape {tuple(xk.shape)}: expected {want_x}")
     if tuple(xv.shape) != want_x:
@@ -147,8 +155,14 @@ def rope_padded(
         raise ValueError(f"rope_padded: xq, xk, xv and out_q must share one dtype of bf16 / f16 / f32, got {[t.dtype for t in tensors]}")
     if cache_v.dtype != cache_k.dtype or cache_k.dtype not in (xq.dtype, torch.int32):
         raise ValueError(f"rope_padded: the caches must have the dtype of the inputs or be int32 (int4 row-wise), got {cache_k.dtype}, {cache_v.dtype}")
-    if int4_cache and (xq.dtype == torch.float32 or dim % 8):
-        raise ValueError("rope_padded: an int4 cache needs bf16 / f16 inputs and dim a multiple of 8")
+    if (int4_cache or fp8_cache) and (xq.dtype == torch.float32 or dim % 8):
+        raise ValueError("rope_padded: a quantised cache needs bf16 / f16 inputs and dim a multiple of 8")
+    if fp8_cache:
+        if cache_k.dtype != torch.int32:
+            raise ValueError("rope_padded: fp8 caches are int32 tensors of four e4m3 values per word")
+        for name, t in (("cache_k_scale_shift", cache_k_scale_shift), ("cache_v_scale_shift", cache_v_scale_shift)):
+            if t is None or t.dtype != torch.int32 or tuple(t.shape) != tuple(cache_k.shape[:-1]) or t.device != device:
+                raise ValueError(f"rope_padded: {name} must be an int32 tensor of shape {tuple(cache_k.shape[:-1])} on the device of the caches")
     if any(t.device != device for t in tensors) or (positions is not None and positions.device != device):
         raise ValueError("rope_padded: all tensors must be on one device")
     for t in (seqstartq, seqstartk, seqlenk):
@@ -165,7 +179,11 @@ def rope_padded(
     p.batch, p.max_q_per_seq = logical_bsz, attn_bias.q_seqinfo.max_seqlen
     p.q_heads, p.kv_heads, p.groups, p.dim = n_q_heads, n_kv_heads, n_groups, dim
     p.adjacents, p.use_dynamic_scaling, p.internal_f64 = int(adjacents), int(use_dynamic_scaling), int(internal_dtype == "f64")
-    p.cache_format = int(int4_cache)
+    p.cache_format = 2 if fp8_cache else int(int4_cache)
+    if fp8_cache:
+        p.k_scale_shift, p.v_scale_shift = cache_k_scale_shift.data_ptr(), cache_v_scale_shift.data_ptr()
+        p.kss_m, p.kss_g, p.kss_h = _strides3(cache_k_scale_shift.unsqueeze(-1), ndim)
+        p.vss_m, p.vss_g, p.vss_h = _strides3(cache_v_scale_shift.unsqueeze(-1), ndim)
     p.theta, p.linear_scale = theta, linear_scale
     p.dynamic_old_context_len, p.dynamic_scale_factor = dynamic_old_context_len, dynamic_scale_factor
     p.dynamic_low_freq_factor, p.dynamic_high_freq_factor = dynamic_low_freq_factor, dynamic_high_freq_factor
