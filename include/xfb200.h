@@ -314,6 +314,11 @@ typedef struct {
   void* v_scale_shift;
   int64_t kss_m, kss_g, kss_h;
   int64_t vss_m, vss_g, vss_h;
+  /* paged caches: entries per row of block_tables.  A key position outside [0, pages_per_seq *
+   * page_size) -- or, flat caches, outside the sequence's slot seqstart_k[b] .. seqstart_k[b+1] -- is
+   * not written. */
+  int32_t pages_per_seq;
+  int32_t reserved;
 } xfb200_rope_params;
 
 XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);

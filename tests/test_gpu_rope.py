@@ -374,3 +374,34 @@ def test_fp8_cache_feeds_decode():
 
     ref, _ = oracle.ref_attention_with_lse(q5.float().cpu(), ex(deq(ck, ks)), ex(deq(cv, vs)), bias.to("cpu"))
     torch.testing.assert_close(attn.float().cpu(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("paged", [False, True])
+def test_lengths_that_do_not_fit_write_nothing_outside_the_slot(paged):
+    """The lengths live on the device and may be updated in place between calls
+    (examples/llama_inference/generate.py:144-187).  If they stop fitting the
+    layout -- fewer keys than new queries, or more keys than the slot holds -- the
+    positions outside the slot are skipped instead of landing in a neighbour's
+    rows; the positions inside it are written as usual."""
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(2)
+    nq, page, D, H = [4, 4, 4], 16, 64, 2
+    B, M = 3, 12
+    xq = torch.randn(1, M, H, D, generator=g).bfloat16().to(dev)
+    xk, xv = torch.randn(1, M, H, D, generator=g).bfloat16().to(dev), torch.randn(1, M, H, D, generator=g).bfloat16().to(dev)
+    if paged:
+        tables = torch.tensor([[2, 5], [0, 3], [4, 1]], dtype=torch.int32)
+        bias = fmha.attn_bias.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(nq, [10, 10, 10], tables, page).to(dev)
+        row_of = lambda b, t: int(tables[b, t // page]) * page + t % page
+    else:
+        bias = fmha.attn_bias.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens(q_seqlen=nq, kv_padding=2 * page, kv_seqlen=[10, 10, 10]).to(dev)
+        row_of = lambda b, t: b * 2 * page + t
+    # sequence 0: 2 keys for 4 queries (positions -2, -1, 0, 1); sequence 1 fits; sequence 2: 34 keys in a slot of 32 (positions 30 .. 33)
+    bias.k_seqinfo.seqlen.copy_(torch.tensor([2, 10, 34], dtype=torch.int32))
+    ck = torch.zeros(1, 6 * page, H, D, dtype=torch.bfloat16, device=dev)
+    cv = torch.zeros_like(ck)
+    rope_padded(xq, xk, xv, ck, cv, bias)
+    written = set(torch.nonzero(cv[0].float().abs().flatten(1).sum(-1)).flatten().tolist())
+    want = {row_of(0, 0), row_of(0, 1)} | {row_of(1, t) for t in range(6, 10)} | {row_of(2, 30), row_of(2, 31)}
+    assert written == want
+    assert torch.equal(cv[0, row_of(0, 0)], xv[0, 2]) and torch.equal(cv[0, row_of(2, 31)], xv[0, 9])

@@ -181,6 +181,7 @@ class RopeParams(C.Structure):
         + [("block_tables", C.c_void_p), ("block_tables_stride", C.c_int64), ("page_size", C.c_int32), ("cache_format", C.c_int32)]
         + [("k_scale_shift", C.c_void_p), ("v_scale_shift", C.c_void_p)]
         + [(f"{t}_{a}", C.c_int64) for t in ("kss", "vss") for a in "mgh"]
+        + [("pages_per_seq", C.c_int32), ("reserved", C.c_int32)]
     )
 
 

@@ -142,10 +142,14 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
   // which is row cache_start + slot_first + t of a flat cache, or goes through the page table
   const int slot_first = p.seqlen_k[b] - (q1 - first);
   if (int(threadIdx.x) < ntok) {
+    // a key position outside the sequence's slot (lengths that do not fit the layout) is not written: row -1
     const int pos = slot_first + int(threadIdx.x);
-    cache_rows[threadIdx.x] = p.block_tables != nullptr
-                                  ? p.block_tables[int64_t(b) * p.block_tables_stride + pos / p.page_size] * p.page_size + pos % p.page_size
-                                  : cache_start + pos;
+    const int slot_rows = p.block_tables != nullptr ? p.pages_per_seq * p.page_size : p.seqstart_k[b + 1] - cache_start;
+    int row = -1;
+    if (pos >= 0 && pos < slot_rows)
+      row = p.block_tables != nullptr ? p.block_tables[int64_t(b) * p.block_tables_stride + pos / p.page_size] * p.page_size + pos % p.page_size
+                                      : cache_start + pos;
+    cache_rows[threadIdx.x] = row;
   }
   auto position = [&](const void* base, int64_t i) -> long long {
     return p.seqpos_i64 ? reinterpret_cast<const long long*>(base)[i * p.seqpos_stride]
@@ -210,9 +214,11 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
             int kind;
             rope_row<T, kQuant>(p, row, first + t, cache_rows[t], src, dst[u], rotate, &kind, kQuant == 2 ? &ss_dst[u] : nullptr);
             to_int4[u] = kQuant != 0 && kind != 0;
-            xw[u] = RopeVec<T>::load(src + x_off);
-            yw[u] = RopeVec<T>::load(src + y_off);
-            tab[u] = rotate ? t * pairs + (kAdj ? v * (E / 2) : v * E) : -1;
+            if (kind == 0 || cache_rows[t] >= 0) {
+              xw[u] = RopeVec<T>::load(src + x_off);
+              yw[u] = RopeVec<T>::load(src + y_off);
+              tab[u] = rotate ? t * pairs + (kAdj ? v * (E / 2) : v * E) : -1;
+            }
             row += nslots;
             while (row >= rows) row -= rows, ++t;
           }
@@ -331,7 +337,9 @@ __global__ void __launch_bounds__(kRopeThreads, kVec ? 4 : 2) rope_padded_kernel
       const T* src;
       T* dst;
       bool rotate;
-      rope_row<T>(p, row, first + t, cache_rows[t], src, dst, rotate);
+      int kind;
+      rope_row<T>(p, row, first + t, cache_rows[t], src, dst, rotate, &kind);
+      if (kind != 0 && cache_rows[t] < 0) continue;
       const int c_re = kAdj ? 2 * j : j;
       const int c_im = kAdj ? 2 * j + 1 : j + pairs;
       const float2 w = cs_table[t * pairs + j];
@@ -423,6 +431,7 @@ extern "C" int xfb200_rope_padded(const xfb200_rope_params* p, void* stream) {
     for (int64_t s : st) ok = ok && s % 2 == 0;
     if (!ok) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: fp8 cache rows must be 8-byte aligned");
   }
+  if (p->block_tables != nullptr && p->pages_per_seq < 1) return set_error(XFB200_E_INVALID, "rope_padded: pages_per_seq %d with a page table", p->pages_per_seq);
   if (p->block_tables != nullptr && p->page_size < 1) return set_error(XFB200_E_INVALID, "rope_padded: page_size %d with a page table", p->page_size);
   if (!(p->linear_scale != 0.f)) return set_error(XFB200_E_INVALID, "rope_padded: linear_scale must not be 0");
   if (p->batch > 65535) return set_error(XFB200_E_UNSUPPORTED, "rope_padded: more than 65535 sequences");

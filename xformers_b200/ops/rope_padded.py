@@ -198,6 +198,7 @@ def rope_padded(
         if tables.device != device or tables.dtype != torch.int32 or tables.ndim != 2 or tables.shape[0] != logical_bsz or tables.stride(1) != 1:
             raise ValueError("`attn_bias.block_tables` must be an int32 [batch, pages] tensor with unit inner stride on the same device as the other inputs")
         p.block_tables, p.block_tables_stride, p.page_size = tables.data_ptr(), tables.stride(0), attn_bias.page_size
+        p.pages_per_seq = tables.shape[1]
     with torch.cuda.device(device):
         rc = _lib.load().xfb200_rope_padded(C.byref(p), C.c_void_p(torch.cuda.current_stream(device).cuda_stream))
     _lib.check(rc, "rope_padded")
