@@ -267,6 +267,32 @@ def test_sharded_keys_merge_to_full_causal(op, shards):
 
 
 @gpu
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_zigzag_key_ranges_merge_to_full_causal(world):
+    """The balanced layout of the long-context path on one GPU: every emulated
+    rank runs sharded_kv_attention_forward on its two key ranges (which merges
+    them locally; no process group, so no exchange), and the merge of the ranks'
+    results equals the full causal attention."""
+    from xformers_b200.ops.fmha.sharded import sharded_kv_attention_forward, zigzag_bounds
+
+    require_cuda()
+    dtype = torch.bfloat16
+    B, S, G, H, D = 1, 1536, 2, 4, 128
+    q, k, v = rand_qkv(B, S, S, G, H, D, dtype, seed=6, gqa=True)
+    outs, lses = [], []
+    for r in range(world):
+        spans = zigzag_bounds(S, world, r)
+        o, l = sharded_kv_attention_forward(q, [k[:, a:b] for a, b in spans], [v[:, a:b] for a, b in spans],
+                                            kv_offset=[a for a, _ in spans], causal=True, partial_dtype=torch.float32)
+        outs.append(o.float())
+        lses.append(l)
+    merged, lse_m = fmha.merge_attentions(outs, lses, output_dtype=dtype)
+    ro, rl = ref(q, k, v, ab.LowerTriangularMask())
+    assert_o_lse(merged, lse_m, ro, rl, dtype, f"zigzag world={world}")
+    _status_ok()
+
+
+@gpu
 def test_partial_chunks_merge_to_full_decode():
     # tests/test_fmha_merge_attentions.py:234-363: chunked attention + merge == full (1e-3 there)
     require_cuda()

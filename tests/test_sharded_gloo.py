@@ -30,10 +30,10 @@ def _cpu_merge(outs, lses, out_dtype):
     return oracle.merge_attentions_ref(outs, lses)
 
 
-def _worker(rank, world, init_file, fail_rank, result_file):
+def _worker(rank, world, init_file, fail_rank, result_file, zigzag=False):
     sys.path.insert(0, ROOT)
     import oracle
-    from xformers_b200.ops.fmha.sharded import shard_bounds, sharded_kv_attention_forward
+    from xformers_b200.ops.fmha.sharded import shard_bounds, sharded_kv_attention_forward, zigzag_bounds
 
     dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world)
     try:
@@ -45,9 +45,16 @@ def _worker(rank, world, init_file, fail_rank, result_file):
         lo, hi = shard_bounds(S, world, rank)
         if rank == fail_rank:
             raise RuntimeError("injected host-side failure before the collective")
-        out, lse = sharded_kv_attention_forward(
-            q, k[:, lo:hi], v[:, lo:hi], kv_offset=lo, causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge
-        )
+        if zigzag:
+            spans = zigzag_bounds(S, world, rank)
+            out, lse = sharded_kv_attention_forward(
+                q, [k[:, a:b] for a, b in spans], [v[:, a:b] for a, b in spans], kv_offset=[a for a, _ in spans],
+                causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge,
+            )
+        else:
+            out, lse = sharded_kv_attention_forward(
+                q, k[:, lo:hi], v[:, lo:hi], kv_offset=lo, causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge
+            )
         ro, rl = oracle.ref_attention_with_lse(q, k, v, oracle.causal_mask(S, S))
         ok = bool((out - ro).abs().max() < 1e-5 and (lse - rl).abs().max() < 1e-5)
         with open(f"{result_file}.{rank}", "w") as f:
@@ -66,6 +73,28 @@ def test_shard_bounds_cover_the_sequence():
             for (a, b), (c, d) in zip(spans, spans[1:]):
                 assert b == c and a <= b
             assert all(a % 128 == 0 for a, _ in spans if a < total)
+
+
+def test_zigzag_bounds_cover_the_sequence_and_balance_causal_work():
+    from xformers_b200.ops.fmha.sharded import zigzag_bounds
+
+    for total in (1, 127, 300, 1024, 131072):
+        for world in (1, 2, 3, 4, 8):
+            spans = sorted(sp for r in range(world) for sp in zigzag_bounds(total, world, r))
+            assert spans[0][0] == 0 and max(b for _, b in spans) == total
+            for (a, b), (c, d) in zip(spans, spans[1:]):
+                assert b == c and a <= b  # the 2 * world chunks tile the sequence in order
+    # visible (query, key) pairs per rank under a causal mask: equal up to the chunk granularity
+    total, world = 131072, 8
+    work = [sum((total - a) * (b - a) - (b - a) * (b - a - 1) // 2 for a, b in zigzag_bounds(total, world, r)) for r in range(world)]
+    assert max(work) / min(work) < 1.001
+
+
+def test_two_rank_zigzag_shards_match_full():
+    with tempfile.TemporaryDirectory() as tmp:
+        init, res = os.path.join(tmp, "init"), os.path.join(tmp, "res")
+        mp.spawn(_worker, args=(2, init, -1, res, True), nprocs=2, join=True)
+        assert [open(f"{res}.{r}").read() for r in range(2)] == ["ok", "ok"]
 
 
 def test_two_rank_gather_and_merge_matches_full():

@@ -9,12 +9,14 @@ different GPUs of one NVSwitch box: rank r holds the contiguous key range
 queries against its shard with the causal diagonal shifted by ``kv_offset_r``,
 and the per-rank ``(O_r, LSE_r)`` are exchanged with one NCCL all-gather over
 NVLink and combined by the same LSE-merge kernel.  Query rows that lie before a
-shard see none of its keys and arrive with ``LSE = -inf`` (weight 0).
+shard see none of its keys and arrive with ``LSE = -inf`` (weight 0).  For
+balanced causal work a rank may hold the two key ranges of :func:`zigzag_bounds`
+instead; it then merges its own two partials before the exchange.
 """
 
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Tuple
+from typing import Callable, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -29,6 +31,22 @@ def shard_bounds(total: int, world_size: int, rank: int) -> Tuple[int, int]:
     per = -(-per // 128) * 128
     lo = min(total, rank * per)
     return lo, min(total, lo + per)
+
+
+def zigzag_bounds(total: int, world_size: int, rank: int) -> List[Tuple[int, int]]:
+    """Two 128-aligned key ranges per rank: chunks ``rank`` and ``2 * world_size -
+    1 - rank`` of ``2 * world_size``.  Under a causal mask every query sees all of
+    an early chunk and little of a late one; pairing them gives every rank the
+    same number of visible (query, key) pairs, which contiguous shards do not
+    (their slowest rank does about twice the average)."""
+    per = -(-total // (2 * world_size))
+    per = -(-per // 128) * 128
+
+    def span(c: int) -> Tuple[int, int]:
+        lo = min(total, c * per)
+        return lo, min(total, lo + per)
+
+    return [span(rank), span(2 * world_size - 1 - rank)]
 
 
 def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype):
@@ -51,10 +69,10 @@ def _merge_on_gpu(outs, lses, out_dtype):
 
 def sharded_kv_attention_forward(
     query: torch.Tensor,
-    key_shard: torch.Tensor,
-    value_shard: torch.Tensor,
+    key_shard: Union[torch.Tensor, Sequence[torch.Tensor]],
+    value_shard: Union[torch.Tensor, Sequence[torch.Tensor]],
     *,
-    kv_offset: int,
+    kv_offset: Union[int, Sequence[int]],
     causal: bool = True,
     scale: Optional[float] = None,
     group: Optional[dist.ProcessGroup] = None,
@@ -64,13 +82,33 @@ def sharded_kv_attention_forward(
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
     key/value shard ``[B, len_r, (G,) H, D]`` starting at global key index
-    ``kv_offset``.  Returns the full ``(out, lse)`` on every rank.
+    ``kv_offset``.  Returns the full ``(out, lse)`` on every rank.  Several key
+    ranges per rank are passed as sequences of shards and offsets (empty ranges
+    are skipped); the rank merges their partials before the exchange.
 
     ``partial_fn`` / ``merge_fn`` exist so that the exchange logic can be
     exercised with CPU stand-ins under the gloo backend.
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    out_r, lse_r = partial_fn(query, key_shard, value_shard, causal, kv_offset, scale, partial_dtype)
+    if isinstance(key_shard, torch.Tensor):
+        key_shard, value_shard, kv_offset = [key_shard], [value_shard], [kv_offset]
+    if not (len(key_shard) == len(value_shard) == len(kv_offset)) or not len(key_shard):
+        raise ValueError("sharded attention: key shards, value shards and offsets must pair up")
+    parts = [
+        partial_fn(query, k, v, causal, off, scale, partial_dtype)
+        for k, v, off in zip(key_shard, value_shard, kv_offset)
+        if k.shape[1] > 0
+    ]
+    if not parts:
+        # this rank holds no keys at all: a partial of weight 0, shaped like a neighbour's (one key, then discarded)
+        k0, v0 = key_shard[0], value_shard[0]
+        one = lambda t: t.new_zeros((t.shape[0], 1) + tuple(t.shape[2:]))
+        out_r, lse_r = partial_fn(query, one(k0), one(v0), False, 0, scale, partial_dtype)
+        out_r, lse_r = torch.zeros_like(out_r), torch.full_like(lse_r, float("-inf"))
+    elif len(parts) == 1:
+        out_r, lse_r = parts[0]
+    else:
+        out_r, lse_r = merge_fn([p[0] for p in parts], [p[1] for p in parts], parts[0][0].dtype)
     if world == 1:
         return merge_fn([out_r], [lse_r], query.dtype)
     out_r = out_r.contiguous()
