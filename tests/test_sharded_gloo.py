@@ -51,6 +51,12 @@ def _worker(rank, world, init_file, fail_rank, result_file, zigzag=False):
                 q, [k[:, a:b] for a, b in spans], [v[:, a:b] for a, b in spans], kv_offset=[a for a, _ in spans],
                 causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge,
             )
+            # both exchanges give the same answer
+            out_g, lse_g = sharded_kv_attention_forward(
+                q, [k[:, a:b] for a, b in spans], [v[:, a:b] for a, b in spans], kv_offset=[a for a, _ in spans],
+                causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge, exchange="all_gather",
+            )
+            assert (out - out_g).abs().max() < 1e-5 and (lse - lse_g).abs().max() < 1e-5
         else:
             out, lse = sharded_kv_attention_forward(
                 q, k[:, lo:hi], v[:, lo:hi], kv_offset=lo, causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge

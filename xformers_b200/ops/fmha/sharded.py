@@ -79,12 +79,18 @@ def sharded_kv_attention_forward(
     partial_dtype: Optional[torch.dtype] = None,
     partial_fn: Callable = _partial_on_gpu,
     merge_fn: Callable = _merge_on_gpu,
+    exchange: str = "all_to_all",
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
     key/value shard ``[B, len_r, (G,) H, D]`` starting at global key index
     ``kv_offset``.  Returns the full ``(out, lse)`` on every rank.  Several key
     ranges per rank are passed as sequences of shards and offsets (empty ranges
     are skipped); the rank merges their partials before the exchange.
+
+    ``exchange="all_to_all"`` (when the number of queries divides by the number of
+    ranks): every rank receives the partials of its slice of the queries, merges
+    them and the merged slices are all-gathered; ``"all_gather"``: every rank
+    receives every partial and merges all queries itself.
 
     ``partial_fn`` / ``merge_fn`` exist so that the exchange logic can be
     exercised with CPU stand-ins under the gloo backend.
@@ -113,6 +119,26 @@ def sharded_kv_attention_forward(
         return merge_fn([out_r], [lse_r], query.dtype)
     out_r = out_r.contiguous()
     lse_r = lse_r.contiguous()
+    mq = out_r.shape[1]
+    if exchange == "all_to_all" and mq % world == 0 and lse_r.shape[-1] == mq:
+        # Every rank merges one slice of the queries: the partials of that slice come
+        # in by all-to-all (1/world of an all-gather's volume), the merged slices in the
+        # output dtype go round by all-gather.
+        ms = mq // world
+        send_o = out_r.view(out_r.shape[0], world, ms, *out_r.shape[2:]).transpose(0, 1).contiguous()      # [world, B, ms, ...]
+        send_l = lse_r.view(*lse_r.shape[:-1], world, ms).movedim(-2, 0).contiguous()                        # [world, B, .., ms]
+        recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
+        dist.all_to_all_single(recv_o, send_o, group=group)
+        dist.all_to_all_single(recv_l, send_l, group=group)
+        out_s, lse_s = merge_fn(recv_o, recv_l, query.dtype)                                               # [B, ms, ...], [B, .., ms]
+        out_s, lse_s = out_s.contiguous(), lse_s.contiguous()
+        all_o = torch.empty((world,) + tuple(out_s.shape), dtype=out_s.dtype, device=out_s.device)
+        all_l = torch.empty((world,) + tuple(lse_s.shape), dtype=lse_s.dtype, device=lse_s.device)
+        dist.all_gather_into_tensor(all_o.view(-1, *out_s.shape[1:]), out_s, group=group)
+        dist.all_gather_into_tensor(all_l.view(-1, *lse_s.shape[1:]), lse_s, group=group)
+        out = all_o.transpose(0, 1).reshape(out_s.shape[0], mq, *out_s.shape[2:])
+        lse = all_l.movedim(0, -2).reshape(*lse_s.shape[:-1], mq)
+        return out, lse
     outs = torch.empty((world,) + tuple(out_r.shape), dtype=out_r.dtype, device=out_r.device)
     lses = torch.empty((world,) + tuple(lse_r.shape), dtype=lse_r.dtype, device=lse_r.device)
     # the flat form (ranks concatenated along dim 0) is the one every backend takes
