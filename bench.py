@@ -554,7 +554,7 @@ def main():
         lt = lflops / (ms / l_steps * 1e-3) / 1e12
         out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms / l_steps, "scaling": "strong",
                                     "ideal_speedup": float(world),
-                                    "workload": "1 x 131072 causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work), local merge, NCCL all-gather of (O, LSE) + LSE merge"}
+                                    "workload": "1 x 131072 causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work), local merge, NCCL all-to-all of the partials by query slice, LSE merge of the slice, all-gather of the merged slices"}
         del lq, lk, lv, lk_full, lv_full
         torch.cuda.empty_cache()
 
