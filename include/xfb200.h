@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define XFB200_ABI_VERSION 2
+#define XFB200_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define XFB200_API __attribute__((visibility("default")))
@@ -51,8 +51,22 @@ enum {
 enum { XFB200_BF16 = 0, XFB200_F16 = 1, XFB200_F32 = 2 };
 
 /* custom_mask_type of the reference boundary (attention.cpp:12-16):
- * 0 none, 1 causal aligned top-left, 2 causal aligned bottom-right. */
-enum { XFB200_MASK_NONE = 0, XFB200_MASK_CAUSAL_TOP_LEFT = 1, XFB200_MASK_CAUSAL_BOTTOM_RIGHT = 2 };
+ * 0 none, 1 causal aligned top-left, 2 causal aligned bottom-right.
+ * 3 (prefill only): a band around the bottom-right diagonal, query i of a block
+ * of mq queries and mkv keys sees key j iff
+ *   i + (mkv - mq) - window_left <= j <= i + (mkv - mq) + window_right
+ * (LocalAttentionFromBottomRightMask and the BlockDiagonalLocalAttention* biases,
+ * xformers/ops/fmha/attn_bias.py:34-38; KAT tests/test_mem_eff_attention.py:2389-2399). */
+enum { XFB200_MASK_NONE = 0, XFB200_MASK_CAUSAL_TOP_LEFT = 1, XFB200_MASK_CAUSAL_BOTTOM_RIGHT = 2, XFB200_MASK_LOCAL_BOTTOM_RIGHT = 3 };
+
+/* kernel_path of xfb200_prefill_params: which kernel may run the call. */
+enum {
+  XFB200_PREFILL_AUTO = 0,        /* the fastest kernel that covers the input            */
+  XFB200_PREFILL_MMA_SYNC = 1,    /* the mma.sync kernel (every head dim, additive bias) */
+  XFB200_PREFILL_TCGEN05 = 2,     /* fail unless a tcgen05 kernel covers the input       */
+  XFB200_PREFILL_TCGEN05_CTA = 4, /* tcgen05, one CTA per block of 256 query rows        */
+  XFB200_PREFILL_TCGEN05_PERSISTENT = 6 /* tcgen05, one persistent CTA per SM            */
+};
 
 enum { XFB200_KV_PLAIN = 0, XFB200_KV_INT4_ROWWISE = 1, XFB200_KV_FP8_ROWWISE = 2 };
 
@@ -103,7 +117,7 @@ typedef struct {
   int32_t window_left; /* < 0: no window; else keys j >= i + shift - window_left */
   float scale;
   int32_t out_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
-  int32_t reserved;
+  int32_t kernel_path; /* XFB200_PREFILL_*; 0 = automatic */
   /* Additive bias (a plain tensor as attn_bias, or LowerTriangularMaskWithTensorBias,
    * fmha/attn_bias.py:43; tests/test_mem_eff_attention.py:1440-1449): NULL, or
    * [batch, G, H, mq, mkv] with unit stride on the last axis and element strides
@@ -111,8 +125,14 @@ typedef struct {
    * Dense batches only; runs on the mma.sync kernel. */
   const void* bias;
   int32_t bias_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
-  int32_t reserved2;
+  int32_t window_right; /* XFB200_MASK_LOCAL_BOTTOM_RIGHT: keys j <= i + shift + window_right (>= 0); else ignored */
   int64_t bias_stride_b, bias_stride_g, bias_stride_h, bias_stride_m;
+  /* Testing aids of the tcgen05 kernels' bounded waits; both 0 in production.
+   * wait_budget_kcycles: a wait gives up after this many thousand SM clocks (0 = the default, 400000).
+   * debug_flags bit 0: the first CTA does not issue its last key-tile copy, so that the wait
+   * for it runs out, the kernel records a status code and returns (see xfb200_prefill_device_status). */
+  int32_t wait_budget_kcycles;
+  int32_t debug_flags;
 } xfb200_prefill_params;
 
 XFB200_API int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream);
@@ -176,9 +196,11 @@ typedef struct {
   int64_t ks_stride_m, ks_stride_g;
   int64_t vs_stride_m, vs_stride_g;
   /* Gappy caches (BlockDiagonalGappyKeysMask and its paged form, fmha/attn_bias.py:33-47): NULL, or
-   * [batch] first key row of every sequence -- an absolute row of k/v for a padded cache (kv_rows
-   * = number of rows of k/v), a row inside the sequence's block table for a paged one.  kv_padding
-   * then bounds seqlen_k[b]. */
+   * [batch] first key row of every sequence -- an absolute row of k/v for a padded cache, a row
+   * inside the sequence's block table for a paged one.  kv_padding then bounds seqlen_k[b].
+   * kv_rows: number of token rows of k/v (pages * page_size for a paged pool).  Required for a
+   * gappy padded cache; otherwise 0 = unknown.  When given, the tiled copies are bounded by it:
+   * a row past the end (a bad page-table entry) reads as zero instead of foreign memory. */
   const int32_t* kv_seqstart;
   int64_t kv_rows;
   /* Local attention for one query per sequence (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
@@ -212,7 +234,8 @@ XFB200_API int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
  *
  * The first call on each device resolves the array's device address (a symbol
  * look-up with that device current, not an allocation); make that first call
- * before any stream capture.
+ * before any stream capture.  The status word of its bounded waits is the one
+ * xfb200_decode_device_status reads, also part of the library image.
  * All calls on a device share the one array, which keeps whatever the last call
  * wrote.  Nothing in it has to start at zero: every chunk that a call merges
  * has been written completely by that same call.  Two calls whose kernels may
@@ -327,14 +350,14 @@ XFB200_API int xfb200_rope_padded(const xfb200_rope_params* p, void* stream);
 /* ---- misc ---------------------------------------------------------------------- */
 XFB200_API int xfb200_abi_version(void);
 XFB200_API const char* xfb200_last_error(void);
-/* Device-side status word of the last prefill launch on the current device
- * (0 = no timed-out wait).  Synchronises the given stream. */
+/* Every wait inside the kernels is bounded.  A kernel that gives one up records a
+ * code in a status word of its device and returns; its output is then not valid.
+ * These calls synchronise the given stream, store the code of the first such event
+ * since the last call in *status_out (0 = none) and clear it.  They return
+ * XFB200_E_DEVICE when the code is non-zero.  The words live in the library image:
+ * no call of this library allocates or frees device memory for them. */
 XFB200_API int xfb200_prefill_device_status(void* stream, int32_t* status_out);
-/* Testing knob: 0 = choose automatically, 1 = always the mma.sync kernel,
- * 2 = fail unless a tcgen05 kernel covers the input; 3, 4, 5 = likewise and pick
- * the tcgen05 variant (128 rows per CTA; 256 rows with 128-key steps; 256 rows
- * with 64-key steps). */
-XFB200_API int xfb200_debug_set_prefill_path(int path);
+XFB200_API int xfb200_decode_device_status(void* stream, int32_t* status_out);
 
 #ifdef __cplusplus
 }

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import oracle
-from gpu_utils import ATOL_O, assert_o_lse, gpu, ref, require_cuda
+from gpu_utils import ATOL_LSE, ATOL_O, assert_o_lse, gpu, ref, require_cuda
 from xformers_b200.ops import fmha
 from xformers_b200.ops.fmha import attn_bias as ab
 
@@ -90,7 +90,7 @@ def test_decoder_int4(kv_heads, padding, bsz, dtype, split_k, rand_scale):
     # values reach 16 in the reference's pattern: tolerance scales with |V|
     assert_o_lse(out, None, ro, rl, dtype, "int4", o_scale=4.0 if not rand_scale else 1.0)
     lerr = (lse.cpu() - rl).abs().max().item()
-    assert lerr <= (2e-2 if not rand_scale else 2e-3), f"int4 LSE error {lerr}"
+    assert lerr <= ATOL_LSE, f"int4 LSE error {lerr:.3e} > {ATOL_LSE:.0e}"
 
 
 @gpu
@@ -111,7 +111,7 @@ def test_decoder_int4_groups(groups, d, kv_heads, padding, bsz, dtype, rand_scal
     ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k_ref, v_ref, bias.to("cpu"))
     assert_o_lse(out, None, ro, rl, dtype, f"int4 x{groups}", o_scale=4.0 if not rand_scale else 1.0)
     lerr = (lse.cpu() - rl).abs().max().item()
-    assert lerr <= (2e-2 if not rand_scale else 2e-3), f"int4 x{groups} LSE error {lerr}"
+    assert lerr <= ATOL_LSE, f"int4 x{groups} LSE error {lerr:.3e} > {ATOL_LSE:.0e}"
 
 
 @gpu

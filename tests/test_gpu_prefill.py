@@ -11,7 +11,7 @@ from xformers_b200.ops import fmha
 from xformers_b200.ops.fmha import attn_bias as ab
 
 P = fmha.b200
-KERNELS = [P.FwOp_Tcgen05, P.FwOp_Tcgen05_S64, P.FwOp_Generic]
+KERNELS = [P.FwOp_Tcgen05_Persistent, P.FwOp_Tcgen05_M256, P.FwOp_Generic]
 
 
 def _status_ok():
@@ -178,7 +178,7 @@ def test_padded_keys_prefill_and_nan_padding(op):
 
 @gpu
 @pytest.mark.parametrize("window", [1, 3, 64, 200])
-@pytest.mark.parametrize("op", KERNELS + [P.FwOp_Tcgen05_M256])
+@pytest.mark.parametrize("op", KERNELS)
 def test_causal_local_padded_keys_and_bottom_right_local(op, window):
     """The window forms of the bottom-right causal masks
     (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
@@ -401,3 +401,80 @@ def test_causal_with_tensor_bias(Mq, Mkv):
     ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), ab.LowerTriangularMaskWithTensorBias(t.float().cpu()))
     assert_o_lse(out, lse, ro, rl, dtype, "causal + tensor bias")
     assert P.FwOp_Tcgen05.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("wl,wr", [(1, 2), (0, 0), (5, 0), (0, 7), (130, 40), (300, 300)])
+@pytest.mark.parametrize("Mq,Mkv", [(4, 4), (200, 200), (129, 520), (520, 129), (1030, 1030)])
+def test_local_band_from_bottom_right(op, wl, wr, Mq, Mkv):
+    """``LocalAttentionFromBottomRightMask`` (tests/test_mem_eff_attention.py:2389-2399):
+    query i sees keys within [i + (Mkv - Mq) - window_left, i + (Mkv - Mq) + window_right]."""
+    require_cuda()
+    dtype = torch.bfloat16
+    q, k, v = rand_qkv(2, Mq, Mkv, 2, 2, 128, dtype, seed=Mq + Mkv + wl, gqa=True)
+    bias = ab.LocalAttentionFromBottomRightMask(window_left=wl, window_right=wr)
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    mask = oracle.local_mask(Mq, Mkv, wl, wr)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), mask.expand(2, 2, 2, Mq, Mkv))
+    assert_o_lse(out, lse, ro, rl, dtype, f"{op.NAME} local band ({wl},{wr})")
+    # rows that see no key at all: zeros and -inf
+    dead = torch.isneginf(mask).all(-1)
+    if dead.any():
+        assert (out[:, dead].float() == 0).all() and torch.isneginf(lse[..., dead]).all()
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("gappy", [False, True])
+def test_block_diagonal_local_padded_and_gappy_keys(op, gappy):
+    """``BlockDiagonalLocalAttentionPaddedKeysMask`` and
+    ``BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask`` (xformers/ops/fmha/attn_bias.py:34-35):
+    the band of the test above inside every block of a padded / gappy key cache."""
+    require_cuda()
+    dtype = torch.float16
+    q_lens, kv_lens, pad = [5, 300, 64, 1], [40, 310, 64, 200], 384
+    wl, wr = 33, 4
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(1, sum(q_lens), 2, 3, 64, generator=g).to(dtype).cuda()
+    k = torch.randn(1, len(q_lens) * pad, 2, 1, 64, generator=g).to(dtype).cuda().expand(-1, -1, -1, 3, -1)
+    v = torch.randn(1, len(q_lens) * pad, 2, 1, 64, generator=g).to(dtype).cuda().expand(-1, -1, -1, 3, -1)
+    if gappy:
+        starts = [7, 400, 800, 1200, len(q_lens) * pad]
+        bias = ab.BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask.from_seqlens_local(q_lens, starts, kv_lens, wl, wr, device="cuda")
+    else:
+        starts = [i * pad for i in range(len(q_lens) + 1)]
+        bias = ab.BlockDiagonalLocalAttentionPaddedKeysMask.from_seqlens_local(q_lens, pad, kv_lens, wl, wr, device="cuda")
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    # the mask from plain integer lists: block b couples its queries with the keys [starts[b], starts[b] + kv_lens[b])
+    mask = torch.full((sum(q_lens), len(q_lens) * pad), float("-inf"))
+    qs = 0
+    for b, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        mask[qs : qs + ql, starts[b] : starts[b] + kl] = oracle.local_mask(ql, kl, wl, wr)
+        qs += ql
+    assert torch.equal(bias.to("cpu").materialize(mask.shape), mask)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), mask.expand(1, 2, 3, *mask.shape))
+    assert_o_lse(out, lse, ro, rl, dtype, f"{op.NAME} block-diagonal local, gappy={gappy}")
+    _status_ok()
+
+
+@gpu
+def test_memory_efficient_attention_is_the_forward_without_grad():
+    """xformers/ops/__init__.py:16: with nothing to differentiate the main entry
+    point is the forward pass (examples/llama_inference/model.py:142 calls it so)."""
+    require_cuda()
+    import xformers_b200.ops as xops
+
+    q, k, v = rand_qkv(1, 300, 300, 2, 4, 128, torch.bfloat16, seed=5, gqa=True)
+    bias = ab.LowerTriangularMask()
+    out = xops.memory_efficient_attention(q, k, v, attn_bias=bias)
+    assert torch.equal(out, xops.memory_efficient_attention_forward(q, k, v, bias))
+    out2 = xops.memory_efficient_attention(q, k, v, bias, op=(P.FwOp_Generic, None), scale=0.05, output_dtype=torch.float32)
+    ro, _ = ref(q, k, v, bias, scale=0.05)
+    assert out2.dtype == torch.float32 and (out2.cpu() - ro).abs().max() <= ATOL_O[torch.bfloat16]
+    qg = q.clone().requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        xops.memory_efficient_attention(qg, k, v, bias)
+    with torch.no_grad():
+        assert torch.equal(xops.memory_efficient_attention(qg, k, v, bias), out)

@@ -25,13 +25,13 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/xfb200.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().xfb200_abi_version() == _lib.ABI_VERSION == 2
+    assert _lib.load().xfb200_abi_version() == _lib.ABI_VERSION == 3
 
 
 def test_struct_sizes_match_header():
     # sizes computed by hand from include/xfb200.h (LP64)
     assert ctypes.sizeof(_lib.Strides) == 32
-    assert ctypes.sizeof(_lib.PrefillParams) == 8 * 8 + 8 * 4 + 4 * 32 + 3 * 8 + 6 * 4 + 8 + 2 * 4 + 4 * 8
+    assert ctypes.sizeof(_lib.PrefillParams) == 8 * 8 + 8 * 4 + 4 * 32 + 3 * 8 + 6 * 4 + 8 + 2 * 4 + 4 * 8 + 2 * 4
     assert ctypes.sizeof(_lib.DecodeParams) == 8 * 8 + 12 * 4 + 12 * 8 + 4 * 4 + 2 * 8 + 4 * 8 + 8 + 8 + 2 * 4
     assert ctypes.sizeof(_lib.MergeParams) == 16 + 8 + 16 + 32 + 24 + 16 + 32 + 24 + 8 * 4
 
@@ -149,8 +149,15 @@ def test_cpu_tensors_and_bad_inputs_raise_value_error():
     bias = ab.BlockDiagonalMask.from_seqlens([4, 4])
     with pytest.raises(ValueError):
         xops.memory_efficient_attention_forward(torch.randn(2, 8, 2, 64), torch.randn(2, 8, 2, 64), torch.randn(2, 8, 2, 64), bias)
-    with pytest.raises(NotImplementedError):
+    # the reference's main entry point: forward when nothing asks for a gradient (CPU tensors: ValueError as above),
+    # NotImplementedError only when autograd would have to record the call
+    with pytest.raises(ValueError):
         xops.memory_efficient_attention(q, q, q)
+    qg = q.clone().requires_grad_(True)
+    with pytest.raises(NotImplementedError):
+        xops.memory_efficient_attention(qg, q, q)
+    with torch.no_grad(), pytest.raises(ValueError):
+        xops.memory_efficient_attention(qg, q, q)
 
 
 def test_not_supported_reasons_strings():

@@ -12,7 +12,7 @@ import os
 from pathlib import Path
 from typing import Optional
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 XFB200_OK = 0
 XFB200_E_INVALID = -1
@@ -21,7 +21,8 @@ XFB200_E_CUDA = -3
 XFB200_E_DEVICE = -4
 
 BF16, F16, F32 = 0, 1, 2
-MASK_NONE, MASK_CAUSAL_TOP_LEFT, MASK_CAUSAL_BOTTOM_RIGHT = 0, 1, 2
+MASK_NONE, MASK_CAUSAL_TOP_LEFT, MASK_CAUSAL_BOTTOM_RIGHT, MASK_LOCAL_BOTTOM_RIGHT = 0, 1, 2, 3
+PREFILL_AUTO, PREFILL_MMA_SYNC, PREFILL_TCGEN05, PREFILL_TCGEN05_CTA, PREFILL_TCGEN05_PERSISTENT = 0, 1, 2, 4, 6
 KV_PLAIN, KV_INT4_ROWWISE, KV_FP8_ROWWISE = 0, 1, 2
 MERGE_MAX_PTRS = 32
 DECODE_STATIC_SCRATCH_BYTES = 16 << 20
@@ -31,7 +32,7 @@ EXPORTED_SYMBOLS = (
     "xfb200_last_error",
     "xfb200_prefill_forward",
     "xfb200_prefill_device_status",
-    "xfb200_debug_set_prefill_path",
+    "xfb200_decode_device_status",
     "xfb200_decode_scratch_bytes",
     "xfb200_decode_forward",
     "xfb200_decode_forward_static_scratch",
@@ -74,14 +75,16 @@ class PrefillParams(C.Structure):
         ("window_left", C.c_int32),
         ("scale", C.c_float),
         ("out_dtype", C.c_int32),
-        ("reserved", C.c_int32),
+        ("kernel_path", C.c_int32),
         ("bias", C.c_void_p),
         ("bias_dtype", C.c_int32),
-        ("reserved2", C.c_int32),
+        ("window_right", C.c_int32),
         ("bias_stride_b", C.c_int64),
         ("bias_stride_g", C.c_int64),
         ("bias_stride_h", C.c_int64),
         ("bias_stride_m", C.c_int64),
+        ("wait_budget_kcycles", C.c_int32),
+        ("debug_flags", C.c_int32),
     ]
 
 
@@ -216,8 +219,8 @@ def load() -> C.CDLL:
     lib.xfb200_prefill_forward.restype = C.c_int
     lib.xfb200_prefill_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
     lib.xfb200_prefill_device_status.restype = C.c_int
-    lib.xfb200_debug_set_prefill_path.argtypes = [C.c_int]
-    lib.xfb200_debug_set_prefill_path.restype = C.c_int
+    lib.xfb200_decode_device_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+    lib.xfb200_decode_device_status.restype = C.c_int
     lib.xfb200_decode_scratch_bytes.argtypes = [C.c_int32] * 6
     lib.xfb200_decode_scratch_bytes.restype = C.c_size_t
     lib.xfb200_decode_forward.argtypes = [C.POINTER(DecodeParams), C.c_void_p]
@@ -242,9 +245,22 @@ class Xfb200Error(RuntimeError):
     pass
 
 
+def check_status_after_every_call() -> bool:
+    """``XFB200_CHECK_STATUS=1``: the operators read the device status word after every
+    launch (a stream synchronisation each time) and raise when a kernel gave up a wait."""
+    return os.environ.get("XFB200_CHECK_STATUS", "0") not in ("", "0")
+
+
+def debug_checks() -> bool:
+    """``XFB200_DEBUG_CHECKS=1``: the operators validate page tables, sequence starts and
+    lengths on the host before a launch (device-to-host copies: a debugging aid)."""
+    return os.environ.get("XFB200_DEBUG_CHECKS", "0") not in ("", "0")
+
+
 def check(rc: int, what: str) -> None:
     """Translate a C return code: invalid -> ValueError, unsupported ->
-    NotImplementedError, CUDA/device failures -> RuntimeError."""
+    NotImplementedError, CUDA failures and kernels that gave up a wait
+    (``XFB200_E_DEVICE``) -> RuntimeError."""
     if rc == XFB200_OK:
         return
     msg = load().xfb200_last_error().decode(errors="replace")

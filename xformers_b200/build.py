@@ -22,9 +22,9 @@ SOURCES = [
     "merge.cu",
     "decode_splitk.cu",
     "prefill_generic.cu",
-    "prefill_sm100.cu",
+    "prefill_sm100_host.cu",
     "prefill_sm100_m256.cu",
-    "prefill_sm100_s64.cu",
+    "prefill_sm100_persist.cu",
     "prefill_api.cu",
     "rope_padded.cu",
 ]

@@ -242,7 +242,7 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
   for (int tile = 0; tile < w.n_tiles; ++tile) {
     const int st = tile % w.stages;
     if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
-      if (lane == 0) atomicExch(a.status, 2);
+      if (lane == 0) atomicCAS(a.status, 0, 2);
       break;
     }
     for (int sp = 0; sp < kSps; ++sp) {
@@ -529,7 +529,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   for (int tile = 0; tile < w.n_tiles; ++tile) {
     const int st = tile % w.stages;
     if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
-      if (lane == 0) atomicExch(a.status, 2);
+      if (lane == 0) atomicCAS(a.status, 0, 2);
       break;
     }
     const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * w.stage_bytes) + hw * W;
@@ -820,7 +820,7 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
   for (int tile = 0; tile < w.n_tiles; ++tile) {
     const int st = tile % w.stages;
     if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
-      if (lane == 0) atomicExch(a.status, 2);
+      if (lane == 0) atomicCAS(a.status, 0, 2);
       break;
     }
     const uint32_t* kst = reinterpret_cast<const uint32_t*>(w.stage_base + st * w.stage_bytes) + hw * W;
@@ -1117,7 +1117,7 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
   for (int tile = 0; tile < w.n_tiles; ++tile) {
     const int st = tile % w.stages;
     if (!mbar_wait(&w.full_bar[st], (tile / w.stages) & 1)) {
-      if (lane == 0) atomicExch(a.status, 2);
+      if (lane == 0) atomicCAS(a.status, 0, 2);
       break;
     }
     const uint8_t* kst = w.stage_base + st * w.stage_bytes;
@@ -1411,12 +1411,12 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
       const int st = tile % kDecStages;
       if (tile >= kDecStages) {
         if (!mbar_wait(&empty_bar[st], ((tile / kDecStages) - 1) & 1)) {
-          if (lane == 0) atomicExch(a.status, 1);
+          if (lane == 0) atomicCAS(a.status, 0, 1);
           return;
         }
       } else if (kQuant && tile == a.q_first_stage) {
         if (!mbar_wait(&q_done_bar, 0)) {
-          if (lane == 0) atomicExch(a.status, 3);
+          if (lane == 0) atomicCAS(a.status, 0, 3);
           return;
         }
       }
@@ -1671,24 +1671,6 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const __grid_constant
 }
 
 // ------------------------------------------------------------------ host side
-static int32_t* decode_status_word() {
-  // one status word per device, allocated on first use and kept
-  static int32_t* words[64] = {nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  if (words[dev] == nullptr) {
-    int32_t* p = nullptr;
-    if (cudaMalloc(&p, 256) != cudaSuccess) return nullptr;
-    cudaMemset(p, 0, 256);
-    words[dev] = p;
-  }
-  return words[dev];
-}
-
-// Set only while xfb200_decode_forward_static_scratch runs on this thread: the
-// status word then lives in the library's own device memory as well.
-static thread_local int32_t* t_status_override = nullptr;
-
 int decode_chunk_tokens(int kv_bound, int split_k) {
   int c = (kv_bound + split_k - 1) / split_k;
   c = (c + kDecChunkAlign - 1) / kDecChunkAlign * kDecChunkAlign;
@@ -1723,11 +1705,13 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   auto kern = decode_splitk_kernel<D, MT, kFmt, kBf16, NG>;
   // 227 KB per CTA includes the static part (the mbarriers)
   if (smem + 1024 > size_t(227 * 1024) / DecOccupancy<kFmt>::kCtasPerSm) return set_error(XFB200_E_UNSUPPORTED, "decode: shared memory %zu B exceeds 227 KB", smem);
-  static size_t configured = 0;  // per instantiation: largest size opted into so far
-  if (smem > configured) {
+  // per instantiation and device (the attribute belongs to the device's context): largest size opted into so far
+  static size_t configured[kMaxDevices] = {0};
+  const int dev = current_device();
+  if (dev < 0 || smem > configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail("decode: cudaFuncSetAttribute", e);
-    configured = smem;
+    if (dev >= 0) configured[dev] = smem;
   }
   dim3 grid(a.split_k, a.batch, head_blocks * a.row_blocks);
   kern<<<grid, kDecThreads, smem, stream>>>(a);
@@ -1818,8 +1802,11 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     a.part_o = reinterpret_cast<float*>(p->scratch);
     a.part_lse = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(p->scratch) + ((rows * p->head_dim * 4 + 255) & ~size_t(255)));
   }
-  a.status = t_status_override != nullptr ? t_status_override : decode_status_word();
-  if (a.status == nullptr) return set_error(XFB200_E_CUDA, "decode: cannot allocate the device status word");
+  {
+    int32_t* words = device_words();
+    if (words == nullptr) return set_error(XFB200_E_CUDA, "decode: cannot resolve the device status word");
+    a.status = words + kWordDecodeStatus;
+  }
 
   // kv heads per CTA: the largest of 8, 4, 2, 1 that divides kv_heads
   int hb = 8;
@@ -1893,9 +1880,12 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
       while (box > 1 && p->page_size % box) box >>= 1;
     EncodeTiledFn enc = encode_tiled_fn();
     if (box >= (fp8 ? 16 : 8) && enc != nullptr) {
-      // token rows: all of a padded cache (rows past the end read as zero); a paged
-      // pool's size is not part of the call, and a copy never leaves its page
-      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : p->kv_seqstart != nullptr ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
+      // token rows: all of a padded cache (rows past the end read as zero); a paged pool's
+      // size when the caller states it (kv_rows), so that a bad table entry reads zeros
+      // instead of foreign memory; a copy never leaves its page
+      const cuuint64_t rows = p->kv_rows > 0              ? cuuint64_t(p->kv_rows)
+                              : p->block_tables != nullptr ? (cuuint64_t(1) << 31)
+                                                           : cuuint64_t(p->batch) * p->kv_padding;
       // 16-bit cache: {64 elements, token rows, 128-byte column groups}; fp8: {128 bytes, token rows, kv heads}
       const cuuint64_t dims[3] = {cuuint64_t(fp8 ? 128 : 64), rows, fp8 ? cuuint64_t(p->kv_heads) : cuuint64_t(p->kv_heads) * (p->head_dim / 64)};
       const cuuint32_t bx[3] = {cuuint32_t(fp8 ? 128 : 64), cuuint32_t(box), cuuint32_t(fp8 ? hb : hb * (p->head_dim / 64))};
@@ -1926,7 +1916,9 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
     };
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc != nullptr && ok16(a.k_ss, a.kss_m, a.kss_g, p->kv_heads) && ok16(a.v_ss, a.vss_m, a.vss_g, p->kv_heads)) {
-      const cuuint64_t rows = p->block_tables != nullptr ? (cuuint64_t(1) << 31) : p->kv_seqstart != nullptr ? cuuint64_t(p->kv_rows) : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t rows = p->kv_rows > 0              ? cuuint64_t(p->kv_rows)
+                              : p->block_tables != nullptr ? (cuuint64_t(1) << 31)
+                                                           : cuuint64_t(p->batch) * p->kv_padding;
       const cuuint64_t dims[3] = {4, cuuint64_t(p->kv_heads), rows};
       const cuuint32_t bx[3] = {4, cuuint32_t(hb), cuuint32_t(a.box_tok)};
       const cuuint32_t estr[3] = {1, 1, 1};
@@ -1979,24 +1971,22 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
 // Split-K decode for callers that cannot allocate device memory.
 //
 // The partial outputs of the key chunks go to a fixed array that is part of the
-// library image instead of caller-provided scratch, and the status word of the
-// bounded waits sits next to it.  Both are file-scope __device__ arrays: in
-// host code their names are host-side stand-ins, not device addresses, so the
-// addresses the kernels receive are looked up once per device with
-// cudaGetSymbolAddress while that device is current.
+// library image instead of caller-provided scratch (the status word of the
+// bounded waits is part of the image for every entry point).  It is a
+// file-scope __device__ array: in host code its name is a host-side stand-in,
+// not a device address, so the address the kernels receive is looked up once
+// per device with cudaGetSymbolAddress while that device is current.
 // ---------------------------------------------------------------------------
 namespace xfb {
 
 static __device__ __align__(256) unsigned char g_static_scratch[XFB200_DECODE_STATIC_SCRATCH_BYTES];
-static __device__ __align__(256) int32_t g_static_status[64];
 
 struct StaticScratchAddr {
   void* scratch = nullptr;
-  int32_t* status = nullptr;
 };
 
-// Device addresses of the two arrays on the current device; resolved on the
-// first call per device (a symbol look-up, not an allocation) and cached.
+// Device address of the array on the current device; resolved on the first
+// call per device (a symbol look-up, not an allocation) and cached.
 static int static_scratch_addresses(StaticScratchAddr* out) {
   static StaticScratchAddr per_device[64];
   int dev = -1;
@@ -2006,12 +1996,8 @@ static int static_scratch_addresses(StaticScratchAddr* out) {
   StaticScratchAddr& slot = per_device[dev];
   if (slot.scratch == nullptr) {
     void* scratch = nullptr;
-    void* status = nullptr;
     e = cudaGetSymbolAddress(&scratch, g_static_scratch);
     if (e != cudaSuccess) return cuda_fail("decode(static scratch): cudaGetSymbolAddress(scratch)", e);
-    e = cudaGetSymbolAddress(&status, g_static_status);
-    if (e != cudaSuccess) return cuda_fail("decode(static scratch): cudaGetSymbolAddress(status)", e);
-    slot.status = static_cast<int32_t*>(status);
     slot.scratch = scratch;
   }
   *out = slot;
@@ -2037,8 +2023,5 @@ extern "C" int xfb200_decode_forward_static_scratch(const xfb200_decode_params* 
   if (rc != XFB200_OK) return rc;
   xfb200_decode_params q = *p;
   q.scratch = addr.scratch;
-  t_status_override = addr.status;
-  rc = xfb200_decode_forward(&q, stream);
-  t_status_override = nullptr;
-  return rc;
+  return xfb200_decode_forward(&q, stream);
 }

@@ -1,22 +1,5 @@
 // xfb200_prefill_forward: host-side validation and kernel selection.
 #include "internal.h"
-#include "prefill_sm100.h"
-
-namespace xfb {
-
-// Debug/testing knob: 0 = automatic, 1 = force the mma.sync kernel, 2 = require the tcgen05 kernel.
-static int g_prefill_path = 0;
-
-}  // namespace xfb
-
-namespace xfb {
-int prefill_path_override() { return g_prefill_path; }
-}  // namespace xfb
-
-extern "C" int xfb200_debug_set_prefill_path(int path) {
-  xfb::g_prefill_path = path;
-  return XFB200_OK;
-}
 
 extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream) {
   using namespace xfb;
@@ -34,9 +17,14 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
   if ((p->seqstart_q == nullptr) != (p->seqstart_k == nullptr))
     return set_error(XFB200_E_INVALID, "prefill: seqstart_q and seqstart_k go together");
   if (p->seqlen_k != nullptr && p->seqstart_k == nullptr) return set_error(XFB200_E_INVALID, "prefill: seqlen_k needs seqstart_k");
-  if (p->mask_type < 0 || p->mask_type > 2) return set_error(XFB200_E_INVALID, "prefill: bad mask_type %d", p->mask_type);
-  if (p->mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT && p->kv_offset != 0)
+  if (p->mask_type < 0 || p->mask_type > XFB200_MASK_LOCAL_BOTTOM_RIGHT) return set_error(XFB200_E_INVALID, "prefill: bad mask_type %d", p->mask_type);
+  if (p->mask_type >= XFB200_MASK_CAUSAL_BOTTOM_RIGHT && p->kv_offset != 0)
     return set_error(XFB200_E_INVALID, "prefill: kv_offset needs the top-left causal mask");
+  if (p->mask_type == XFB200_MASK_LOCAL_BOTTOM_RIGHT && (p->window_left < 0 || p->window_right < 0))
+    return set_error(XFB200_E_INVALID, "prefill: the local mask needs window_left >= 0 and window_right >= 0");
+  if (p->kernel_path != XFB200_PREFILL_AUTO && p->kernel_path != XFB200_PREFILL_MMA_SYNC && p->kernel_path != XFB200_PREFILL_TCGEN05 &&
+      p->kernel_path != XFB200_PREFILL_TCGEN05_CTA && p->kernel_path != XFB200_PREFILL_TCGEN05_PERSISTENT)
+    return set_error(XFB200_E_INVALID, "prefill: bad kernel_path %d", p->kernel_path);
   if (p->window_left >= 0 && p->mask_type == XFB200_MASK_NONE)
     return set_error(XFB200_E_UNSUPPORTED, "prefill: a left window without a causal mask");
   // 16-byte vector loads / cp.async need aligned rows
@@ -57,8 +45,8 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // (the tcgen05 kernels take no additive bias)
-  const bool can100 = g_prefill_path != 1 && p->mkv > 0 && p->bias == nullptr && prefill_sm100_supported(p);
-  if (g_prefill_path >= 2 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
+  const bool can100 = p->kernel_path != XFB200_PREFILL_MMA_SYNC && p->mkv > 0 && p->bias == nullptr && prefill_sm100_supported(p);
+  if (p->kernel_path >= XFB200_PREFILL_TCGEN05 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
   if (can100) return prefill_sm100_launch(p, st);
   return prefill_generic_launch(p, st);
 }

@@ -1,6 +1,6 @@
 // Generic attention-forward kernel on warp-level mma.sync (m16n8k16).
 //
-// Covers every shape the tcgen05 kernel (prefill_sm100.cu) does not take:
+// Covers every shape the tcgen05 kernels do not take:
 // head dims other than 64/128 (any multiple of 8 up to 256), different
 // value head dim is not supported.  Same mask model, same outputs.
 //
@@ -69,12 +69,14 @@ __global__ void __launch_bounds__(kGenThreads) prefill_generic_kernel(const __gr
   }
   const int m0 = qt * kGenBM;
   if (m0 >= qlen) return;
-  const int shift = (p.mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT ? klen - qlen : 0) - p.kv_offset;
-  const bool causal = p.mask_type != XFB200_MASK_NONE;
+  // query i sees key j iff i + shift - window_left <= j <= i + shift + wr (each bound only when it is >= 0)
+  const int shift = (p.mask_type >= XFB200_MASK_CAUSAL_BOTTOM_RIGHT ? klen - qlen : 0) - p.kv_offset;
+  const int wr = p.mask_type == XFB200_MASK_NONE ? -1 : p.mask_type == XFB200_MASK_LOCAL_BOTTOM_RIGHT ? p.window_right : 0;
+  const bool causal = wr >= 0;
 
   // key range that any row of this tile can see
   int n_hi = klen;
-  if (causal) n_hi = min(n_hi, m0 + kGenBM - 1 + shift + 1);
+  if (causal) n_hi = min(n_hi, m0 + kGenBM - 1 + shift + wr + 1);
   int n_lo = 0;
   if (p.window_left >= 0) n_lo = max(0, m0 + shift - p.window_left);
   n_lo = n_lo / kGenBN * kGenBN;
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(kGenThreads) prefill_generic_kernel(const __gr
         const int col = n0 + j * 8 + 2 * c + (e & 1);
         const int i = (e >> 1) ? i1 : i0;
         bool vis = col < klen;
-        if (causal) vis = vis && col <= i + shift;
+        if (causal) vis = vis && col <= i + shift + wr;
         if (p.window_left >= 0) vis = vis && col >= i + shift - p.window_left;
         float x = -INFINITY;
         if (vis) {
@@ -246,11 +248,10 @@ static int launch_generic_t(const GenericArgs& ga, cudaStream_t stream) {
   const xfb200_prefill_params& p = ga.p;
   auto kern = prefill_generic_kernel<DP, kBf16>;
   const size_t smem = size_t(kGenBM + 2 * kGenBN) * (DP * 2 + 16);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {false};  // the attribute belongs to the device's context
+  if (first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (e != cudaSuccess) return cuda_fail("prefill(generic): cudaFuncSetAttribute", e);
-    configured = true;
   }
   dim3 grid((p.mq + kGenBM - 1) / kGenBM, p.groups * p.heads_per_group, p.batch);
   if (grid.x == 0 || grid.y == 0 || grid.z == 0) return XFB200_OK;

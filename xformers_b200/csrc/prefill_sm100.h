@@ -14,22 +14,27 @@ struct Sm100Args {
   const int32_t* seqstart_q;
   const int32_t* seqstart_k;
   const int32_t* seqlen_k;
-  int32_t* status;
+  int32_t* status;    // [0] first code a launch gave up with, [1] epoch of that launch
+  int32_t* counters;  // persistent kernel: [0] next work item, [1] CTAs that have finished; zero between launches
   int32_t batch, mq, mkv, groups, heads_per_group;
   int32_t kv_h_is_broadcast;  // K/V head stride 0: KV head index is g only
   xfb200_strides os;
   int64_t lse_b, lse_g, lse_h;
-  int32_t mask_type, kv_offset, window_left, out_dtype;
+  // query i of a block sees key j iff i + shift - window_left <= j <= i + shift + window_right, each bound only
+  // when it is >= 0; shift = (bottom_right ? keys - queries of the block : 0) - kv_offset
+  int32_t bottom_right, kv_offset, window_left, window_right;
+  int32_t out_dtype;
   float scale_log2;
-  int32_t q_tiles;
+  int32_t q_tiles;  // blocks of 256 query rows per sequence (static bound)
+  uint32_t epoch;   // differs from launch to launch, never 0
+  int32_t debug_flags;
+  long long wait_budget;  // SM clocks after which a wait gives up
 };
 
-// 256 query rows per CTA (two 128-row tiles sharing every K/V tile), 128-key steps, one score buffer per tile.
+// One CTA per block of 256 query rows (two 128-row tiles sharing every K/V tile), 128-key steps.
 int prefill_sm100_m256_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream);
-// The same CTA shape with 64-key steps and two score buffers per tile.
-int prefill_sm100_s64_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream);
-
-// 0 = default kernel choice; 3 = the 128-rows-per-CTA kernel, 4 = 256 rows with 128-key steps, 5 = 256 rows with 64-key steps (testing knobs).
-int prefill_path_override();
+// The same tile shape run by one persistent CTA per SM that pulls blocks from a work counter,
+// with the output of a block written by its own warps while the next block computes.
+int prefill_sm100_persist_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream);
 
 }  // namespace xfb

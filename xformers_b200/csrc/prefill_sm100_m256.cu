@@ -29,7 +29,9 @@
 // (raised only when it grows by more than 2^8) so that rescaling the
 // accumulator in tensor memory is rare.
 //
-// Masks, GQA indexing, NaN hygiene and bounded waits as in the 128-row kernel.
+// Masks are index arithmetic on (row, key) positions; K/V heads of a GQA group are
+// indexed, never expanded; V rows past a sequence's end are zeroed in shared memory
+// and K garbage is masked by select, so NaN in padding cannot leak; every wait is bounded.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -122,6 +124,13 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
   }
 }
 
+// Records the first code a launch gives up with (kept until the host reads it) and marks the
+// launch, so that its remaining CTAs leave at once.
+__device__ __forceinline__ void give_up(const Sm100Args& a, int code) {
+  atomicCAS(a.status, 0, code);
+  reinterpret_cast<volatile int32_t*>(a.status)[1] = int32_t(a.epoch);
+}
+
 template <int D, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const __grid_constant__ Sm100Args a) {
   using L = Smem<D>;
@@ -140,7 +149,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   const int g = gh / a.heads_per_group, h = gh % a.heads_per_group;
   const int b = int(blockIdx.x) / n_heads;
 
-  if (*reinterpret_cast<volatile int32_t*>(a.status) != 0) return;  // an earlier CTA gave up: drain the grid
+  if (reinterpret_cast<volatile int32_t*>(a.status)[1] == int32_t(a.epoch)) return;  // a CTA of this launch gave up: drain the grid
 
   int q_row0 = 0, k_row0 = 0, qlen = a.mq, klen = a.mkv, tb = b;
   if (a.seqstart_q != nullptr) {
@@ -152,8 +161,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   }
   const int m0 = qt * kBM * kTiles;
   if (m0 >= qlen) return;
-  const bool causal = a.mask_type != XFB200_MASK_NONE;
-  const int shift = (a.mask_type == XFB200_MASK_CAUSAL_BOTTOM_RIGHT ? klen - qlen : 0) - a.kv_offset;
+  // query i sees key j iff i + shift - window_left <= j <= i + shift + wr (each bound only when it is >= 0)
+  const int wr = a.window_right;
+  const bool causal = wr >= 0;
+  const int shift = (a.bottom_right ? klen - qlen : 0) - a.kv_offset;
 
   // Key-tile range [jlo_t, jhi_t) of each query tile, in units of kBN keys from n_base.
   int jlo[kTiles], jhi[kTiles];
@@ -164,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
   for (int t = 0; t < kTiles; ++t) {
     const int mt0 = m0 + t * kBM;
     int hi = klen, lo = n_base;
-    if (causal) hi = min(hi, mt0 + kBM + shift);
+    if (causal) hi = min(hi, mt0 + kBM + shift + wr);
     if (a.window_left >= 0) lo = max(n_base, max(0, mt0 + shift - a.window_left) / kBN * kBN);
     if (mt0 >= qlen) hi = lo;  // no valid row in this tile
     jlo[t] = (lo - n_base) / kBN;
@@ -222,19 +233,20 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         const int it = j - j_begin, st = it % kStagesK, use = it / kStagesK;
         const int sv = it % kStagesV, use_v = it / kStagesV;
         const int row = k_row0 + n_base + j * kBN;
-        if (use > 0 && !mbar_wait(&bar->k_empty[st], (use - 1) & 1, abort_flag)) {
-          atomicExch(a.status, 11);
+        if (use > 0 && !mbar_wait(&bar->k_empty[st], (use - 1) & 1, abort_flag, a.wait_budget)) {
+          give_up(a, 11);
           *abort_flag = 1;
           break;
         }
-        {
+        // (testing aid: the first CTA leaves out its last key tile, so that the wait for it runs out)
+        if (!((a.debug_flags & 1) && blockIdx.x == 0 && blockIdx.y == 0 && j == j_end - 1)) {
           mbar_expect_tx(&bar->k_full[st], L::kKV);
 #pragma unroll
           for (int hf = 0; hf < kHalves; ++hf)
             tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, kv_head, row, tb);
         }
-        if (use_v > 0 && !mbar_wait(&bar->v_empty[sv], (use_v - 1) & 1, abort_flag)) {
-          atomicExch(a.status, 12);
+        if (use_v > 0 && !mbar_wait(&bar->v_empty[sv], (use_v - 1) & 1, abort_flag, a.wait_budget)) {
+          give_up(a, 12);
           *abort_flag = 1;
           break;
         }
@@ -295,8 +307,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       int ks = 0, kph = 0;  // K stage / phase of tile j
       int vs = 0, vph = 0;  // V stage / phase of tile j
       int cnt = 0;          // products of this query tile so far
-      ok = mbar_wait(&bar->q_full, 0, abort_flag) && mbar_wait(&bar->k_full[0], 0, abort_flag);
-      if (!ok && lane == 0) atomicExch(a.status, 21);
+      ok = mbar_wait(&bar->q_full, 0, abort_flag, a.wait_budget) && mbar_wait(&bar->k_full[0], 0, abort_flag, a.wait_budget);
+      if (!ok && lane == 0) give_up(a, 21);
       if (ok) {
         tc_fence_after();
         if (lane == 0) {
@@ -315,10 +327,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         const bool act_next = has_next && (j + 1) >= jlo[t] && (j + 1) < jhi[t];
         int ks1 = ks + 1, kph1 = kph;
         if (ks1 == kStagesK) ks1 = 0, kph1 ^= 1;
-        ok = mbar_wait(&bar->v_full[vs], vph, abort_flag);
-        if (ok && has_next) ok = mbar_wait(&bar->k_full[ks1], kph1, abort_flag);
+        ok = mbar_wait(&bar->v_full[vs], vph, abort_flag, a.wait_budget);
+        if (ok && has_next) ok = mbar_wait(&bar->k_full[ks1], kph1, abort_flag, a.wait_budget);
         if (!ok) {
-          if (lane == 0) atomicExch(a.status, 22);
+          if (lane == 0) give_up(a, 22);
           break;
         }
         const int n0 = n_base + j * kBN;
@@ -333,9 +345,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
           __syncwarp();
         }
         if (act) {
-          ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag);
+          ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag, a.wait_budget);
           if (!ok) {
-            if (lane == 0) atomicExch(a.status, 23 + t);
+            if (lane == 0) give_up(a, 23 + t);
             break;
           }
           tc_fence_after();
@@ -346,10 +358,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
         // therefore issued alternately, which keeps the two tiles half a period
         // apart; the token is passed a few MMAs before the end of a block so
         // that the hand-over latency is hidden.
-        ok = mbar_wait(&bar->turn[t], turn_ph, abort_flag);
+        ok = mbar_wait(&bar->turn[t], turn_ph, abort_flag, a.wait_budget);
         turn_ph ^= 1;
         if (!ok) {
-          if (lane == 0) atomicExch(a.status, 25 + t);
+          if (lane == 0) give_up(a, 25 + t);
           break;
         }
         if (lane == 0) {
@@ -385,7 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     const uint32_t tmem_o = tmem + 256 + t * 128 + lane_sel;
     const int mt0 = m0 + t * kBM;
     const int i_loc = mt0 + row;
-    const int col_hi = causal ? min(klen, i_loc + shift + 1) : klen;
+    const int col_hi = causal ? min(klen, i_loc + shift + wr + 1) : klen;
     const int col_lo = a.window_left >= 0 ? i_loc + shift - a.window_left : 0;
     const float sl2 = a.scale_log2;
     float m_run = -INFINITY, l_run = 0.f;
@@ -394,9 +406,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
 
     for (int j = jlo[t]; j < jhi[t]; ++j, ++cnt) {
       const int n0 = n_base + j * kBN;
-      ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag);
+      ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag, a.wait_budget);
       if (!ok) {
-        atomicExch(a.status, 31 + t);
+        give_up(a, 31 + t);
         *abort_flag = 1;
         break;
       }
@@ -410,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
       tc_wait_ld();
       float* s = reinterpret_cast<float*>(sr);
 
-      const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift) ||
+      const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + wr) ||
                              (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
       if (need_mask) {
 #pragma unroll
@@ -499,8 +511,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_m256_kernel(const _
     // ---- epilogue
     const bool have = cnt > 0;
     if (ok && have) {
-      ok = mbar_wait(&bar->pv_done[t], (cnt - 1) & 1, abort_flag);
-      if (!ok) atomicExch(a.status, 33 + t);
+      ok = mbar_wait(&bar->pv_done[t], (cnt - 1) & 1, abort_flag, a.wait_budget);
+      if (!ok) give_up(a, 33 + t);
       tc_fence_after();
     }
     const bool valid_row = i_loc < qlen;
@@ -558,11 +570,10 @@ template <int D, bool kBf16>
 static int launch_t(const Sm100Args& a, cudaStream_t stream) {
   auto kern = prefill_sm100_m256_kernel<D, kBf16>;
   constexpr int smem = Smem<D>::kTotal;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxDevices] = {false};  // the attribute belongs to the device's context
+  if (first_use_on_device(configured)) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_fail("prefill(sm100, 256 rows): cudaFuncSetAttribute", e);
-    configured = true;
   }
   const int64_t bh = int64_t(a.groups) * a.heads_per_group * a.batch;
   if (bh > 0x7fffffff || a.q_tiles > 65535) return set_error(XFB200_E_UNSUPPORTED, "prefill: grid too large");

@@ -53,14 +53,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // wait inside these kernels) or as soon as `abort_flag` (shared memory, set by
 // a sibling warp that already gave up) becomes non-zero.
 constexpr long long kWaitBudgetCycles = 400000000LL;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag = nullptr) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag = nullptr,
+                                          long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0) {
       if (abort_flag != nullptr && *abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) return false;
+      if (clock64() - t0 > budget_cycles) return false;
     }
   }
 }
@@ -184,6 +185,18 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                      \
       : "r"(taddr)                                                                                                     \
       : "memory")
+
+// tcgen05.wait::ld with the 32 destination registers of an earlier load tied to it as
+// read-write operands: nothing that reads them can be scheduled above the wait.
+#define XFB_TMEM_WAIT_LD_32(r)                                                                                          \
+  asm volatile("tcgen05.wait::ld.sync.aligned;"                                                                        \
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),       \
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), \
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]),           \
+                 "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),           \
+                 "+r"(r[30]), "+r"(r[31])                                                                              \
+               :                                                                                                       \
+               : "memory")
 
 #define XFB_TMEM_ST_16(taddr, r)                                                                                      \
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" \

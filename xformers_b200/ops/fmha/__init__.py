@@ -3,8 +3,9 @@
 operator base classes and dispatcher, with B200-native operators registered.
 
 Out of scope and therefore absent: the backward pass
-(``memory_efficient_attention`` with autograd, ``*BwOp``), dropout, and the
-reference's other backends (``cutlass``, ``flash``, ``flash3``, ``ck``).
+(``memory_efficient_attention`` raises when autograd would have to record the
+call; ``*BwOp``), dropout, and the reference's other backends (``cutlass``,
+``flash``, ``flash3``, ``ck``).
 """
 
 from __future__ import annotations
@@ -37,7 +38,7 @@ MemoryEfficientAttentionB200SplitKOp = (b200_splitk.FwOp, None)
 
 ALL_FW_OPS: List[Type[AttentionFwOpBase]] = [b200.FwOp, b200_splitk.FwOp]
 ALL_BW_OPS: List[Type[AttentionBwOpBase]] = []
-_OPS_LOOKUP = {op.NAME: op for op in ALL_FW_OPS + [b200.FwOp_Generic, b200.FwOp_Tcgen05, b200.FwOp_Tcgen05_M256, b200.FwOp_Tcgen05_S64] + list(b200_splitk.FwOp_Map.values())}
+_OPS_LOOKUP = {op.NAME: op for op in ALL_FW_OPS + [b200.FwOp_Generic, b200.FwOp_Tcgen05, b200.FwOp_Tcgen05_M256, b200.FwOp_Tcgen05_Persistent] + list(b200_splitk.FwOp_Map.values())}
 
 
 def _serialize_op(op):
@@ -143,11 +144,33 @@ def memory_efficient_attention_partial(
     return out, lse
 
 
-def memory_efficient_attention(*args, **kwargs):
-    raise NotImplementedError(
-        "memory_efficient_attention with autograd (backward pass) is outside this library; "
-        "use memory_efficient_attention_forward"
-    )
+def memory_efficient_attention(
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attn_bias: Optional[Union[torch.Tensor, AttentionBias]] = None,
+    p: float = 0.0,
+    scale: Optional[float] = None,
+    *,
+    op=None,
+    output_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """The reference's main entry point (xformers/ops/__init__.py:16; called as
+    such by examples/llama_inference/model.py:142 and in the docstring of
+    xformers/ops/rope_padded.py:49-53).  When no input asks for a gradient, or
+    gradient mode is off, it is the forward pass and runs here; the backward
+    pass is outside this library, so a call that autograd would have to record
+    raises ``NotImplementedError``."""
+    if torch.is_grad_enabled() and any(t.requires_grad for t in (query, key, value)):
+        raise NotImplementedError(
+            "memory_efficient_attention: an input requires grad, and the backward pass is outside this library; "
+            "call it under torch.no_grad(), or use memory_efficient_attention_forward"
+        )
+    if isinstance(attn_bias, torch.Tensor) and torch.is_grad_enabled() and attn_bias.requires_grad:
+        raise NotImplementedError("memory_efficient_attention: attn_bias requires grad; the backward pass is outside this library")
+    if p != 0.0:
+        raise NotImplementedError("dropout is outside the forward hot path")
+    return _run_forward(Inputs(query, key, value, attn_bias, p, scale, output_dtype), op, needs_lse=False)[0]
 
 
 from . import torch_library  # noqa: E402,F401  (defines torch.ops.xformers_b200.memory_efficient_attention_forward[_with_bias])

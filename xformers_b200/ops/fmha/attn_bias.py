@@ -571,6 +571,42 @@ class BlockDiagonalCausalLocalAttentionPaddedKeysMask(BlockDiagonalPaddedKeysMas
 
 
 @dataclass
+class BlockDiagonalLocalAttentionPaddedKeysMask(BlockDiagonalPaddedKeysMask):
+    """Padded-keys block-diagonal mask with a band around the bottom-right
+    diagonal instead of a causal one: query i of a block of ql queries sees key
+    t of its sequence iff ``i + kv_seqlen[b] - ql - window_left <= t <= i +
+    kv_seqlen[b] - ql + window_right`` (xformers/ops/fmha/attn_bias.py:35; the
+    band of ``LocalAttentionFromBottomRightMask``, tests/test_mem_eff_attention.py:2389-2399,
+    per sequence)."""
+
+    window_left: int = 0
+    window_right: int = 0
+
+    def __post_init__(self) -> None:
+        if self.window_left < 0 or self.window_right < 0:
+            raise ValueError(f"Expected non-negative windows, got ({self.window_left}, {self.window_right})")
+
+    def to(self, device):
+        return type(self)(q_seqinfo=self.q_seqinfo.to(device), k_seqinfo=self.k_seqinfo.to(device),
+                          window_left=self.window_left, window_right=self.window_right)
+
+    def _block(self, ql: int, kl: int, device) -> torch.Tensor:
+        return _band(ql, kl, device, shift=kl - ql, window_left=self.window_left, window_right=self.window_right)
+
+    @classmethod
+    def from_seqlens_local(cls, q_seqlen: Sequence[int], kv_padding: int, kv_seqlen: Sequence[int], window_left: int,
+                           window_right: int, *, device=None):
+        if len(q_seqlen) != len(kv_seqlen):
+            raise ValueError("q_seqlen and kv_seqlen must describe the same number of sequences")
+        return cls(
+            q_seqinfo=_SeqLenInfo.from_seqlens(q_seqlen, device=device),
+            k_seqinfo=_PaddedSeqLenInfo.from_seqlens_padded(kv_seqlen, kv_padding, device=device),
+            window_left=window_left,
+            window_right=window_right,
+        )
+
+
+@dataclass
 class BlockDiagonalGappyKeysMask(BlockDiagonalPaddedKeysMask):
     """Keys of sequence b are the rows ``[kv_seqstarts[b], kv_seqstarts[b] +
     kv_seqlen[b])`` of the flat key tensor: like the padded-keys mask, but the
@@ -607,6 +643,40 @@ class BlockDiagonalGappyKeysMask(BlockDiagonalPaddedKeysMask):
 @dataclass
 class BlockDiagonalCausalWithOffsetGappyKeysMask(BlockDiagonalGappyKeysMask):
     _CAUSAL: ClassVar[bool] = True
+
+
+@dataclass
+class BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask(BlockDiagonalGappyKeysMask):
+    """Gappy-keys block-diagonal mask with a band around the bottom-right
+    diagonal of every block: query i of a block of ql queries sees key t of its
+    sequence iff ``i + kv_seqlen[b] - ql - window_left <= t <= i + kv_seqlen[b] -
+    ql + window_right`` (xformers/ops/fmha/attn_bias.py:34)."""
+
+    window_left: int = 0
+    window_right: int = 0
+
+    def __post_init__(self) -> None:
+        if self.window_left < 0 or self.window_right < 0:
+            raise ValueError(f"Expected non-negative windows, got ({self.window_left}, {self.window_right})")
+
+    def to(self, device):
+        return type(self)(q_seqinfo=self.q_seqinfo.to(device), k_seqinfo=self.k_seqinfo.to(device),
+                          window_left=self.window_left, window_right=self.window_right)
+
+    def _block(self, ql: int, kl: int, device) -> torch.Tensor:
+        return _band(ql, kl, device, shift=kl - ql, window_left=self.window_left, window_right=self.window_right)
+
+    @classmethod
+    def from_seqlens_local(cls, q_seqlen: Sequence[int], kv_seqstarts: Sequence[int], kv_seqlen: Sequence[int],
+                           window_left: int, window_right: int, *, device=None):
+        if len(q_seqlen) != len(kv_seqlen):
+            raise ValueError("q_seqlen and kv_seqlen must describe the same number of sequences")
+        return cls(
+            q_seqinfo=_SeqLenInfo.from_seqlens(q_seqlen, device=device),
+            k_seqinfo=_GappySeqInfo.from_seqlens_gappy(kv_seqstarts, kv_seqlen, device=device),
+            window_left=window_left,
+            window_right=window_right,
+        )
 
 
 @dataclass

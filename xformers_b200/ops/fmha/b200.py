@@ -3,8 +3,9 @@
 Slots into the dispatcher next to the reference's forward operators
 (``fmha.cutlass_blackwell.FwOp``, ``fmha.flash.FwOp``; registration record as
 tests/test_mem_eff_attention.py:104-111 reads it).  The arithmetic is done by
-``xfb200_prefill_forward`` of libxfb200.so: a TMA + tcgen05/TMEM kernel for
-head dims 64 and 128, an mma.sync kernel for the other head dims.
+``xfb200_prefill_forward`` of libxfb200.so: a persistent TMA + tcgen05/TMEM
+kernel for head dims 64 and 128, an mma.sync kernel for the other head dims
+and for additive tensor biases.
 """
 
 from __future__ import annotations
@@ -16,6 +17,9 @@ import torch
 
 from ... import _lib
 from .attn_bias import (
+    BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask,
+    BlockDiagonalLocalAttentionPaddedKeysMask,
+    LocalAttentionFromBottomRightMask,
     BlockDiagonalCausalFromBottomRightMask,
     BlockDiagonalCausalLocalAttentionFromBottomRightMask,
     BlockDiagonalCausalLocalAttentionMask,
@@ -55,30 +59,55 @@ def _bias_tensor(bias: Any) -> Optional[torch.Tensor]:
     return None
 
 
-def _mask_of(bias: Any) -> Tuple[int, int]:
-    """(mask_type, window_left) of a bias object."""
+def _mask_of(bias: Any) -> Tuple[int, int, int]:
+    """(mask_type, window_left, window_right) of a bias object."""
     if bias is None or type(bias) in (BlockDiagonalMask, BlockDiagonalPaddedKeysMask, BlockDiagonalGappyKeysMask):
-        return _lib.MASK_NONE, -1
+        return _lib.MASK_NONE, -1, 0
     if isinstance(bias, torch.Tensor):
-        return _lib.MASK_NONE, -1
+        return _lib.MASK_NONE, -1, 0
     if type(bias) in (LowerTriangularMask, BlockDiagonalCausalMask, LowerTriangularMaskWithTensorBias):
-        return _lib.MASK_CAUSAL_TOP_LEFT, -1
+        return _lib.MASK_CAUSAL_TOP_LEFT, -1, 0
     if type(bias) in (
         LowerTriangularFromBottomRightMask,
         BlockDiagonalCausalFromBottomRightMask,
         BlockDiagonalCausalWithOffsetPaddedKeysMask,
         BlockDiagonalCausalWithOffsetGappyKeysMask,
     ):
-        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, -1
+        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, -1, 0
     if type(bias) in (LowerTriangularMaskLocalAttention, BlockDiagonalCausalLocalAttentionMask):
-        return _lib.MASK_CAUSAL_TOP_LEFT, bias._window_size - 1
+        return _lib.MASK_CAUSAL_TOP_LEFT, bias._window_size - 1, 0
     if type(bias) in (
         BlockDiagonalCausalLocalAttentionFromBottomRightMask,
         BlockDiagonalCausalLocalAttentionPaddedKeysMask,
         LowerTriangularFromBottomRightLocalAttentionMask,
     ):
-        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, bias._window_size - 1
+        return _lib.MASK_CAUSAL_BOTTOM_RIGHT, bias._window_size - 1, 0
+    if type(bias) in (
+        LocalAttentionFromBottomRightMask,
+        BlockDiagonalLocalAttentionPaddedKeysMask,
+        BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask,
+    ):
+        return _lib.MASK_LOCAL_BOTTOM_RIGHT, bias.window_left, bias.window_right
     raise NotImplementedError(f"bias {type(bias)}")
+
+
+def _debug_check_varlen(bias, total_q: int, total_k: int) -> None:
+    """Host-side validation of the device arrays a varlen bias carries
+    (``XFB200_DEBUG_CHECKS=1``): the kernels trust them."""
+    qs = bias.q_seqinfo.seqstart.cpu().tolist()
+    ks = bias.k_seqinfo.seqstart.cpu().tolist()
+    if any(b < a for a, b in zip(qs, qs[1:])) or qs[0] < 0 or qs[-1] > total_q:
+        raise ValueError(f"q_seqinfo.seqstart {qs} is not a monotone partition of {total_q} query rows")
+    if any(x < 0 or x > total_k for x in ks):
+        raise ValueError(f"k_seqinfo.seqstart {ks} leaves the {total_k} key rows")
+    if isinstance(bias, BlockDiagonalPaddedKeysMask):
+        lens = bias.k_seqinfo.seqlen.cpu().tolist()
+        for i, n in enumerate(lens):
+            slot = (ks[i + 1] if i + 1 < len(ks) else total_k) - ks[i]
+            if n < 0 or n > slot:
+                raise ValueError(f"k_seqinfo.seqlen[{i}] = {n} does not fit its slot of {slot} rows")
+    elif any(b < a for a, b in zip(ks, ks[1:])):
+        raise ValueError(f"k_seqinfo.seqstart {ks} is not monotone")
 
 
 class FwOp(AttentionFwOpBase):
@@ -105,6 +134,9 @@ class FwOp(AttentionFwOpBase):
         LowerTriangularFromBottomRightLocalAttentionMask,
         BlockDiagonalGappyKeysMask,
         BlockDiagonalCausalWithOffsetGappyKeysMask,
+        LocalAttentionFromBottomRightMask,
+        BlockDiagonalLocalAttentionPaddedKeysMask,
+        BlockDiagonalLocalAttentionFromBottomRightGappyKeysMask,
         torch.Tensor,
         LowerTriangularMaskWithTensorBias,
     )
@@ -116,8 +148,11 @@ class FwOp(AttentionFwOpBase):
     SUPPORTS_BMGHK = True
     VARLEN_LSE_PACKED = True
     _TEST_K = [32, 64, 128, 256]
-    # 0 = automatic; 1 = force the mma.sync kernel; 2 = require the tcgen05 kernel
-    KERNEL_PATH = 0
+    # which kernel may run the call (XFB200_PREFILL_* of the C ABI): 0 = automatic
+    KERNEL_PATH = _lib.PREFILL_AUTO
+    # testing aids of the bounded waits (see include/xfb200.h); 0 in production
+    _WAIT_BUDGET_KCYCLES = 0
+    _DEBUG_FLAGS = 0
 
     @classmethod
     def shape_not_supported_reasons(cls, Mq: int, Mkv: int, K: int, Kv: int) -> List[str]:
@@ -162,7 +197,7 @@ class FwOp(AttentionFwOpBase):
                 reasons.append("additive bias needs unit stride on its last axis")
             if bt.dtype not in _DTYPE_CODE:
                 reasons.append(f"additive bias dtype {bt.dtype}")
-            if cls.KERNEL_PATH >= 2:
+            if cls.KERNEL_PATH >= _lib.PREFILL_TCGEN05:
                 reasons.append("additive biases run on the mma.sync kernel only")
         return reasons
 
@@ -191,7 +226,9 @@ class FwOp(AttentionFwOpBase):
                 if lse is not None:
                     lse.fill_(float("-inf"))
             else:
-                mask_type, window_left = _mask_of(bias)
+                mask_type, window_left, window_right = _mask_of(bias)
+                if varlen and _lib.debug_checks():
+                    _debug_check_varlen(bias, Mq, Mkv)
                 p = _lib.PrefillParams()
                 p.q, p.k, p.v, p.out = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr()
                 p.lse = _ptr(lse)
@@ -216,17 +253,17 @@ class FwOp(AttentionFwOpBase):
                     b5 = bt if bt.ndim == 5 else bt.unsqueeze(1)  # [B, G, H, Mq, Mkv]
                     p.bias, p.bias_dtype = b5.data_ptr(), _DTYPE_CODE[b5.dtype]
                     p.bias_stride_b, p.bias_stride_g, p.bias_stride_h, p.bias_stride_m = b5.stride(0), b5.stride(1), b5.stride(2), b5.stride(3)
-                p.mask_type, p.kv_offset, p.window_left = mask_type, kv_offset, window_left
+                p.mask_type, p.kv_offset, p.window_left, p.window_right = mask_type, kv_offset, window_left, window_right
                 p.scale = inp.scale_float
+                p.kernel_path = cls.KERNEL_PATH
+                p.wait_budget_kcycles, p.debug_flags = cls._WAIT_BUDGET_KCYCLES, cls._DEBUG_FLAGS
                 lib = _lib.load()
-                if cls.KERNEL_PATH:
-                    lib.xfb200_debug_set_prefill_path(cls.KERNEL_PATH)
-                try:
+                # launch on q's device, whatever the current one is
+                with torch.cuda.device(q.device):
                     rc = lib.xfb200_prefill_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
-                finally:
-                    if cls.KERNEL_PATH:
-                        lib.xfb200_debug_set_prefill_path(0)
-                _lib.check(rc, "b200.FwOp")
+                    _lib.check(rc, "b200.FwOp")
+                    if _lib.check_status_after_every_call():
+                        check_device_status(q.device)
 
         if inp.query.ndim == 4:
             out = out[:, :, 0]
@@ -242,38 +279,49 @@ class FwOp_Generic(FwOp):
     """Same operator pinned to the mma.sync kernel (tests, comparisons)."""
 
     NAME = "b200F-mma"
-    KERNEL_PATH = 1
+    KERNEL_PATH = _lib.PREFILL_MMA_SYNC
 
 
 class FwOp_Tcgen05(FwOp):
-    """Same operator, failing unless the tcgen05 kernel covers the input."""
+    """Same operator, failing unless a tcgen05 kernel covers the input."""
 
     NAME = "b200F-tc5"
-    KERNEL_PATH = 2
+    KERNEL_PATH = _lib.PREFILL_TCGEN05
     SUPPORTED_MAX_K = 128
     _TEST_K = [64, 128]
 
 
+class FwOp_Tcgen05_Persistent(FwOp_Tcgen05):
+    """tcgen05 kernel, one persistent CTA per SM pulling blocks of 256 query rows (the default)."""
+
+    NAME = "b200F-tc5-persistent"
+    KERNEL_PATH = _lib.PREFILL_TCGEN05_PERSISTENT
+
+
 class FwOp_Tcgen05_M256(FwOp_Tcgen05):
-    """tcgen05 kernel with 128-key steps and one score buffer per query tile."""
+    """tcgen05 kernel with one CTA per block of 256 query rows."""
 
     NAME = "b200F-tc5-m256"
-    KERNEL_PATH = 4
-
-
-class FwOp_Tcgen05_S64(FwOp_Tcgen05):
-    """tcgen05 kernel with 64-key steps and two score buffers per query tile."""
-
-    NAME = "b200F-tc5-s64"
-    KERNEL_PATH = 5
+    KERNEL_PATH = _lib.PREFILL_TCGEN05_CTA
 
 
 def prefill_device_status(device=None) -> int:
-    """Status word of the tcgen05 kernel on ``device`` (0 = every wait was
-    satisfied).  Synchronises the current stream; meant for tests."""
+    """Code of the first wait a tcgen05 prefill kernel gave up on ``device`` since the
+    last call (0 = none), cleared by the call.  Synchronises the current stream."""
     dev = torch.device("cuda" if device is None else device)
     with torch.cuda.device(dev):
         st = C.c_int32(0)
         rc = _lib.load().xfb200_prefill_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st))
-        _lib.check(rc, "prefill_device_status")
+        if rc != _lib.XFB200_E_DEVICE:
+            _lib.check(rc, "prefill_device_status")
     return st.value
+
+
+def check_device_status(device=None) -> None:
+    """Raises ``RuntimeError`` when a prefill kernel gave up a wait on ``device``
+    (its output is not valid); clears the status.  Synchronises the current stream."""
+    dev = torch.device("cuda" if device is None else device)
+    with torch.cuda.device(dev):
+        st = C.c_int32(0)
+        rc = _lib.load().xfb200_prefill_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st))
+        _lib.check(rc, "b200.FwOp")

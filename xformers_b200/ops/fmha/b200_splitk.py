@@ -54,6 +54,52 @@ def _geometry(inp: Inputs):
 _LOCAL_BIASES = (BlockDiagonalCausalLocalAttentionPaddedKeysMask, PagedBlockDiagonalCausalLocalPaddedKeysMask)
 
 
+def _debug_check_decode(bias, p, k: torch.Tensor) -> None:
+    """Host-side validation of the device arrays a decode call trusts
+    (``XFB200_DEBUG_CHECKS=1``): lengths within their slots, page ids within the pool."""
+    if not isinstance(bias, (BlockDiagonalPaddedKeysMask, PagedBlockDiagonalPaddedKeysMask)):
+        return
+    lens = bias.k_seqinfo.seqlen.cpu().tolist()
+    if any(n < 0 or n > p.kv_padding for n in lens):
+        raise ValueError(f"kv_seqlen {lens} does not fit the slot of {p.kv_padding} keys")
+    if isinstance(bias, PagedBlockDiagonalPaddedKeysMask):
+        num_pages = k.shape[1] // bias.page_size
+        table = bias.block_tables.cpu()
+        for b, n in enumerate(lens):
+            first = 0
+            if isinstance(bias, PagedBlockDiagonalGappyKeysMask):
+                first = int(bias.slot_starts()[b])
+            used = table[b, first // bias.page_size : -(-(first + n) // bias.page_size)] if n > 0 else table[b, :0]
+            if used.numel() and (int(used.min()) < 0 or int(used.max()) >= num_pages):
+                raise ValueError(f"block_tables[{b}] names a page outside the pool of {num_pages} pages")
+    else:
+        starts = bias.k_seqinfo.seqstart.cpu().tolist()
+        for b, n in enumerate(lens):
+            if starts[b] < 0 or starts[b] + n > k.shape[1]:
+                raise ValueError(f"sequence {b}: keys [{starts[b]}, {starts[b] + n}) leave the {k.shape[1]} rows of the cache")
+
+
+def decode_device_status(device=None) -> int:
+    """Code of the first wait a decode kernel gave up on ``device`` since the last
+    call (0 = none), cleared by the call.  Synchronises the current stream."""
+    dev = torch.device("cuda" if device is None else device)
+    with torch.cuda.device(dev):
+        st = C.c_int32(0)
+        rc = _lib.load().xfb200_decode_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st))
+        if rc != _lib.XFB200_E_DEVICE:
+            _lib.check(rc, "decode_device_status")
+    return st.value
+
+
+def check_device_status(device=None) -> None:
+    """Raises ``RuntimeError`` when a decode kernel gave up a wait on ``device``; clears the status."""
+    dev = torch.device("cuda" if device is None else device)
+    with torch.cuda.device(dev):
+        st = C.c_int32(0)
+        rc = _lib.load().xfb200_decode_device_status(C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st))
+        _lib.check(rc, "b200_splitk.FwOp")
+
+
 class FwOp(AttentionFwOpBase):
     """Flash-decoding on sm_100a.  ``SPLIT_K = None`` picks the split count."""
 
@@ -258,7 +304,6 @@ class FwOp(AttentionFwOpBase):
                     p.kv_padding = bias.k_seqinfo.padding
                     if isinstance(bias, BlockDiagonalGappyKeysMask):
                         kv_start = bias.k_seqinfo.seqstart
-                        p.kv_rows = k.shape[1]
                 if kv_start is not None:
                     p.kv_seqstart = kv_start.data_ptr()
                 if isinstance(
@@ -278,6 +323,10 @@ class FwOp(AttentionFwOpBase):
                 p.batch, p.mq = B, Mq
                 p.seqlen_k = None
                 p.kv_padding = k.shape[1]
+            # token rows of the cache tensors: bounds the tiled copies, so that a bad page-table entry reads zeros
+            p.kv_rows = B * k.shape[1]
+            if _lib.debug_checks():
+                _debug_check_decode(bias, p, k)
             row_bytes = D if fp8 else (D // 8 + cls.NUM_GROUPS) * 4 if quantized else D * 2
             p.split_k = cls.get_split_k(p.batch, min(p.kv_padding, p.window_size) if p.window_size else p.kv_padding, p.kv_heads, row_bytes)
             lib = _lib.load()
@@ -287,7 +336,9 @@ class FwOp(AttentionFwOpBase):
             p.scale = inp.scale_float
             with torch.cuda.device(q.device):
                 rc = lib.xfb200_decode_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream(q.device).cuda_stream))
-            _lib.check(rc, cls.NAME)
+                _lib.check(rc, cls.NAME)
+                if _lib.check_status_after_every_call():
+                    check_device_status(q.device)
 
         if lse is not None:
             lse = lse.view(G, H, B, Mq).permute(2, 0, 1, 3)
