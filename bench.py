@@ -14,12 +14,19 @@ batch of synthetic input:
 * `e2e`: the same metric through the public API with HOST (pinned) q/k/v and a
   host copy of the output inside the timed region.
 * `roofline`: tensor-pipe roofline of the prefill kernel against the measured
-  cuBLAS bf16 peak of this pool (MEASURED_PEAKS.json), `decode_bf16` /
-  `decode_int4`: KV-read GB/s of the split-K decode configuration (64
-  sequences, lengths U[1024,32768], paged 256, Hq=64/Hkv=8) with their HBM
-  rooflines, `varlen_gqa`: the packed varlen GQA prefill configuration,
+  cuBLAS bf16 peak of this pool (MEASURED_PEAKS.json); `sustained`: the same
+  kernel over a timed region of at least a second, against the sustained peak.
+  `decode_bf16` / `decode_int4` / `decode_fp8`: KV-read GB/s of the split-K
+  decode configuration (64 sequences, lengths U[1024,32768], paged 256,
+  Hq=64/Hkv=8) with their HBM rooflines, `rope_padded`, `varlen_gqa`: the packed
+  varlen GQA prefill configuration; these legs are medians of CUDA-graph replays.
   `long_context`: one 131072-token causal sequence with the key axis sharded
-  over the N ranks (NCCL all-gather of partials + LSE merge).
+  over the N ranks in two ranges each (equal causal work), partials exchanged by
+  NCCL all-to-all per query slice, LSE merge, all-gather of the merged slices;
+  `long_context_contiguous`: the same sequence with one contiguous key shard per
+  rank and an all-gather of the partials.
+* every leg carries `parity`: a slice of that leg's own output compared with
+  the CPU oracle outside the timed region (max-abs error of O and of the LSE).
 * `cpu_baseline`: the CPU oracle timed on a bounded slice of the headline
   configuration on this box's host cores (a reported baseline only).
 
@@ -53,8 +60,8 @@ CFG2 = dict(B=4, M=4096, H=32, D=128)
 CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch, from the ncu captures summarised
-# under profiles/: bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch: constants taken from the ncu captures
+# summarised under profiles/ (a run of this script does not measure them): bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
 NCU_TRAFFIC = {"prefill": 141.44e6 + 19.52e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
                "decode_fp8": (613.01e6 + 14.01e6) / 505.51e6, "rope": (100.70e6 + 55.24e6) / 201.33e6}
@@ -143,10 +150,10 @@ def use_all_host_threads():
 
 
 def cpu_step(q, k, v):
+    # (the CPU arm imports the oracle only: nothing of the product package is loaded into its process)
     import oracle
-    from xformers_b200.ops.fmha.attn_bias import LowerTriangularMask
 
-    return oracle.ref_attention_with_lse(q, k, v, LowerTriangularMask())
+    return oracle.ref_attention_with_lse(q, k, v, oracle.causal_mask(q.shape[1], k.shape[1]))
 
 
 def time_cpu(budget_s: float, max_reps: int, warmup: int = 1):
@@ -184,7 +191,10 @@ def run_reference_arm(args):
         "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference attention (oracle); mslk, which holds the reference kernels, is not installable offline"},
+        "config": {"workload": WORKLOAD, "per_gpu_batch": CFG2["B"], "l2": "inputs (512 MiB per step) exceed the 126 MB L2",
+                   "parallelism": f"batch-sharded x{args.gpus}, no communication", "peaks": load_peaks()["source"],
+                   "sample": f"each step computes B={CPU_SAMPLE['B']} x H={CPU_SAMPLE['H']} heads of the workload (1/{CFG2['B'] * CFG2['H'] // (CPU_SAMPLE['B'] * CPU_SAMPLE['H'])} of it); value = FLOPs of the sample / time",
+                   "note": "CPU restatement of the reference attention (oracle); mslk, which holds the reference kernels, is not installable offline"},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -212,6 +222,73 @@ def event_time_ms(fn, steps, warmup, barrier=None):
     if barrier is not None:
         barrier()
     return e0.elapsed_time(e1), (t0, t1)
+
+
+def graph_time_ms(fn, reps, warmup=3):
+    """Median device time of ``reps`` replays of a CUDA graph holding one call of ``fn`` (the reference's
+    harness times its decode operators the same way, xformers/benchmarks/utils.py:733-750).  The eager
+    warm-up calls come first: whatever a first call sets up happens outside the capture."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    t0 = time.time()
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        times.append((e0, e1))
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = sorted(a.elapsed_time(b) for a, b in times)
+    return statistics.median(ms), ms[0], (t0, t1)
+
+
+def parity_block(out, lse, ref_out, ref_lse, rows):
+    """max-abs error of a slice of a leg's output against the oracle (tolerances: O 2e-2 for bf16, LSE 1e-3)."""
+    eo = float((out.float().cpu() - ref_out).abs().max()) if out is not None else None
+    el = None
+    if lse is not None:
+        l, r = lse.float().cpu(), ref_lse
+        el = float(torch.where(torch.isneginf(l) & torch.isneginf(r), torch.zeros_like(l), (l - r).abs()).max())
+    ok = (eo is None or eo <= 2e-2) and (el is None or el <= 1e-3)
+    return {"max_abs_o": eo, "max_abs_lse": el, "rows": rows, "ok": bool(ok), "tolerance": "O 2e-2, LSE 1e-3"}
+
+
+def decode_parity(q, k, v, bias, out, lse, quant, kss=None, vss=None, n_seqs=4):
+    """Oracle check of a few sequences of a paged decode leg: their pages are gathered, dequantised on the host."""
+    import oracle
+
+    lens = bias.k_seqinfo.seqlen_py
+    order = sorted(range(len(lens)), key=lambda i: lens[i])
+    picks = sorted(set([order[0], order[-1]] + order[len(order) // 3 :: max(1, len(order) // 3)][: n_seqs - 2]))
+    eo = el = 0.0
+    for b in picks:
+        rows = torch.from_numpy(oracle.physical_rows(bias.block_tables, bias.page_size, b, lens[b])).to(k.device)
+        kb, vb = k[0, rows, :, 0].cpu(), v[0, rows, :, 0].cpu()
+        if quant == "fp8":
+            ksc, ksh = oracle.split_scale_shift(kss[0, rows, :, 0].cpu())
+            vsc, vsh = oracle.split_scale_shift(vss[0, rows, :, 0].cpu())
+            kr = oracle.dequantize_fp8_asymmetric(oracle.unpack_fp8_words(kb), ksc, ksh)
+            vr = oracle.dequantize_fp8_asymmetric(oracle.unpack_fp8_words(vb), vsc, vsh)
+        elif quant:
+            kr, vr = oracle.dequantize_kv_int4(kb), oracle.dequantize_kv_int4(vb)
+        else:
+            kr, vr = kb.float(), vb.float()
+        G = q.shape[3]
+        qb = q[0, b].float().cpu()[None, None]
+        ro, rl = oracle.ref_attention_with_lse(qb, kr[None, :, :, None].expand(-1, -1, -1, G, -1), vr[None, :, :, None].expand(-1, -1, -1, G, -1))
+        eo = max(eo, float((out[:, b : b + 1].float().cpu() - ro).abs().max()))
+        el = max(el, float((lse[:, :, :, b : b + 1].cpu() - rl).abs().max()))
+    return {"max_abs_o": eo, "max_abs_lse": el, "rows": f"sequences {picks} of {len(lens)}", "ok": bool(eo <= 2e-2 and el <= 1e-3),
+            "tolerance": "O 2e-2, LSE 1e-3"}
 
 
 def gpu_quantize_int4(x):
@@ -364,18 +441,39 @@ def main():
     flops = causal_flops(B, M, H, D)
     launches = 0
     if "prefill" in legs:
+        import oracle
+
         fn = lambda: xops.memory_efficient_attention_forward(q, k, v, causal, op=fmha.b200.FwOp)
         ms, win = event_time_ms(fn, args.steps, args.warmup, barrier)
         windows.append(win)
         ms = max_over_ranks(ms)
-        status = fmha.b200.prefill_device_status()
         per_step = ms / args.steps
         tfs = flops / (per_step * 1e-3) / 1e12
         launches = args.steps
         out_line.update({"value": tfs * world, "ms_per_step": per_step, "gpu_launches": launches})
+        # the same launch over a timed region of at least a second: what the kernel holds once the part is power-capped
+        s_steps = max(args.steps, int(math.ceil(1000.0 / max(per_step, 1e-3))))
+        s_ms, win = event_time_ms(fn, s_steps, 0, barrier)
+        windows.append(win)
+        s_ms = max_over_ranks(s_ms)
+        s_tfs = flops / (s_ms / s_steps * 1e-3) / 1e12
+        status = fmha.b200.prefill_device_status()
+        # parity of this leg's own output: two heads of the first batch element against the oracle
+        po, pl = xops.memory_efficient_attention_forward_requires_grad(q, k, v, causal, op=fmha.b200.FwOp)
+        hs = [0, H - 1]
+        ro, rl = oracle.ref_attention_with_lse(q[:1, :, hs].float().cpu(), k[:1, :, hs].float().cpu(), v[:1, :, hs].float().cpu(), oracle.causal_mask(M, M))
+        out_line["parity"] = parity_block(po[:1, :, hs], pl[:1, hs], ro, rl, f"batch 0, heads {hs}, all {M} rows (rank {rank})")
+        del po, pl
         out_line["roofline"] = {"bound": "tensor", "achieved": tfs, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                "frac": tfs / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill"] * (B / 1), "traffic_unit": "bytes per launch (ncu, B=1 case scaled by B)", "kernel": "prefill_sm100_m256_kernel<128, bf16>",
+                                "frac": tfs / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill"] * (B / 1),
+                                "traffic_unit": "bytes per launch (constant from profiles/: ncu on the B=1 case, scaled by B)",
+                                "kernel": "prefill_sm100_persist_kernel<128, bf16>",
                                 "of": peaks["source"], "frac_of_nominal_2250": tfs / 2250.0, "device_status": status}
+        out_line["sustained"] = {"value": s_tfs * world, "unit": UNIT, "steps": s_steps, "timed_region_s": s_ms * 1e-3, "ms_per_step": s_ms / s_steps,
+                                 "peak": peaks["bf16_tflops_sustained"], "frac": s_tfs / peaks["bf16_tflops_sustained"], "of": peaks["source"],
+                                 "note": "same launch repeated for at least a second; the peak is cuBLAS bf16 held for seconds under the power cap"}
+        launches += s_steps + 1
+        out_line["gpu_launches"] = launches
     # ------------------------------------------------------------------ e2e
     if "e2e" in legs:
         hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
@@ -449,40 +547,43 @@ def main():
     torch.cuda.empty_cache()
 
     # --------------------------------------------------- decode (rank 0 only)
-    for name, quant in (("decode_bf16", False), ("decode_int4", True)):
+    for name, quant in (("decode_bf16", False), ("decode_int4", True), ("decode_fp8", "fp8")):
         if name in legs and rank == 0:
-            dq, dk, dv, dbias, nbytes = decode_workload(dev, quant, B=16 if args.small else 64)
-            fn = lambda: xops.memory_efficient_attention_forward(dq, dk, dv, dbias, op=fmha.b200_splitk.FwOp)
-            d_steps = max(5, min(args.steps, 30))
-            ms, win = event_time_ms(fn, d_steps, 3)
+            wl = decode_workload(dev, quant, B=16 if args.small else 64)
+            dq, dk, dv, dbias, nbytes = wl[:5]
+            kss = vss = None
+            if quant == "fp8":
+                kss, vss = wl[5], wl[6]
+                inp = fmha.triton_splitk.InputsFp8(query=dq, key=dk, value=dv, attn_bias=dbias, k_fp8_scale_shift=kss, v_fp8_scale_shift=vss)
+                fn = lambda: fmha._memory_efficient_attention_forward(inp, op=fmha.b200_splitk.FwOp)
+                fn_lse = lambda: fmha._memory_efficient_attention_forward_requires_grad(inp, op=fmha.b200_splitk.FwOp)
+            else:
+                fn = lambda: xops.memory_efficient_attention_forward(dq, dk, dv, dbias, op=fmha.b200_splitk.FwOp)
+                fn_lse = lambda: xops.memory_efficient_attention_forward_requires_grad(dq, dk, dv, dbias, op=fmha.b200_splitk.FwOp)
+            d_reps = max(20, min(args.steps, 50))
+            med, best, win = graph_time_ms(fn, d_reps)
             windows.append(win)
-            gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
-            split = fmha.b200_splitk.FwOp.get_split_k(16 if args.small else 64, 32768, 8, 68 if quant else 256)
-            out_line[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes, "split_k": split,
+            gbs = nbytes / (med * 1e-3) / 1e9
+            o_, l_ = fn_lse()
+            l_ = l_.lse if hasattr(l_, "lse") else l_
+            par = decode_parity(dq, dk, dv, dbias, o_, l_, quant, kss, vss)
+            par["device_status"] = fmha.b200_splitk.decode_device_status()
+            row_bytes = 132 if quant == "fp8" else 68 if quant else 256
+            split = fmha.b200_splitk.FwOp.get_split_k(16 if args.small else 64, 32768, 8, row_bytes)
+            out_line[name] = {"value": gbs, "unit": "GB/s", "ms_per_step": med, "ms_best": best, "replays": d_reps, "timing": "median of CUDA-graph replays",
+                              "bytes_per_step": nbytes, "split_k": split, "parity": par,
                               "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                           "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name] * nbytes, "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 16-sequence case)",
+                                           "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC[name] * nbytes,
+                                           "traffic_unit": "bytes per launch (constant from profiles/: ncu ratio to algorithmic bytes on the 16-sequence case)",
                                            "of": peaks["source"]},
-                              "workload": "64 seqs, kv len U[1024,32768], paged 256, Hq=64 Hkv=8 D=128, 1 query each; cache far larger than L2"}
-            del dq, dk, dv, dbias
+                              "workload": "64 seqs, kv len U[1024,32768], paged 256, Hq=64 Hkv=8 D=128, 1 query each; cache far larger than L2"
+                                          + ("; row-wise fp8 cache (128 B + one scale/shift word per token and head)" if quant == "fp8" else "; int4 row-wise cache (68 B per token and head)" if quant else "")}
+            launches += 2 * (d_reps + 7)
+            del dq, dk, dv, dbias, wl, kss, vss, o_, l_
+            if quant == "fp8":
+                del inp
             torch.cuda.empty_cache()
         barrier()
-
-    if "decode_fp8" in legs and rank == 0:
-        dq, dk, dv, dbias, nbytes, kss, vss = decode_workload(dev, "fp8", B=16 if args.small else 64)
-        inp = fmha.triton_splitk.InputsFp8(query=dq, key=dk, value=dv, attn_bias=dbias, k_fp8_scale_shift=kss, v_fp8_scale_shift=vss)
-        fn = lambda: fmha._memory_efficient_attention_forward(inp, op=fmha.b200_splitk.FwOp)
-        d_steps = max(5, min(args.steps, 30))
-        ms, win = event_time_ms(fn, d_steps, 3)
-        windows.append(win)
-        gbs = nbytes / (ms / d_steps * 1e-3) / 1e9
-        out_line["decode_fp8"] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / d_steps, "bytes_per_step": nbytes,
-                                  "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                               "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode_fp8"] * nbytes,
-                                               "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 16-sequence case)", "of": peaks["source"]},
-                                  "workload": "as decode_bf16 with a row-wise fp8 cache (128 B + one scale/shift word per token and head)"}
-        del dq, dk, dv, dbias, kss, vss, inp
-        torch.cuda.empty_cache()
-    barrier()
 
     # ------------------------------ rope_padded: prefill into a padded cache (rank 0)
     if "rope" in legs and rank == 0:
@@ -500,14 +601,15 @@ def main():
             with torch.no_grad():
                 xops.rope_padded(rq, rk, rv, rck, rcv, rbias, out_q=rout)
 
-        r_steps = max(5, min(args.steps, 30))
-        ms, win = event_time_ms(rope_step, r_steps, 3)
+        r_reps = max(20, min(args.steps, 50))
+        med, best, win = graph_time_ms(rope_step, r_reps)
         windows.append(win)
         rbytes = 2 * rq.numel() * 2 + 2 * (rk.numel() + rv.numel()) * 2  # every row read once and written once
-        gbs = rbytes / (ms / r_steps * 1e-3) / 1e9
-        out_line["rope_padded"] = {"value": gbs, "unit": "GB/s", "ms_per_step": ms / r_steps, "bytes_per_step": rbytes,
+        gbs = rbytes / (med * 1e-3) / 1e9
+        launches += r_reps + 6
+        out_line["rope_padded"] = {"value": gbs, "unit": "GB/s", "ms_per_step": med, "ms_best": best, "replays": r_reps, "timing": "median of CUDA-graph replays", "bytes_per_step": rbytes,
                                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                                                "traffic": NCU_TRAFFIC["rope"] * rbytes, "traffic_unit": "bytes per launch (ncu ratio to algorithmic bytes on the 2-sequence case)", "of": peaks["source"]},
+                                                "traffic": NCU_TRAFFIC["rope"] * rbytes, "traffic_unit": "bytes per launch (constant from profiles/: ncu ratio to algorithmic bytes on the 2-sequence case)", "of": peaks["source"]},
                                    "workload": f"{r_seqs} seqs x {r_len} new tokens into slots of {r_pad} rows, Hq={r_hq} Hkv={r_hkv} D=128 bf16, adjacent pairs; {rbytes >> 20} MiB per step, larger than L2"}
         del rq, rk, rv, rck, rcv, rout
         torch.cuda.empty_cache()

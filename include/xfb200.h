@@ -133,6 +133,12 @@ typedef struct {
    * for it runs out, the kernel records a status code and returns (see xfb200_prefill_device_status). */
   int32_t wait_budget_kcycles;
   int32_t debug_flags;
+  /* Two key ranges in one call (a rank of a sharded long sequence that holds two ranges of the
+   * keys, stored back to back): rows [0, kv_split) of k/v start at global key kv_offset, rows
+   * [kv_split, mkv) at global key kv_offset2 >= kv_offset + kv_split.  kv_split a multiple of
+   * 128; 0 = one range.  Dense inputs, XFB200_MASK_CAUSAL_TOP_LEFT, no window; tcgen05 path. */
+  int32_t kv_split;
+  int32_t kv_offset2;
 } xfb200_prefill_params;
 
 XFB200_API int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream);

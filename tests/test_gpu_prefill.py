@@ -478,3 +478,56 @@ def test_memory_efficient_attention_is_the_forward_without_grad():
         xops.memory_efficient_attention(qg, k, v, bias)
     with torch.no_grad():
         assert torch.equal(xops.memory_efficient_attention(qg, k, v, bias), out)
+
+
+@gpu
+@pytest.mark.parametrize("op", KERNELS)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("growth,jump_at", [(2.5, 512), (4.0, 600), (40.0, 600), (40.0, 130), (0.05, 384), (12.0, 1000)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_scores_that_jump_along_the_keys(op, dtype, growth, jump_at, causal):
+    """Keys from position ``jump_at`` on are ``growth`` times larger: the row maxima move by a few
+    powers of two (re-based one step late), by more than 2^14 (the one-pass softmax has to stop in
+    the middle of a tile and rescale what it already stored) or not at all (shrinking scores)."""
+    require_cuda()
+    B, M, H, D = 2, 1152, 2, 128
+    q, k, v = rand_qkv(B, M, M, 1, H, D, dtype, seed=int(growth * 10) + jump_at, gqa=False)
+    q, k, v = q[:, :, 0], k[:, :, 0].clone(), v[:, :, 0]
+    k[:, jump_at:] *= growth
+    bias = ab.LowerTriangularMask() if causal else None
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = ref(q, k, v, bias)
+    assert_o_lse(out, lse, ro, rl, dtype, f"{op.NAME} growth {growth} at {jump_at}")
+    _status_ok()
+
+
+@gpu
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("q0,Mq,L0,o0,L1,o1", [(0, 1000, 256, 0, 300, 700), (0, 1000, 128, 128, 77, 900), (512, 300, 384, 0, 200, 640),
+                                              (0, 515, 256, 600, 128, 2000), (100, 400, 128, 0, 256, 128)])
+def test_two_key_ranges_in_one_launch(D, q0, Mq, L0, o0, L1, o1):
+    """``kv_split``: a rank of a sharded causal sequence holds the key ranges [o0, o0 + L0) and [o1, o1 + L1) back to
+    back; query rows are the global rows q0 .. q0 + Mq.  One launch equals the oracle on the visible keys."""
+    require_cuda()
+    dtype = torch.bfloat16
+    S = max(o1 + L1, q0 + Mq)
+    q, k, v = rand_qkv(1, S, S, 2, 2, D, dtype, seed=L0 + L1 + o1, gqa=True)
+    qs = q[:, q0 : q0 + Mq]
+    kc = torch.cat([k[:, o0 : o0 + L0, :, :1], k[:, o1 : o1 + L1, :, :1]], dim=1).expand(-1, -1, -1, 2, -1)
+    vc = torch.cat([v[:, o0 : o0 + L0, :, :1], v[:, o1 : o1 + L1, :, :1]], dim=1).expand(-1, -1, -1, 2, -1)
+    inp = fmha.Inputs(qs, kc, vc, ab.LowerTriangularMask(), output_dtype=torch.float32, is_partial=True)
+    out, ctx = P.FwOp._apply(inp, want_lse=True, kv_offset=o0 - q0, kv_split=L0, kv_offset2=o1 - q0)
+    # oracle: the same keys with the mask built from global positions
+    key_pos = torch.cat([torch.arange(o0, o0 + L0), torch.arange(o1, o1 + L1)])
+    vis = key_pos.view(1, -1) <= (q0 + torch.arange(Mq)).view(-1, 1)
+    mask = torch.zeros(Mq, L0 + L1).masked_fill_(~vis, float("-inf"))
+    ro, rl = oracle.ref_attention_with_lse(qs.float().cpu(), kc.float().cpu(), vc.float().cpu(), mask.expand(1, 2, 2, Mq, L0 + L1))
+    assert_o_lse(out, ctx.lse, ro, rl, dtype, "two key ranges")
+    dead = ~vis.any(-1)
+    if dead.any():
+        assert (out[:, dead] == 0).all() and torch.isneginf(ctx.lse[..., dead]).all()
+    _status_ok()
+    with pytest.raises(ValueError):
+        P.FwOp._apply(inp, want_lse=True, kv_offset=0, kv_split=100, kv_offset2=o1)  # not a multiple of 128
+    with pytest.raises(NotImplementedError):
+        P.FwOp_Tcgen05_M256._apply(inp, want_lse=True, kv_offset=o0 - q0, kv_split=L0, kv_offset2=o1 - q0)

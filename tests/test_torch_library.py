@@ -67,3 +67,32 @@ def test_matches_python_entry_point_and_compiles():
 
     compiled = torch.compile(f, fullgraph=True, backend="aot_eager")
     torch.testing.assert_close(compiled(q, k, v), want.float() * 2)
+
+
+def test_merge_varargs_custom_op_is_registered_with_a_fake():
+    s = str(torch.ops.xformers_b200.fmha_merge_attentions_varargs.default._schema)
+    assert "Tensor[] attn_split, Tensor[] lse_split, bool write_lse=True, ScalarType? output_dtype=None" in s
+    a = [torch.empty(2, 5, 3, 4, 64, device="meta") for _ in range(3)]
+    l = [torch.empty(2, 3, 4, 5, device="meta") for _ in range(3)]
+    out, lse = torch.ops.xformers_b200.fmha_merge_attentions_varargs(a, l, True, torch.bfloat16)
+    assert out.shape == (2, 5, 3, 4, 64) and out.dtype == torch.bfloat16 and lse.shape == (2, 3, 4, 5)
+
+
+@pytest.mark.gpu
+def test_merge_varargs_compiles_without_graph_break():
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = [torch.randn(2, 5, 3, 4, 64, generator=g, device=dev) for _ in range(3)]
+    l = [torch.randn(2, 3, 4, 5, generator=g, device=dev) for _ in range(3)]
+    want_o, want_l = fmha.merge_attentions(a, l)
+
+    def f(a0, a1, a2, l0, l1, l2):
+        o, lse = fmha.merge_attentions_varargs([a0, a1, a2], [l0, l1, l2])
+        return o * 2, lse
+
+    compiled = torch.compile(f, fullgraph=True, backend="aot_eager")
+    o, lse = compiled(*a, *l)
+    torch.testing.assert_close(o, want_o * 2)
+    torch.testing.assert_close(lse, want_l)
+    o2, none = fmha.merge_attentions_varargs(a, l, write_lse=False)
+    assert none is None and torch.equal(o2, want_o)

@@ -85,6 +85,8 @@ class PrefillParams(C.Structure):
         ("bias_stride_m", C.c_int64),
         ("wait_budget_kcycles", C.c_int32),
         ("debug_flags", C.c_int32),
+        ("kv_split", C.c_int32),
+        ("kv_offset2", C.c_int32),
     ]
 
 

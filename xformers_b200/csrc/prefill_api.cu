@@ -37,6 +37,15 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
   if (((p->o_strides.b | p->o_strides.m | p->o_strides.g | p->o_strides.h) * osz) % 8 || (reinterpret_cast<uintptr_t>(p->out) & 7))
     return set_error(XFB200_E_INVALID, "prefill: out rows must be 8-byte aligned");
 
+  if (p->kv_split != 0) {
+    if (p->kv_split < 0 || p->kv_split >= p->mkv || p->kv_split % 128 != 0)
+      return set_error(XFB200_E_INVALID, "prefill: kv_split %d must be a multiple of 128 inside (0, mkv)", p->kv_split);
+    if (p->mask_type != XFB200_MASK_CAUSAL_TOP_LEFT || p->window_left >= 0 || p->seqstart_q != nullptr || p->bias != nullptr)
+      return set_error(XFB200_E_UNSUPPORTED, "prefill: two key ranges need dense inputs and the plain top-left causal mask");
+    if (int64_t(p->kv_offset2) < int64_t(p->kv_offset) + p->kv_split)
+      return set_error(XFB200_E_INVALID, "prefill: the second key range must lie behind the first (kv_offset2 >= kv_offset + kv_split)");
+  }
+
   if (p->bias != nullptr) {
     if (p->seqstart_q != nullptr) return set_error(XFB200_E_UNSUPPORTED, "prefill: an additive bias with concatenated sequences");
     if (p->bias_dtype != XFB200_BF16 && p->bias_dtype != XFB200_F16 && p->bias_dtype != XFB200_F32)
@@ -48,5 +57,6 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
   const bool can100 = p->kernel_path != XFB200_PREFILL_MMA_SYNC && p->mkv > 0 && p->bias == nullptr && prefill_sm100_supported(p);
   if (p->kernel_path >= XFB200_PREFILL_TCGEN05 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
   if (can100) return prefill_sm100_launch(p, st);
+  if (p->kv_split != 0) return set_error(XFB200_E_UNSUPPORTED, "prefill: two key ranges in one call need the tcgen05 kernel (head dim 64 or 128)");
   return prefill_generic_launch(p, st);
 }

@@ -23,6 +23,9 @@ struct Sm100Args {
   // query i of a block sees key j iff i + shift - window_left <= j <= i + shift + window_right, each bound only
   // when it is >= 0; shift = (bottom_right ? keys - queries of the block : 0) - kv_offset
   int32_t bottom_right, kv_offset, window_left, window_right;
+  // two key ranges in one tensor (persistent kernel, dense causal only): rows [0, kv_split) of k/v start at global key
+  // kv_offset, rows from kv_split on at kv_offset2; 0 = one range
+  int32_t kv_split, kv_offset2;
   int32_t out_dtype;
   float scale_log2;
   int32_t q_tiles;  // blocks of 256 query rows per sequence (static bound)

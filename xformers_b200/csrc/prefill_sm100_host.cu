@@ -93,12 +93,16 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   a.bottom_right = p->mask_type >= XFB200_MASK_CAUSAL_BOTTOM_RIGHT ? 1 : 0;
   a.kv_offset = p->kv_offset, a.window_left = p->window_left, a.out_dtype = p->out_dtype;
   a.window_right = p->mask_type == XFB200_MASK_NONE ? -1 : p->mask_type == XFB200_MASK_LOCAL_BOTTOM_RIGHT ? p->window_right : 0;
+  a.kv_split = p->kv_split, a.kv_offset2 = p->kv_offset2;
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.q_tiles = (p->mq + 255) / 256;
   a.debug_flags = p->debug_flags;
   a.wait_budget = p->wait_budget_kcycles > 0 ? 1000LL * p->wait_budget_kcycles : kDefaultWaitBudgetCycles;
   const bool bf16 = p->dtype == XFB200_BF16;
-  if (p->kernel_path == XFB200_PREFILL_TCGEN05_CTA) return prefill_sm100_m256_launch(a, D, bf16, stream);
+  if (p->kernel_path == XFB200_PREFILL_TCGEN05_CTA) {
+    if (p->kv_split > 0) return set_error(XFB200_E_UNSUPPORTED, "prefill: two key ranges in one call need the persistent kernel");
+    return prefill_sm100_m256_launch(a, D, bf16, stream);
+  }
   return prefill_sm100_persist_launch(a, D, bf16, stream);
 }
 

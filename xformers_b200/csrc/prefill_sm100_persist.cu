@@ -15,10 +15,13 @@
 //                the tensor pipe does not wait for the write-back.
 //   warp 12/13   MMA issuer of tile 0 / 1 (one lane issues); the two pass a
 //                token so that their blocks of MMAs alternate on the tensor pipe
-//   warp 14      scheduler + TMA producer: pulls the next item, announces it to
-//                the other warps through a small ring in shared memory, loads
-//                Q (per tile) and the K/V tiles into 2-deep rings that run on
-//                across item boundaries
+//   warp 14      scheduler + TMA producer: pulls the next item one item ahead of
+//                time, works out its geometry once and announces it to the other
+//                warps through a small ring of descriptors in shared memory,
+//                loads Q (per tile) and the K/V tiles into 2-deep rings that run
+//                on across item boundaries.  Items in which no query sees any
+//                key (possible when the key axis is sharded) never enter the
+//                ring: this warp writes their zeros and -inf itself.
 //   warp 15      idle
 //
 // Tensor memory (all 512 columns): S0 | S1 | O0 | O1, fp32.  The probabilities
@@ -29,12 +32,23 @@
 // further hand-shakes; across items the first PV of a tile waits until the
 // output warps have read the previous O_t out of tensor memory.
 //
-// Softmax: in steady state a step is one pass -- 32 score columns at a time come
-// out of tensor memory while the previous 32 are turned into probabilities
-// against the running maximum of the row, and the row maximum of the step is
-// only compared with it afterwards.  The first step of an item, steps that
-// need masking and steps where some row's maximum grew by more than 2^8 take two
-// passes (maximum first), the last case after discarding the one-pass result.
+// Softmax: thread = row; a step is one pass over its 128 scores, 32 columns (a
+// chunk) at a time: out of tensor memory, masked (diagonal and ragged tiles
+// only), turned into probabilities against the row's reference maximum and
+// stored back as P at once.  The reference maximum is the running one of the
+// previous steps (the first chunk gives it for a fresh row); when a step's
+// maximum exceeds it by more than 2^8 the row is re-based at the start of the
+// next step, when O_t may be touched again.  Only a score more than 2^14 above
+// the reference -- its probability would leave the 16-bit range -- stops the
+// pass: the rest of the row is then scanned for its true maximum and what was
+// already stored is rescaled (rare, and exact either way).  The chunk body
+// exists once and runs four times per step.  Measured alternatives (all within
+// a few percent, none better on the causal 4k case): the whole row in registers
+// as in the one-CTA-per-block kernel; two passes over tensor memory (maximum,
+// then probabilities); the next chunk's load in flight behind the current one;
+// part of the exponentials as a cubic on the FMA pipe (slower at every
+// fraction).  The exponential unit, shared by the two tiles' warps of a
+// scheduler, and in-order issue of a warp that runs almost alone set the pace.
 //
 // Masks are index arithmetic on (row, key) positions; K/V heads of a GQA group
 // are indexed, never expanded; V rows past a sequence's end are zeroed in
@@ -60,21 +74,34 @@ constexpr int kStages = 2;  // depth of the K and of the V ring
 constexpr int kSched = 4;   // depth of the ring that announces work items
 constexpr int kThreads = 512;
 constexpr int kOutWarp0 = 8, kMmaWarp0 = 12, kTmaWarp = 14;
-constexpr int kItemReaders = 14;  // warps that read every announced item (all but the producer and the idle one)
+constexpr int kItemReaders = 14;  // warps that read every announced item (all but the scheduler and the idle one)
 // registers per thread after setmaxnreg; the sum over the 16 warps must fit what the CTA was launched with
 #ifndef XFB_PST_REGS_SOFTMAX
-#define XFB_PST_REGS_SOFTMAX 192
+#define XFB_PST_REGS_SOFTMAX 176
 #endif
 #ifndef XFB_PST_REGS_OUT
-#define XFB_PST_REGS_OUT 64
+#define XFB_PST_REGS_OUT 80
 #endif
 #ifndef XFB_PST_REGS_AUX
-#define XFB_PST_REGS_AUX 64
+#define XFB_PST_REGS_AUX 80
 #endif
 constexpr int kRegsLaunch = 128, kRegsSoftmax = XFB_PST_REGS_SOFTMAX, kRegsOut = XFB_PST_REGS_OUT, kRegsAux = XFB_PST_REGS_AUX;
 static_assert(8 * kRegsSoftmax + 4 * kRegsOut + 4 * kRegsAux <= 16 * kRegsLaunch, "setmaxnreg would ask for more registers than the CTA owns");
-constexpr float kRescaleThreshold = 8.0f;
+constexpr float kRescaleThreshold = 8.0f;  // a row is re-based when its maximum grew by more than 2^8
+constexpr float kOverflowLimit = 14.0f;    // probabilities up to 2^14 against a stale maximum are fine in f16 and bf16
 constexpr uint32_t kHalfBytes = 128 * 128;  // one 64-column block of a 128-row tile
+
+// Geometry of a work item, worked out once by the scheduler warp and read by the others from shared memory.
+struct Item {
+  int idx;  // item number, -1 = no more work
+  int b, head, kv_head, tb;
+  int g, h;
+  int q_row0, k_row0, qlen, klen;
+  int m0, shift, n_base;
+  int shift2;  // two key ranges in one tensor: what `shift` is for the keys from row kv_split on
+  int jlo[kTiles], jhi[kTiles];  // key-step range of each query tile, in steps of kBN keys from n_base
+  int j_begin, j_end;            // steps any tile takes part in
+};
 
 struct __align__(8) Barriers {
   uint64_t sched_full[kSched], sched_empty[kSched];
@@ -84,7 +111,7 @@ struct __align__(8) Barriers {
   uint64_t o_full[kTiles], o_empty[kTiles];
   uint64_t stats_full[kTiles], stats_empty[kTiles];
   uint64_t turn[kTiles];  // token of the tensor pipe: the two MMA warps issue their blocks alternately
-  int32_t sched_item[kSched];
+  Item sched_item[kSched];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -98,9 +125,9 @@ struct Smem {
   static constexpr int kV = kK + kStages * kKV;
   static constexpr int kStats = kV + kStages * kKV;          // float2 [kTiles][kBM]: running maximum (log2 units), row sum
   static constexpr int kBar = kStats + kTiles * kBM * 8;
-  static constexpr int kTotal = kBar + 512 + 1024;
+  static constexpr int kTotal = kBar + 1024 + 1024;
 };
-static_assert(sizeof(Barriers) <= 512, "barrier block");
+static_assert(sizeof(Barriers) <= 1024, "barrier block");
 
 // Packed fp32 pairs live in 64-bit registers; building and splitting them with
 // mov.b64 keeps everything in registers (no address-taken locals).
@@ -133,6 +160,16 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 template <bool kBf16>
+__device__ __forceinline__ void unpack_pair(uint32_t x, float& lo, float& hi) {
+  if constexpr (kBf16) {
+    lo = __uint_as_float(x << 16);
+    hi = __uint_as_float(x & 0xffff0000u);
+  } else {
+    const float2 f = __half22float2(*reinterpret_cast<__half2*>(&x));
+    lo = f.x, hi = f.y;
+  }
+}
+template <bool kBf16>
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
   if constexpr (kBf16) {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -143,6 +180,21 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
   }
 }
 
+#ifdef XFB_PST_PROFILE
+// Timing build only: per-CTA cycle counters of the MMA issuers (slots 0-15 / 16-31) and of one softmax warp per
+// tile (32-47 / 48-63), read back with xfb200_debug_read_prefill_profile.
+__device__ long long g_prof[160][64];
+#define XFB_PROF_DECL(n) long long prof_acc[n] = {0}; long long prof_t = clock64();
+#define XFB_PROF_LAP(k) { const long long _n = clock64(); prof_acc[k] += _n - prof_t; prof_t = _n; }
+#define XFB_PROF_COUNT(k) { prof_acc[k] += 1; }
+#define XFB_PROF_STORE(base, n) { if (lane == 0 && blockIdx.x < 160) for (int _i = 0; _i < (n); ++_i) g_prof[blockIdx.x][(base) + _i] += prof_acc[_i]; }
+#else
+#define XFB_PROF_DECL(n)
+#define XFB_PROF_LAP(k)
+#define XFB_PROF_COUNT(k)
+#define XFB_PROF_STORE(base, n)
+#endif
+
 // Records the first code a launch gives up with (kept until the host reads it) and marks the
 // launch, so that CTAs that have not started yet leave at once.
 __device__ __forceinline__ void give_up(const Sm100Args& a, int code) {
@@ -150,18 +202,9 @@ __device__ __forceinline__ void give_up(const Sm100Args& a, int code) {
   reinterpret_cast<volatile int32_t*>(a.status)[1] = int32_t(a.epoch);
 }
 
-// Geometry of a work item; every warp derives it from the item's number.
-struct Item {
-  int b, head, kv_head, tb;
-  int g, h;
-  int q_row0, k_row0, qlen, klen;
-  int m0, shift, n_base;
-  int jlo[kTiles], jhi[kTiles];  // key-step range of each query tile, in steps of kBN keys from n_base
-  int j_begin, j_end;            // steps any tile takes part in
-};
-
 // Returns false when the item has no query row at all (a row block past the end of its sequence).
 __device__ __forceinline__ bool decode_item(const Sm100Args& a, int idx, Item& it) {
+  it.idx = idx;
   const int n_heads = a.groups * a.heads_per_group;
   const int n_bh = n_heads * a.batch;
   const int qt = a.q_tiles - 1 - idx / n_bh;  // heaviest (latest) row blocks first
@@ -181,6 +224,7 @@ __device__ __forceinline__ bool decode_item(const Sm100Args& a, int idx, Item& i
   it.m0 = qt * kBM * kTiles;
   if (it.m0 >= it.qlen) return false;
   it.shift = (a.bottom_right ? it.klen - it.qlen : 0) - a.kv_offset;
+  it.shift2 = -a.kv_offset2;
   it.n_base = 0;
   if (a.window_left >= 0) it.n_base = max(0, it.m0 + it.shift - a.window_left) / kBN * kBN;
   it.j_begin = 0x7fffffff, it.j_end = 0;
@@ -189,6 +233,12 @@ __device__ __forceinline__ bool decode_item(const Sm100Args& a, int idx, Item& i
     const int mt0 = it.m0 + t * kBM;
     int hi = it.klen, lo = it.n_base;
     if (a.window_right >= 0) hi = min(hi, mt0 + kBM + it.shift + a.window_right);
+    if (a.kv_split > 0) {
+      // Two key ranges back to back (causal, the second one later in the sequence): rows that see any key of the
+      // second range see all of the first, so the visible keys are still one run of rows of the tensor.
+      const int hi1 = min(it.klen - a.kv_split, mt0 + kBM + it.shift2);
+      hi = hi1 > 0 ? a.kv_split + hi1 : min(a.kv_split, mt0 + kBM + it.shift);
+    }
     if (a.window_left >= 0) lo = max(it.n_base, max(0, mt0 + it.shift - a.window_left) / kBN * kBN);
     if (mt0 >= it.qlen) hi = lo;  // no valid row in this tile
     it.jlo[t] = (lo - it.n_base) / kBN;
@@ -254,11 +304,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
     const uint32_t tmem = bar->tmem_base;
     volatile uint32_t* abort_flag = &bar->abort_flag;
 
-    // Next announced item: its number, -1 after the last one, -2 when the wait ran out.
-    auto pop_item = [&](int& seq) -> int {
+    // Next announced item (every announced item has key steps): its number, -1 after the last one, -2 when the
+    // wait ran out.  `take` copies what the caller needs out of the descriptor before the slot is handed back.
+    auto pop_item = [&](int& seq, auto&& take) -> int {
       const int slot = seq % kSched;
       if (!mbar_wait(&bar->sched_full[slot], (seq / kSched) & 1, abort_flag, budget)) return -2;
-      const int idx = *reinterpret_cast<volatile int32_t*>(&bar->sched_item[slot]);
+      const Item* d = &bar->sched_item[slot];
+      const int idx = d->idx;
+      if (idx >= 0) take(*d);
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar->sched_empty[slot]);
       ++seq;
@@ -269,79 +322,122 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsAux));
       if (warp == kTmaWarp) {
         // ============================================ scheduler + TMA producer
+        // Lane 0 waits and issues; all lanes run the loop, because pulling an item (a broadcast)
+        // and writing the rows of an item without visible keys are done by the whole warp.
         if (lane == 0) {
           prefetch_tensormap(&a.tm_q);
           prefetch_tensormap(&a.tm_k);
           prefetch_tensormap(&a.tm_v);
-          int seq = 0;           // items announced
-          int kstep = 0;         // K/V steps loaded, over all items
-          int aq[kTiles] = {0, 0};  // items in which tile t took part so far
-          bool ok = true;
-          while (ok) {
-            Item it;
-            int idx;
-            for (;;) {
-              idx = atomicAdd(a.counters, 1);
-              if (idx >= n_items) {
-                idx = -1;
-                break;
-              }
-              if (decode_item(a, idx, it)) break;
+        }
+        int seq = 0;              // items announced
+        int kstep = 0;            // K/V steps loaded, over all items
+        int aq[kTiles] = {0, 0};  // items in which tile t took part so far
+        bool ok = true;
+        // Pulls item numbers until one has key steps.  Row blocks past the end of their sequence are
+        // skipped; blocks whose rows see no key at all get their result here: zeros and -inf.
+        auto next_item = [&](Item& it) {
+          for (;;) {
+            int idx = 0;
+            if (lane == 0) idx = atomicAdd(a.counters, 1);
+            idx = __shfl_sync(0xffffffffu, idx, 0);
+            if (idx >= n_items) {
+              it.idx = -1;
+              return;
             }
-            const int slot = seq % kSched;
+            if (!decode_item(a, idx, it)) continue;
+            if (it.j_end > it.j_begin) return;
+            const int nrows = min(kBM * kTiles, it.qlen - it.m0);
+            const int osz = a.out_dtype == XFB200_F32 ? 4 : 2;
+            const int chunks = D * osz / 16;
+            uint8_t* ob = reinterpret_cast<uint8_t*>(a.out);
+            const int64_t base = int64_t(it.tb) * a.os.b + int64_t(it.q_row0 + it.m0) * a.os.m + int64_t(it.g) * a.os.g + int64_t(it.h) * a.os.h;
+            for (int i = lane; i < nrows * chunks; i += 32) {
+              const int r = i / chunks, c = i % chunks;
+              *reinterpret_cast<uint4*>(ob + (base + int64_t(r) * a.os.m) * osz + c * 16) = make_uint4(0, 0, 0, 0);
+            }
+            if (a.lse != nullptr) {
+              const int64_t lo = a.seqstart_q != nullptr ? int64_t(it.g) * a.lse_g + int64_t(it.h) * a.lse_h + it.q_row0 + it.m0
+                                                         : int64_t(it.b) * a.lse_b + int64_t(it.g) * a.lse_g + int64_t(it.h) * a.lse_h + it.m0;
+              for (int r = lane; r < nrows; r += 32) a.lse[lo + r] = -INFINITY;
+            }
+          }
+        };
+        Item cur, nxt;
+        next_item(cur);
+        while (ok) {
+          const int slot = seq % kSched;
+          if (lane == 0) {
             if (seq >= kSched && !mbar_wait(&bar->sched_empty[slot], (seq / kSched - 1) & 1, abort_flag, budget)) {
               give_up(a, 10);
               ok = false;
-              break;
+            } else {
+              bar->sched_item[slot] = cur;
+              mbar_arrive(&bar->sched_full[slot]);  // (release: the descriptor is visible to whoever sees the phase)
             }
-            *reinterpret_cast<volatile int32_t*>(&bar->sched_item[slot]) = idx;
-            mbar_arrive(&bar->sched_full[slot]);  // (release: the item number is visible to whoever sees the phase)
-            ++seq;
-            if (idx < 0) break;
-            if (it.j_end <= it.j_begin) continue;  // nothing visible: only the output warps handle it
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) {
-              if (it.jhi[t] <= it.jlo[t]) continue;
-              if (aq[t] > 0 && !mbar_wait(&bar->q_empty[t], (aq[t] - 1) & 1, abort_flag, budget)) {
-                give_up(a, 13);
-                ok = false;
-                break;
-              }
-              ++aq[t];
-              mbar_expect_tx(&bar->q_full[t], L::kQTile);
-#pragma unroll
-              for (int hf = 0; hf < kHalves; ++hf)
-                tma_load_4d(smem + L::kQ + t * L::kQTile + hf * kHalfBytes, &a.tm_q, &bar->q_full[t], hf * 64, it.head,
-                            it.q_row0 + it.m0 + t * kBM, it.tb);
+          }
+          ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+          ++seq;
+          if (!ok || cur.idx < 0) break;
+          // Loads are issued in the order in which what they wait for comes free at the end of the previous
+          // item: the K tile of the first step (its stage is released one step before the end), Q of tile 0,
+          // the V tile of the first step, Q of tile 1, then the remaining steps.  A Q load that waited for
+          // the very last QK of the previous item must not hold back the first K tile.
+          auto load_q = [&](int t) {
+            if (!ok || (t == 0 ? cur.jhi[0] <= cur.jlo[0] : cur.jhi[1] <= cur.jlo[1])) return;
+            if (aq[t] > 0 && !mbar_wait(&bar->q_empty[t], (aq[t] - 1) & 1, abort_flag, budget)) {
+              give_up(a, 13);
+              ok = false;
+              return;
             }
-            for (int j = it.j_begin; ok && j < it.j_end; ++j, ++kstep) {
+            ++aq[t];
+            mbar_expect_tx(&bar->q_full[t], L::kQTile);
+#pragma unroll
+            for (int hf = 0; hf < kHalves; ++hf)
+              tma_load_4d(smem + L::kQ + t * L::kQTile + hf * kHalfBytes, &a.tm_q, &bar->q_full[t], hf * 64, cur.head,
+                          cur.q_row0 + cur.m0 + t * kBM, cur.tb);
+          };
+          bool have_next = false;
+          for (int j = cur.j_begin; j < cur.j_end; ++j, ++kstep) {
+            if (lane == 0 && ok) {
               const int st = kstep % kStages, use = kstep / kStages;
-              const int row = it.k_row0 + it.n_base + j * kBN;
+              const int row = cur.k_row0 + cur.n_base + j * kBN;
               if (use > 0 && !mbar_wait(&bar->k_empty[st], (use - 1) & 1, abort_flag, budget)) {
                 give_up(a, 11);
                 ok = false;
-                break;
               }
               // (testing aid: the CTA that got the first item leaves out its last key tile, so that the wait for it runs out)
-              if (!((a.debug_flags & 1) && idx == 0 && j == it.j_end - 1)) {
+              if (ok && !((a.debug_flags & 1) && cur.idx == 0 && j == cur.j_end - 1)) {
                 mbar_expect_tx(&bar->k_full[st], L::kKV);
 #pragma unroll
                 for (int hf = 0; hf < kHalves; ++hf)
-                  tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, it.kv_head, row, it.tb);
+                  tma_load_4d(smem + L::kK + st * L::kKV + hf * kHalfBytes, &a.tm_k, &bar->k_full[st], hf * 64, cur.kv_head, row, cur.tb);
               }
-              if (use > 0 && !mbar_wait(&bar->v_empty[st], (use - 1) & 1, abort_flag, budget)) {
+              if (j == cur.j_begin) load_q(0);
+              if (ok && use > 0 && !mbar_wait(&bar->v_empty[st], (use - 1) & 1, abort_flag, budget)) {
                 give_up(a, 12);
                 ok = false;
-                break;
               }
-              mbar_expect_tx(&bar->v_full[st], L::kKV);
+              if (ok) {
+                mbar_expect_tx(&bar->v_full[st], L::kKV);
 #pragma unroll
-              for (int hf = 0; hf < kHalves; ++hf)
-                tma_load_4d(smem + L::kV + st * L::kKV + hf * kHalfBytes, &a.tm_v, &bar->v_full[st], hf * 64, it.kv_head, row, it.tb);
+                for (int hf = 0; hf < kHalves; ++hf)
+                  tma_load_4d(smem + L::kV + st * L::kKV + hf * kHalfBytes, &a.tm_v, &bar->v_full[st], hf * 64, cur.kv_head, row, cur.tb);
+              }
+              if (j == cur.j_begin) load_q(1);
+            }
+            ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+            if (!ok) break;
+            // The first two steps fit the rings at once; from here on every load waits for a stage to
+            // come free, so this is the moment to pull the next item: its latency costs nothing.
+            if (!have_next && (j == cur.j_begin + 1 || j == cur.j_end - 1)) {
+              next_item(nxt);
+              have_next = true;
             }
           }
-          if (!ok) *abort_flag = 1;
+          if (!ok) break;
+          cur = nxt;
         }
+        if (!ok) *abort_flag = 1;
       } else if (warp == kMmaWarp0 || warp == kMmaWarp0 + 1) {
         // ================================================= MMA issuer of tile t
         // tcgen05.mma is issued almost synchronously (the queue in front of the
@@ -349,6 +445,17 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         // spends on anything else -- a satisfied mbarrier wait alone costs ~90 --
         // is a clock the tensor pipe idles.  Hence one issuing warp per query tile:
         // while one waits for its softmax, the other keeps the pipe fed.
+#if !defined(XFB_PST_PROFILE_MMA)
+#define XFB_MPROF_DECL(n)
+#define XFB_MPROF_LAP(k)
+#define XFB_MPROF_COUNT(k)
+#define XFB_MPROF_STORE(b, n)
+#else
+#define XFB_MPROF_DECL(n) XFB_PROF_DECL(n)
+#define XFB_MPROF_LAP(k) XFB_PROF_LAP(k)
+#define XFB_MPROF_COUNT(k) XFB_PROF_COUNT(k)
+#define XFB_MPROF_STORE(b, n) XFB_PROF_STORE(b, n)
+#endif
         const int t = warp - kMmaWarp0;
         constexpr uint32_t idesc_qk = umma_idesc(kBM, kBN, kBf16, false, false);
         constexpr uint32_t idesc_pv = umma_idesc(kBM, D, kBf16, false, true);
@@ -391,20 +498,12 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           int j_begin, j_end, jlo, jhi, n_base, klen;
         };
         Steps cur, nxt;
-        // next item that has key steps (the others concern the output warps only)
         auto pop_with_steps = [&](Steps& st) -> int {
-          for (;;) {
-            const int i = pop_item(seq);
-            if (i < 0) return i;
-            Item it;
-            decode_item(a, i, it);
-            if (it.j_end > it.j_begin) {
-              st.j_begin = it.j_begin, st.j_end = it.j_end, st.n_base = it.n_base, st.klen = it.klen;
-              st.jlo = t == 0 ? it.jlo[0] : it.jlo[1];
-              st.jhi = t == 0 ? it.jhi[0] : it.jhi[1];
-              return i;
-            }
-          }
+          return pop_item(seq, [&](const Item& it) {
+            st.j_begin = it.j_begin, st.j_end = it.j_end, st.n_base = it.n_base, st.klen = it.klen;
+            st.jlo = t == 0 ? it.jlo[0] : it.jlo[1];
+            st.jhi = t == 0 ? it.jhi[0] : it.jhi[1];
+          });
         };
         int ci = pop_with_steps(cur);
         if (ci == -2) {
@@ -419,6 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           int kq = 0;           // items whose first QK of this tile has been issued
           int kp = 0;           // items whose last PV of this tile has been issued
           int turn_ph = 0;
+          XFB_MPROF_DECL(16)
           {
             // the very first step: nothing to multiply by V yet
             const bool act = j >= cur.jlo && j < cur.jhi;
@@ -440,6 +540,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             }
           }
           while (ok) {
+            XFB_MPROF_LAP(0)
             // ---- the step after (cur, j): same item, or the first step of the next item with steps
             bool has_next = true, same_item = true;
             int nj = j + 1;
@@ -454,6 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
               has_next = ni >= 0;
               nj = nxt.j_begin;
             }
+            XFB_MPROF_LAP(1)  // pulling the next item
             const int nx_jlo = same_item ? cur.jlo : nxt.jlo, nx_jhi = same_item ? cur.jhi : nxt.jhi;
             const bool act = j >= cur.jlo && j < cur.jhi;
             const bool act_next = has_next && nj >= nx_jlo && nj < nx_jhi;
@@ -462,10 +564,18 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             if (ks1 == kStages) ks1 = 0, kph1 ^= 1;
             ok = mbar_wait(&bar->v_full[vs], vph, abort_flag, budget);
             if (ok && has_next) ok = mbar_wait(&bar->k_full[ks1], kph1, abort_flag, budget);
-            if (ok && first_qk_next) ok = mbar_wait(&bar->q_full[t], kq & 1, abort_flag, budget);
             if (!ok) {
               if (lane == 0) give_up(a, 22);
               break;
+            }
+            // The first QK of the next item needs its Q tile.  If that has not landed yet, the token is not
+            // held back for it: the block ends after the PV and the QK follows out of turn (late_qk).
+            XFB_MPROF_LAP(2)  // waits for V and the next K
+            bool late_qk = false;
+            if (first_qk_next) {
+              int ready = 0;
+              if (lane == 0) ready = mbar_try_wait(&bar->q_full[t], kq & 1) ? 1 : 0;
+              late_qk = __shfl_sync(0xffffffffu, ready, 0) == 0;
             }
             const int n0 = cur.n_base + j * kBN;
             if (n0 + kBN > cur.klen) {
@@ -478,6 +588,21 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
               fence_proxy_async_smem();
               __syncwarp();
             }
+            // If both warps issued at will, their MMAs would interleave one by one,
+            // both tiles would finish together and both softmaxes would run at the
+            // same time with the tensor pipe idle.  Blocks (PV, next QK) are
+            // therefore issued alternately, which keeps the two tiles half a period
+            // apart; the token is passed a few MMAs before the end of a block so
+            // that the hand-over latency is hidden.  The token is waited for before
+            // P: it normally arrives first, and even a satisfied wait costs ~90 clocks
+            // that would otherwise sit between the softmax and its PV.
+            ok = mbar_wait(&bar->turn[t], turn_ph, abort_flag, budget);
+            turn_ph ^= 1;
+            if (!ok) {
+              if (lane == 0) give_up(a, 25 + t);
+              break;
+            }
+            XFB_MPROF_LAP(4)  // wait for the token
             if (act) {
               ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag, budget);
               // the first PV of an item overwrites O_t: the output warps must have read the previous one
@@ -488,25 +613,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
               }
               tc_fence_after();
             }
-            // If both warps issued at will, their MMAs would interleave one by one,
-            // both tiles would finish together and both softmaxes would run at the
-            // same time with the tensor pipe idle.  Blocks (PV, next QK) are
-            // therefore issued alternately, which keeps the two tiles half a period
-            // apart; the token is passed a few MMAs before the end of a block so
-            // that the hand-over latency is hidden.
-            ok = mbar_wait(&bar->turn[t], turn_ph, abort_flag, budget);
-            turn_ph ^= 1;
-            if (!ok) {
-              if (lane == 0) give_up(a, 25 + t);
-              break;
-            }
+            XFB_MPROF_LAP(3)  // V tail, wait for P (and for the output warps at the first PV of an item)
             if (lane == 0) {
               if (act) {
                 issue_pv(vs, j > cur.jlo);
                 if (j == cur.jhi - 1) tc_commit(&bar->o_full[t]);
               }
               tc_commit(&bar->v_empty[vs]);
-              if (act_next) {
+              if (act_next && !late_qk) {
                 issue_qk_part(ks1, 0, D / 32);
                 mbar_arrive(&bar->turn[1 - t]);
                 issue_qk_part(ks1, D / 32, D / 16);
@@ -515,8 +629,27 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
               } else {
                 mbar_arrive(&bar->turn[1 - t]);
               }
-              if (has_next) tc_commit(&bar->k_empty[ks1]);
+              if (has_next && !late_qk) tc_commit(&bar->k_empty[ks1]);
             }
+            XFB_MPROF_LAP(5)  // issuing the block
+            if (late_qk) {
+              XFB_MPROF_COUNT(8)
+              ok = mbar_wait(&bar->k_full[ks1], kph1, abort_flag, budget);
+              if (ok && first_qk_next) ok = mbar_wait(&bar->q_full[t], kq & 1, abort_flag, budget);
+              if (!ok) {
+                if (lane == 0) give_up(a, 27 + t);
+                break;
+              }
+              tc_fence_after();
+              if (lane == 0) {
+                issue_qk_part(ks1, 0, D / 16);
+                tc_commit(&bar->s_full[t]);
+                if (nj == nx_jhi - 1) tc_commit(&bar->q_empty[t]);
+                tc_commit(&bar->k_empty[ks1]);
+              }
+            }
+            XFB_MPROF_LAP(6)  // a QK issued out of turn
+            XFB_MPROF_COUNT(7)
             if (act) {
               ++cnt;
               if (j == cur.jhi - 1) ++kp;
@@ -528,6 +661,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             ks = ks1, kph = kph1;
             if (++vs == kStages) vs = 0, vph ^= 1;
           }
+          XFB_MPROF_STORE(t * 16, 16)
         }
         if (!ok) *abort_flag = 1;
       }
@@ -540,7 +674,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
       int ko[kTiles] = {0, 0};  // items in which tile t took part so far
       bool ok = true;
       while (ok) {
-        const int idx = pop_item(seq);
+        Item it;
+        const int idx = pop_item(seq, [&](const Item& d) { it = d; });
         if (idx < 0) {
           if (idx == -2) {
             give_up(a, 40);
@@ -548,8 +683,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           }
           break;
         }
-        Item it;
-        decode_item(a, idx, it);
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) {
           const int i_loc = it.m0 + t * kBM + row;
@@ -636,35 +769,74 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
       int cnt = 0;  // steps of this tile so far, over all items
       int ka = 0;   // items in which this tile took part so far
       bool ok = true;
+      XFB_PROF_DECL(16)
 
-      // 32 score columns -> 16 packed probability pairs against the maximum -m (nm2 = (-m, -m)); the
-      // raw scores also go into the four running-maximum chains and the probabilities into the sums
-      auto exp_block = [&](const uint32_t (&sr)[32], uint32_t* pr, uint64_t nm2, float (&mx4)[4], uint64_t (&sum2)[4]) {
-        const float* s = reinterpret_cast<const float*>(sr);
+      // visibility of the 32 columns starting at key `col0` for this thread's row: hidden scores become -inf
+      int col_lo = 0, col_hi = 0;
+      auto mask_chunk = [&](float* sc, int col0) {
 #pragma unroll
-        for (int c = 0; c < 32; c += 8) {
-          mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
-          mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
-          mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
-          mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
+        for (int c = 0; c < 32; ++c) {
+          const int col = col0 + c;
+          sc[c] = (col >= col_lo && col < col_hi) ? sc[c] : -INFINITY;
         }
+      };
+      auto chunk_max = [](const float* sc) -> float {
+        float m0 = fmax3(sc[0], sc[1], sc[2]), m1 = fmax3(sc[3], sc[4], sc[5]), m2 = fmax3(sc[6], sc[7], sc[8]), m3 = fmax3(sc[9], sc[10], sc[11]);
+        m0 = fmax3(m0, sc[12], sc[13]), m1 = fmax3(m1, sc[14], sc[15]), m2 = fmax3(m2, sc[16], sc[17]), m3 = fmax3(m3, sc[18], sc[19]);
+        m0 = fmax3(m0, sc[20], sc[21]), m1 = fmax3(m1, sc[22], sc[23]), m2 = fmax3(m2, sc[24], sc[25]), m3 = fmax3(m3, sc[26], sc[27]);
+        m0 = fmax3(m0, sc[28], sc[29]), m1 = fmax3(m1, sc[30], sc[31]);
+        return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+      };
+      // 32 score columns -> 16 packed probability pairs against the maximum -m (nm2 = (-m, -m)), summed into
+      // sum2 and stored to columns [16c, 16c + 16) of S_t
+      auto exp_store = [&](const float* sc, int c, uint64_t nm2, uint64_t (&sum2)[4]) {
+        uint32_t pr[16];
+        // (blocks of 16 independent elements: all FMAs, then all exp2, then the sums and packs -- a lone warp per
+        // scheduler hides no latency by switching warps, the instruction stream has to)
 #pragma unroll
-        for (int c = 0; c < 32; c += 16) {
+        for (int h = 0; h < 32; h += 16) {
           float e[16];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) f2_unpack(ffma2(f2_pack(s[c + i], s[c + i + 1]), sc2, nm2), e[i], e[i + 1]);
+          for (int i = 0; i < 16; i += 2) f2_unpack(ffma2(f2_pack(sc[h + i], sc[h + i + 1]), sc2, nm2), e[i], e[i + 1]);
 #pragma unroll
           for (int i = 0; i < 16; ++i) e[i] = fast_exp2(e[i]);
 #pragma unroll
           for (int i = 0; i < 16; i += 2) {
             sum2[(i / 2) & 3] = fadd2(sum2[(i / 2) & 3], f2_pack(e[i], e[i + 1]));
-            pr[(c + i) / 2] = pack_pair<kBf16>(e[i], e[i + 1]);
+            pr[(h + i) / 2] = pack_pair<kBf16>(e[i], e[i + 1]);
           }
         }
+        XFB_TMEM_ST_16(tmem_s + c * 16, pr);
+      };
+      // O_t *= alpha (per row), through registers
+      auto rescale_o = [&](float alpha) {
+        const uint64_t al2 = f2_pack(alpha, alpha);
+#pragma unroll
+        for (int cblk = 0; cblk < D / 32; ++cblk) {
+          uint32_t orr[32];
+          XFB_TMEM_LD_32(tmem_o + cblk * 32, orr);
+          XFB_TMEM_WAIT_LD_32(orr);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1;
+            f2_unpack(fmul2(f2_pack(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), al2), x0, x1);
+            orr[i] = __float_as_uint(x0);
+            orr[i + 1] = __float_as_uint(x1);
+          }
+          XFB_TMEM_ST_32(tmem_o + cblk * 32, orr);
+        }
+        tc_wait_st();
       };
 
       while (ok) {
-        const int idx = pop_item(seq);
+        struct {
+          int jlo, jhi, m0, shift, shift2, n_base, klen;
+        } it;
+        const int idx = pop_item(seq, [&](const Item& d) {
+          it.jlo = t == 0 ? d.jlo[0] : d.jlo[1];
+          it.jhi = t == 0 ? d.jhi[0] : d.jhi[1];
+          it.m0 = d.m0, it.shift = d.shift, it.shift2 = d.shift2, it.n_base = d.n_base, it.klen = d.klen;
+        });
         if (idx < 0) {
           if (idx == -2) {
             give_up(a, 30);
@@ -672,139 +844,136 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           }
           break;
         }
-        Item it;
-        decode_item(a, idx, it);
-        const int jlo = t == 0 ? it.jlo[0] : it.jlo[1], jhi = t == 0 ? it.jhi[0] : it.jhi[1];
+        const int jlo = it.jlo, jhi = it.jhi;
         if (jhi <= jlo) continue;  // this tile sees no key in this item
         const int mt0 = it.m0 + t * kBM;
         const int i_loc = mt0 + row;
         const bool causal = a.window_right >= 0;
-        const int col_hi = causal ? min(it.klen, i_loc + it.shift + a.window_right + 1) : it.klen;
-        const int col_lo = a.window_left >= 0 ? i_loc + it.shift - a.window_left : 0;
-        float m_run = -INFINITY, l_run = 0.f;
+        col_hi = causal ? min(it.klen, i_loc + it.shift + a.window_right + 1) : it.klen;
+        col_lo = a.window_left >= 0 ? i_loc + it.shift - a.window_left : 0;
+        // m_run: the maximum the probabilities and O_t are taken against (log2 units); m_pend: what it becomes
+        // at the start of the next step (a raise is applied one step late, when O_t may be touched again);
+        // l_run: the row sum against m_run
+        float m_run = -INFINITY, m_pend = -INFINITY, l_run = 0.f;
 
+        XFB_PROF_LAP(0)  // between items: statistics hand-over, next descriptor
         for (int j = jlo; j < jhi; ++j, ++cnt) {
-          const int n0 = it.n_base + j * kBN;
+          int n0 = it.n_base + j * kBN;
+          int klen = it.klen, shift = it.shift;
+          if (a.kv_split > 0) {
+            // which of the two key ranges this step lies in: positions and limits are relative to that range
+            const bool second = n0 >= a.kv_split;
+            klen = second ? it.klen - a.kv_split : a.kv_split;
+            shift = second ? it.shift2 : it.shift;
+            n0 -= second ? a.kv_split : 0;
+            col_hi = min(klen, i_loc + shift + 1);
+          }
           ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag, budget);
+          XFB_PROF_LAP(1)  // wait for the scores
           if (!ok) {
             give_up(a, 31 + t);
             break;
           }
           tc_fence_after();
-          const bool need_mask = (n0 + kBN > it.klen) || (causal && n0 + kBN - 1 > mt0 + it.shift + a.window_right) ||
-                                 (a.window_left >= 0 && n0 < mt0 + kBM - 1 + it.shift - a.window_left);
-          uint32_t pr[kBN / 2];
-          bool done = false;
-          if (j > jlo && !need_mask) {
-            // ---- one pass against the running maximum
-            const float m_use = m_run == -INFINITY ? 0.f : m_run;
-            const uint64_t nm2 = f2_pack(-m_use, -m_use);
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+          const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + a.window_right) ||
+                                 (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
+          {
+            // ---- a raise of the reference maximum that the previous step left pending.  QK(t,j) completing
+            // implies PV(t,j-1) completed: O_t is quiescent here.
+            if (j > jlo && __any_sync(0xffffffffu, m_pend != m_run)) {
+              const float alpha = m_pend == m_run ? 1.f : (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_pend));
+              rescale_o(alpha);
+              l_run *= alpha;
+              m_run = m_pend;
+            }
             uint64_t sum2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
-            uint32_t sa[32], sb[32];
-            XFB_TMEM_LD_32(tmem_s, sa);
-            XFB_TMEM_WAIT_LD_32(sa);
-            XFB_TMEM_LD_32(tmem_s + 32, sb);
-            exp_block(sa, pr, nm2, mx4, sum2);
-            XFB_TMEM_WAIT_LD_32(sb);
-            XFB_TMEM_LD_32(tmem_s + 64, sa);
-            exp_block(sb, pr + 16, nm2, mx4, sum2);
-            XFB_TMEM_WAIT_LD_32(sa);
-            XFB_TMEM_LD_32(tmem_s + 96, sb);
-            exp_block(sa, pr + 32, nm2, mx4, sum2);
-            XFB_TMEM_WAIT_LD_32(sb);
-            exp_block(sb, pr + 48, nm2, mx4, sum2);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;  // scale > 0 (host guarantees)
-            // tcgen05.ld / st are warp-wide: if any row of the warp has to move its maximum, the warp takes the two-pass route
-            if (!__any_sync(0xffffffffu, mx > m_run + kRescaleThreshold)) {
+            float step_max = -INFINITY;  // of the raw scores of this step (visible ones)
+            uint32_t sa[32];
+            int bad = -1;  // first chunk that could not be taken against the current maximum (warp-uniform)
+            // One pass, 32 score columns (a chunk) at a time: masked (diagonal and ragged tiles only), checked, turned
+            // into 16 packed probability pairs that go straight back to tensor memory.  P chunk c lands in columns
+            // [16c, 16c + 16), which held scores that are in registers by then.  One chunk body run four times: the
+            // code of a step stays small, which a scheduler that runs this warp almost alone rewards.
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+              XFB_TMEM_LD_32(tmem_s + c * 32, sa);
+              XFB_TMEM_WAIT_LD_32(sa);
+              float* sc = reinterpret_cast<float*>(sa);
+              if (need_mask) mask_chunk(sc, n0 + c * 32);
+              const float cm = chunk_max(sc);
+              step_max = fmaxf(step_max, cm);
+              const float cms = cm * sl2;  // scale > 0 (host guarantees)
+              if (c == 0 && j == jlo) m_run = m_pend = cms;  // a fresh row: the first chunk gives the provisional maximum
+              // the probabilities of a chunk must stay finite in 16 bits: at most 2^kOverflowLimit against the reference
+              if (__any_sync(0xffffffffu, cms > m_run + kOverflowLimit)) {
+                bad = c;
+                break;
+              }
+              const float m_use = m_run == -INFINITY ? 0.f : m_run;
+              exp_store(sc, c, f2_pack(-m_use, -m_use), sum2);
+            }
+            if (bad < 0) {
+              // a row whose maximum grew by more than the threshold is re-based at the start of the next step
+              const float sm = step_max * sl2;
+              if (sm > m_run + kRescaleThreshold) m_pend = sm;
+            } else {
+              XFB_PROF_COUNT(7)
+              // ---- rare: some score of the warp's rows lies more than 2^kOverflowLimit above its reference maximum
+              // (or the row had no maximum yet).  Chunks below `bad` are stored against the old maximum, the scores
+              // of the others are still in tensor memory: find the true maximum of the rest, re-base everything.
+              float mxr = -INFINITY;
+              for (int c = bad; c < kBN / 32; ++c) {
+                XFB_TMEM_LD_32(tmem_s + c * 32, sa);
+                XFB_TMEM_WAIT_LD_32(sa);
+                float* sc = reinterpret_cast<float*>(sa);
+                if (need_mask) mask_chunk(sc, n0 + c * 32);
+                mxr = fmaxf(mxr, chunk_max(sc));
+              }
+              const float m_new = fmaxf(m_run, mxr * sl2);
+              const float alpha = m_new == m_run ? 1.f : (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new));
+              if (j > jlo) rescale_o(alpha);
+              {
+                float x0, x1, y0, y1;
+                f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
+                f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
+                l_run = (l_run + ((x0 + x1) + (y0 + y1))) * alpha;
+                sum2[0] = sum2[1] = sum2[2] = sum2[3] = f2_pack(0.f, 0.f);
+              }
+              for (int c = 0; c < bad; ++c) {
+                uint32_t pq[16];
+                XFB_TMEM_LD_16(tmem_s + c * 16, pq);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  float lo, hi;
+                  unpack_pair<kBf16>(pq[i], lo, hi);
+                  pq[i] = pack_pair<kBf16>(lo * alpha, hi * alpha);
+                }
+                XFB_TMEM_ST_16(tmem_s + c * 16, pq);
+              }
+              m_run = m_pend = m_new;
+              const float m_use = m_run == -INFINITY ? 0.f : m_run;
+              for (int c = bad; c < kBN / 32; ++c) {
+                XFB_TMEM_LD_32(tmem_s + c * 32, sa);
+                XFB_TMEM_WAIT_LD_32(sa);
+                if (need_mask) mask_chunk(reinterpret_cast<float*>(sa), n0 + c * 32);
+                tc_wait_st();  // (the store of an earlier round of this loop has read the registers it was given)
+                exp_store(reinterpret_cast<float*>(sa), c, f2_pack(-m_use, -m_use), sum2);
+              }
+            }
+            XFB_PROF_COUNT(6)
+            {
               float x0, x1, y0, y1;
               f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
               f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
               l_run += (x0 + x1) + (y0 + y1);
-              done = true;
             }
-          }
-          if (!done) {
-            // ---- two passes: the row maximum first, then the probabilities (S_t is still intact)
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int cblk = 0; cblk < kBN / 32; ++cblk) {
-              uint32_t sr[32];
-              XFB_TMEM_LD_32(tmem_s + cblk * 32, sr);
-              XFB_TMEM_WAIT_LD_32(sr);
-              float* s = reinterpret_cast<float*>(sr);
-              if (need_mask) {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                  const int col = n0 + cblk * 32 + c;
-                  s[c] = (col >= col_lo && col < col_hi) ? s[c] : -INFINITY;
-                }
-              }
-#pragma unroll
-              for (int c = 0; c < 32; c += 8) {
-                mx4[0] = fmax3(mx4[0], s[c], s[c + 1]);
-                mx4[1] = fmax3(mx4[1], s[c + 2], s[c + 3]);
-                mx4[2] = fmax3(mx4[2], s[c + 4], s[c + 5]);
-                mx4[3] = fmax3(mx4[3], s[c + 6], s[c + 7]);
-              }
-            }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
-            const bool raise = mx > m_run + kRescaleThreshold;  // also true on the first visible key (m_run = -inf)
-            const float m_new = raise ? mx : m_run;
-            const float alpha = raise ? (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new)) : 1.f;
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            // QK(t,j) completing implies PV(t,j-1) completed: O_t is quiescent here
-            if (j > jlo && __any_sync(0xffffffffu, raise)) {
-              const uint64_t al2 = f2_pack(alpha, alpha);
-#pragma unroll
-              for (int cblk = 0; cblk < D / 32; ++cblk) {
-                uint32_t orr[32];
-                XFB_TMEM_LD_32(tmem_o + cblk * 32, orr);
-                XFB_TMEM_WAIT_LD_32(orr);
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                  float x0, x1;
-                  f2_unpack(fmul2(f2_pack(__uint_as_float(orr[i]), __uint_as_float(orr[i + 1])), al2), x0, x1);
-                  orr[i] = __float_as_uint(x0);
-                  orr[i + 1] = __float_as_uint(x1);
-                }
-                XFB_TMEM_ST_32(tmem_o + cblk * 32, orr);
-              }
-            }
-            l_run *= alpha;
-            m_run = m_new;
-            const uint64_t nm2 = f2_pack(-m_use, -m_use);
-            uint64_t sum2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
-            float dummy[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int cblk = 0; cblk < kBN / 32; ++cblk) {
-              uint32_t sr[32];
-              XFB_TMEM_LD_32(tmem_s + cblk * 32, sr);
-              XFB_TMEM_WAIT_LD_32(sr);
-              if (need_mask) {
-                float* s = reinterpret_cast<float*>(sr);
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                  const int col = n0 + cblk * 32 + c;
-                  s[c] = (col >= col_lo && col < col_hi) ? s[c] : -INFINITY;
-                }
-              }
-              exp_block(sr, pr + cblk * 16, nm2, dummy, sum2);
-            }
-            float x0, x1, y0, y1;
-            f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
-            f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
-            l_run += (x0 + x1) + (y0 + y1);
-          }
-          {
-            uint32_t* p0 = pr;
-            uint32_t* p1 = pr + 32;
-            XFB_TMEM_ST_32(tmem_s, p0);
-            XFB_TMEM_ST_32(tmem_s + 32, p1);
+            XFB_PROF_LAP(2)
           }
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(&bar->p_full[t]);
+          XFB_PROF_LAP(4)  // storing P
         }
         if (!ok) break;
         // hand the row's statistics to the output warps
@@ -819,6 +988,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
       }
       if (!ok) *abort_flag = 1;
       tc_fence_before();
+      XFB_PROF_STORE(warp * 8, 8)
     }
 
     __syncthreads();
@@ -857,6 +1027,18 @@ static int launch_t(const Sm100Args& a, cudaStream_t stream) {
 }
 
 }  // namespace pst
+
+#ifdef XFB_PST_PROFILE
+extern "C" __attribute__((visibility("default"))) int xfb200_debug_read_prefill_profile(long long* out, int clear) {
+  cudaDeviceSynchronize();
+  cudaError_t e = cudaMemcpyFromSymbol(out, pst::g_prof, sizeof(long long) * 160 * 64);
+  if (e == cudaSuccess && clear) {
+    static long long zeros[160 * 64] = {0};
+    e = cudaMemcpyToSymbol(pst::g_prof, zeros, sizeof(zeros));
+  }
+  return e == cudaSuccess ? 0 : -3;
+}
+#endif
 
 int prefill_sm100_persist_launch(Sm100Args a, int head_dim, bool bf16, cudaStream_t stream) {
   if (head_dim == 128) return bf16 ? pst::launch_t<128, true>(a, stream) : pst::launch_t<128, false>(a, stream);

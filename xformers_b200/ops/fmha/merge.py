@@ -114,8 +114,37 @@ def merge_attentions(
     return out5, lse_out
 
 
+def _merge_varargs_impl(
+    attn_split: List[torch.Tensor],
+    lse_split: List[torch.Tensor],
+    write_lse: bool = True,
+    output_dtype: Optional[torch.dtype] = None,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    out, lse = merge_attentions(list(attn_split), list(lse_split), write_lse, output_dtype)
+    if lse is None:  # a custom op returns tensors only: an empty one stands for "not written"
+        lse = out.new_empty((0,), dtype=torch.float32)
+    return out, lse
+
+
+def _merge_varargs_fake(attn_split, lse_split, write_lse=True, output_dtype=None):
+    a0, l0 = attn_split[0], lse_split[0]
+    out = a0.new_empty(a0.shape, dtype=output_dtype or a0.dtype)
+    lse = l0.new_empty(l0.shape if write_lse else (0,), dtype=torch.float32)
+    return out, lse
+
+
+# The list form as a custom operator with a fake implementation, so that a graph traced by
+# torch.compile(fullgraph=True) keeps the merge as one opaque node (the reference registers
+# ``xformers::fmha_merge_attentions_varargs`` for the same purpose, xformers/ops/fmha/triton_splitk.py:42-53).
+_merge_varargs_op = torch.library.custom_op(
+    "xformers_b200::fmha_merge_attentions_varargs", _merge_varargs_impl, mutates_args=(), device_types=["cuda"]
+)
+torch.library.register_fake("xformers_b200::fmha_merge_attentions_varargs", _merge_varargs_fake)
+
+
 def merge_attentions_varargs(attn_split: List[torch.Tensor], lse_split: List[torch.Tensor], write_lse: bool = True,
                              output_dtype: Optional[torch.dtype] = None):
     """List form under the name the reference registers as a custom op
-    (xformers/ops/fmha/triton_splitk.py:42-53)."""
-    return merge_attentions(list(attn_split), list(lse_split), write_lse, output_dtype)
+    (xformers/ops/fmha/triton_splitk.py:42-53): ``(out, lse)``, ``lse`` ``None`` when not written."""
+    out, lse = _merge_varargs_op(list(attn_split), list(lse_split), write_lse, output_dtype)
+    return out, (lse if write_lse else None)

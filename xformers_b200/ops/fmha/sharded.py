@@ -4,19 +4,26 @@ The reference has no ring or context-parallel attention; its long-context
 primitive is algebraic: attention over parts of the keys
 (``memory_efficient_attention_partial``) followed by ``merge_attentions``
 (tests/test_fmha_merge_attentions.py:234-363).  Here the parts live on
-different GPUs of one NVSwitch box: rank r holds the contiguous key range
-``[kv_offset_r, kv_offset_r + len_r)``, runs the prefill kernel over all
-queries against its shard with the causal diagonal shifted by ``kv_offset_r``,
-and the per-rank ``(O_r, LSE_r)`` are exchanged with one NCCL all-gather over
-NVLink and combined by the same LSE-merge kernel.  Query rows that lie before a
-shard see none of its keys and arrive with ``LSE = -inf`` (weight 0).  For
-balanced causal work a rank may hold the two key ranges of :func:`zigzag_bounds`
-instead; it then merges its own two partials before the exchange.
+different GPUs of one NVSwitch box: rank r holds one or two ranges of the keys,
+runs the prefill kernel over the queries against them with the causal diagonal
+shifted by the ranges' positions, and the per-rank ``(O_r, LSE_r)`` are
+exchanged over NCCL/NVLink and combined by the same LSE-merge kernel.  Query
+rows that lie before a range see none of its keys and arrive with ``LSE =
+-inf`` (weight 0).
+
+For balanced causal work a rank holds the two key ranges of
+:func:`zigzag_bounds`; they are laid back to back once (keys and values are
+small next to the partial outputs) and one kernel launch covers both, so no
+local merge is needed.  The queries are processed in stripes: the exchange of
+a stripe -- all-to-all of the partials by query slice, LSE merge of the slice,
+all-gather of the merged slices -- runs on a side stream while the next stripe
+is computed.  Remote data is always landed in local memory by NCCL before a
+kernel reads it.
 """
 
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence, Tuple, Union
+from typing import Callable, Dict, List, Optional, Sequence, Tuple, Union
 
 import torch
 import torch.distributed as dist
@@ -49,7 +56,7 @@ def zigzag_bounds(total: int, world_size: int, rank: int) -> List[Tuple[int, int
     return [span(rank), span(2 * world_size - 1 - rank)]
 
 
-def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype):
+def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype, kv_split: int = 0, kv_offset2: int = 0):
     from . import b200
 
     inp = Inputs(q, k, v, LowerTriangularMask() if causal else None, scale=scale, output_dtype=partial_dtype, is_partial=True)
@@ -57,7 +64,7 @@ def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype)
     reasons = b200.FwOp.not_supported_reasons(inp)
     if reasons:
         raise ValueError("sharded attention: " + "; ".join(reasons))
-    out, ctx = b200.FwOp._apply(inp, want_lse=True, kv_offset=kv_offset if causal else 0)
+    out, ctx = b200.FwOp._apply(inp, want_lse=True, kv_offset=kv_offset if causal else 0, kv_split=kv_split, kv_offset2=kv_offset2)
     return out, ctx.lse
 
 
@@ -65,6 +72,25 @@ def _merge_on_gpu(outs, lses, out_dtype):
     from .merge import merge_attentions
 
     return merge_attentions(outs, lses, write_lse=True, output_dtype=out_dtype)
+
+
+def _cat_keeping_broadcast(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``torch.cat`` along the sequence axis that keeps a broadcast head axis (stride 0) broadcast."""
+    if a.ndim == 5 and a.stride(3) == 0 and b.stride(3) == 0:
+        return torch.cat([a[:, :, :, :1], b[:, :, :, :1]], dim=1).expand(-1, -1, -1, a.shape[3], -1)
+    if a.ndim == 4 and a.stride(2) == 0 and b.stride(2) == 0:
+        return torch.cat([a[:, :, :1], b[:, :, :1]], dim=1).expand(-1, -1, a.shape[2], -1)
+    return torch.cat([a, b], dim=1)
+
+
+_COMM_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
+
+
+def _comm_stream(device: torch.device):
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _COMM_STREAMS:
+        _COMM_STREAMS[idx] = torch.cuda.Stream(device=device)
+    return _COMM_STREAMS[idx]
 
 
 def sharded_kv_attention_forward(
@@ -80,17 +106,23 @@ def sharded_kv_attention_forward(
     partial_fn: Callable = _partial_on_gpu,
     merge_fn: Callable = _merge_on_gpu,
     exchange: str = "all_to_all",
+    stripes: int = 1,
+    timings: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
     key/value shard ``[B, len_r, (G,) H, D]`` starting at global key index
     ``kv_offset``.  Returns the full ``(out, lse)`` on every rank.  Several key
     ranges per rank are passed as sequences of shards and offsets (empty ranges
-    are skipped); the rank merges their partials before the exchange.
+    are skipped).
 
-    ``exchange="all_to_all"`` (when the number of queries divides by the number of
-    ranks): every rank receives the partials of its slice of the queries, merges
-    them and the merged slices are all-gathered; ``"all_gather"``: every rank
-    receives every partial and merges all queries itself.
+    ``exchange="all_to_all"`` (when the queries of a stripe divide by the number
+    of ranks): every rank receives the partials of its slice of the queries,
+    merges them and the merged slices are all-gathered; ``"all_gather"``: every
+    rank receives every partial and merges all queries itself.  ``stripes`` cuts
+    the queries into that many stripes whose exchanges overlap the attention of
+    the following stripe (CUDA tensors, all-to-all exchange).  ``timings``, a
+    dict, receives CUDA events (``start``, ``attention_done``, ``done``) for a
+    break-down.
 
     ``partial_fn`` / ``merge_fn`` exist so that the exchange logic can be
     exercised with CPU stand-ins under the gloo backend.
@@ -100,48 +132,121 @@ def sharded_kv_attention_forward(
         key_shard, value_shard, kv_offset = [key_shard], [value_shard], [kv_offset]
     if not (len(key_shard) == len(value_shard) == len(kv_offset)) or not len(key_shard):
         raise ValueError("sharded attention: key shards, value shards and offsets must pair up")
-    parts = [
-        partial_fn(query, k, v, causal, off, scale, partial_dtype)
-        for k, v, off in zip(key_shard, value_shard, kv_offset)
-        if k.shape[1] > 0
-    ]
-    if not parts:
-        # this rank holds no keys at all: a partial of weight 0, shaped like a neighbour's (one key, then discarded)
-        k0, v0 = key_shard[0], value_shard[0]
-        one = lambda t: t.new_zeros((t.shape[0], 1) + tuple(t.shape[2:]))
-        out_r, lse_r = partial_fn(query, one(k0), one(v0), False, 0, scale, partial_dtype)
-        out_r, lse_r = torch.zeros_like(out_r), torch.full_like(lse_r, float("-inf"))
-    elif len(parts) == 1:
-        out_r, lse_r = parts[0]
-    else:
-        out_r, lse_r = merge_fn([p[0] for p in parts], [p[1] for p in parts], parts[0][0].dtype)
+    ranges = [(k, v, int(off)) for k, v, off in zip(key_shard, value_shard, kv_offset) if k.shape[1] > 0]
+    mq = query.shape[1]
+    on_gpu = query.is_cuda
+
+    # Two ranges that one launch can cover: causal, the first one a whole number of key tiles, the second one later.
+    fused = None
+    if (partial_fn is _partial_on_gpu and causal and len(ranges) == 2 and ranges[0][0].shape[1] % 128 == 0
+            and ranges[1][2] >= ranges[0][2] + ranges[0][0].shape[1] and query.shape[-1] in (64, 128)):
+        (k0, v0, o0), (k1, v1, o1) = ranges
+        fused = (_cat_keeping_broadcast(k0, k1), _cat_keeping_broadcast(v0, v1), k0.shape[1], o0, o1)
+
+    def local_partial(a: int, b: int):
+        """(out, lse) of this rank's keys for the query rows [a, b)."""
+        q = query[:, a:b]
+        if fused is not None:
+            kc, vc, split, o0, o1 = fused
+            return partial_fn(q, kc, vc, True, o0 - a, scale, partial_dtype, kv_split=split, kv_offset2=o1 - a)
+        parts = [partial_fn(q, k, v, causal, off - a, scale, partial_dtype) for k, v, off in ranges]
+        if not parts:
+            # this rank holds no keys at all: a partial of weight 0, shaped like a neighbour's (one key, then discarded)
+            k0, v0 = key_shard[0], value_shard[0]
+            one = lambda t: t.new_zeros((t.shape[0], 1) + tuple(t.shape[2:]))
+            o, l = partial_fn(q, one(k0), one(v0), False, 0, scale, partial_dtype)
+            return torch.zeros_like(o), torch.full_like(l, float("-inf"))
+        if len(parts) == 1:
+            return parts[0]
+        return merge_fn([p[0] for p in parts], [p[1] for p in parts], parts[0][0].dtype)
+
+    if timings is not None and on_gpu:
+        timings["start"] = torch.cuda.Event(enable_timing=True)
+        timings["start"].record()
+
     if world == 1:
-        return merge_fn([out_r], [lse_r], query.dtype)
-    out_r = out_r.contiguous()
-    lse_r = lse_r.contiguous()
-    mq = out_r.shape[1]
-    if exchange == "all_to_all" and mq % world == 0 and lse_r.shape[-1] == mq:
-        # Every rank merges one slice of the queries: the partials of that slice come
-        # in by all-to-all (1/world of an all-gather's volume), the merged slices in the
-        # output dtype go round by all-gather.
-        ms = mq // world
-        send_o = out_r.view(out_r.shape[0], world, ms, *out_r.shape[2:]).transpose(0, 1).contiguous()      # [world, B, ms, ...]
-        send_l = lse_r.view(*lse_r.shape[:-1], world, ms).movedim(-2, 0).contiguous()                        # [world, B, .., ms]
+        out_r, lse_r = local_partial(0, mq)
+        res = merge_fn([out_r], [lse_r], query.dtype)
+        if timings is not None and on_gpu:
+            for name in ("attention_done", "done"):
+                timings[name] = torch.cuda.Event(enable_timing=True)
+                timings[name].record()
+        return res
+
+    use_a2a = exchange == "all_to_all" and mq % world == 0
+    n_stripes = max(1, int(stripes)) if (use_a2a and on_gpu) else 1
+    while n_stripes > 1 and (mq % n_stripes or (mq // n_stripes) % world):
+        n_stripes -= 1
+
+    if not use_a2a:
+        out_r, lse_r = local_partial(0, mq)
+        out_r, lse_r = out_r.contiguous(), lse_r.contiguous()
+        if timings is not None and on_gpu:
+            timings["attention_done"] = torch.cuda.Event(enable_timing=True)
+            timings["attention_done"].record()
+        outs = torch.empty((world,) + tuple(out_r.shape), dtype=out_r.dtype, device=out_r.device)
+        lses = torch.empty((world,) + tuple(lse_r.shape), dtype=lse_r.dtype, device=lse_r.device)
+        # the flat form (ranks concatenated along dim 0) is the one every backend takes
+        dist.all_gather_into_tensor(outs.view(-1, *out_r.shape[1:]), out_r, group=group)
+        dist.all_gather_into_tensor(lses.view(-1, *lse_r.shape[1:]), lse_r, group=group)
+        res = merge_fn(outs, lses, query.dtype)
+        if timings is not None and on_gpu:
+            timings["done"] = torch.cuda.Event(enable_timing=True)
+            timings["done"].record()
+        return res
+
+    # ---- all-to-all by query slice, stripe by stripe
+    ms = mq // n_stripes       # rows of a stripe
+    msw = ms // world          # rows of a stripe that one rank merges
+    # the result is allocated by the calling stream; the side stream fills it stripe by stripe
+    out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
+    lse = torch.empty((query.shape[0],) + tuple(query.shape[2:-1]) + (mq,), dtype=torch.float32, device=query.device)
+    main = torch.cuda.current_stream(query.device) if on_gpu else None
+    comm = _comm_stream(query.device) if (on_gpu and n_stripes > 1) else main
+
+    def exchange_stripe(a: int, out_s: torch.Tensor, lse_s: torch.Tensor):
+        B = out_s.shape[0]
+        # partials of query slice w go to rank w: [world, B, msw, ...] (no copy for B == 1) and [world, B, .., msw]
+        send_o = out_s.reshape(B, world, msw, *out_s.shape[2:]).transpose(0, 1).contiguous()
+        send_l = lse_s.reshape(*lse_s.shape[:-1], world, msw).movedim(-2, 0).contiguous()
         recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
         dist.all_to_all_single(recv_o, send_o, group=group)
         dist.all_to_all_single(recv_l, send_l, group=group)
-        out_s, lse_s = merge_fn(recv_o, recv_l, query.dtype)                                               # [B, ms, ...], [B, .., ms]
-        out_s, lse_s = out_s.contiguous(), lse_s.contiguous()
-        all_o = torch.empty((world,) + tuple(out_s.shape), dtype=out_s.dtype, device=out_s.device)
-        all_l = torch.empty((world,) + tuple(lse_s.shape), dtype=lse_s.dtype, device=lse_s.device)
-        dist.all_gather_into_tensor(all_o.view(-1, *out_s.shape[1:]), out_s, group=group)
-        dist.all_gather_into_tensor(all_l.view(-1, *lse_s.shape[1:]), lse_s, group=group)
-        out = all_o.transpose(0, 1).reshape(out_s.shape[0], mq, *out_s.shape[2:])
-        lse = all_l.movedim(0, -2).reshape(*lse_s.shape[:-1], mq)
-        return out, lse
-    outs = torch.empty((world,) + tuple(out_r.shape), dtype=out_r.dtype, device=out_r.device)
-    lses = torch.empty((world,) + tuple(lse_r.shape), dtype=lse_r.dtype, device=lse_r.device)
-    # the flat form (ranks concatenated along dim 0) is the one every backend takes
-    dist.all_gather_into_tensor(outs.view(-1, *out_r.shape[1:]), out_r, group=group)
-    dist.all_gather_into_tensor(lses.view(-1, *lse_r.shape[1:]), lse_r, group=group)
-    return merge_fn(outs, lses, query.dtype)
+        m_o, m_l = merge_fn(recv_o, recv_l, query.dtype)                       # [B, msw, ...], [B, .., msw]
+        m_o, m_l = m_o.contiguous(), m_l.contiguous()
+        if B == 1:
+            # the merged slices of a stripe are consecutive rows of the result: gather them in place
+            dist.all_gather_into_tensor(out[0, a : a + ms], m_o[0], group=group)
+        else:
+            all_o = torch.empty((world,) + tuple(m_o.shape), dtype=m_o.dtype, device=m_o.device)
+            dist.all_gather_into_tensor(all_o.view(-1, *m_o.shape[1:]), m_o, group=group)
+            out[:, a : a + ms] = all_o.transpose(0, 1).reshape(B, ms, *m_o.shape[2:])
+        all_l = torch.empty((world,) + tuple(m_l.shape), dtype=m_l.dtype, device=m_l.device)
+        dist.all_gather_into_tensor(all_l.view(-1, *m_l.shape[1:]), m_l, group=group)
+        lse[..., a : a + ms] = all_l.movedim(0, -2).reshape(*m_l.shape[:-1], ms)
+
+    for s in range(n_stripes):
+        a = s * ms
+        out_s, lse_s = local_partial(a, a + ms)
+        if comm is main:
+            exchange_stripe(a, out_s, lse_s)
+            continue
+        ready = torch.cuda.Event()
+        ready.record(main)
+        # (allocated by the calling stream, consumed by the side stream: their memory must not be reused before that)
+        out_s.record_stream(comm)
+        lse_s.record_stream(comm)
+        with torch.cuda.stream(comm):
+            comm.wait_event(ready)
+            exchange_stripe(a, out_s, lse_s)
+    if timings is not None and on_gpu:
+        timings["attention_done"] = torch.cuda.Event(enable_timing=True)
+        timings["attention_done"].record(main)
+    if comm is not main:
+        out.record_stream(comm)
+        lse.record_stream(comm)
+        main.wait_stream(comm)
+    if timings is not None and on_gpu:
+        timings["done"] = torch.cuda.Event(enable_timing=True)
+        timings["done"].record(main)
+    return out, lse
