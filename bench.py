@@ -350,7 +350,8 @@ def decode_workload(dev, quant, seed: int = 0, B: int = 64):
             vq[:, lo : lo + step], vss[:, lo : lo + step] = gpu_quantize_fp8(v[:, lo : lo + step])
         k, v = kq, vq
         row_bytes = D + 4
-        kss, vss = kss.expand(-1, -1, -1, G).contiguous(), vss.expand(-1, -1, -1, G).contiguous()
+        # one scale/shift word per token and kv head, expanded over the query heads of the group like K and V themselves
+        kss, vss = kss.expand(-1, -1, -1, G), vss.expand(-1, -1, -1, G)
     elif quant:
         kq = torch.empty(shape[:-1] + (D // 8 + 1,), dtype=torch.int32, device=dev)
         vq = torch.empty_like(kq)
@@ -617,6 +618,8 @@ def main():
 
     # ------------------------------------------- packed varlen GQA (rank 0)
     if "varlen" in legs and rank == 0:
+        import oracle
+
         g = torch.Generator().manual_seed(0)
         lens = torch.randint(256, 4097, (16,), generator=g).tolist()
         total = sum(lens)
@@ -626,38 +629,102 @@ def main():
         vv = torch.randn(1, total, 8, 1, 128, generator=gd, device=dev, dtype=torch.bfloat16).expand(-1, -1, -1, 4, -1)
         vbias = ab.BlockDiagonalCausalMask.from_seqlens(lens, device=dev)
         fn = lambda: xops.memory_efficient_attention_forward(vq, vk, vv, vbias, op=fmha.b200.FwOp)
-        v_steps = max(5, min(args.steps, 30))
-        ms, win = event_time_ms(fn, v_steps, 3)
+        v_reps = max(20, min(args.steps, 50))
+        med, best, win = graph_time_ms(fn, v_reps)
         windows.append(win)
         vflops = 8192.0 * sum(l * l for l in lens)
-        vt = vflops / (ms / v_steps * 1e-3) / 1e12
-        out_line["varlen_gqa"] = {"value": vt, "unit": UNIT, "ms_per_step": ms / v_steps, "frac_of_peak": vt / peaks["bf16_tflops"],
+        vt = vflops / (med * 1e-3) / 1e12
+        # parity: the shortest and the longest sequence, one KV group each
+        vo, vl = xops.memory_efficient_attention_forward_requires_grad(vq, vk, vv, vbias, op=fmha.b200.FwOp)
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        eo = el = 0.0
+        picks = [min(range(16), key=lambda i: lens[i]), max(range(16), key=lambda i: lens[i])]
+        for i, grp in zip(picks, (0, 7)):
+            a_, b_ = starts[i], starts[i + 1]
+            ro, rl = oracle.ref_attention_with_lse(vq[:, a_:b_, grp].float().cpu(), vk[:, a_:b_, grp].float().cpu(), vv[:, a_:b_, grp].float().cpu(),
+                                                   oracle.causal_mask(b_ - a_, b_ - a_))
+            eo = max(eo, float((vo[:, a_:b_, grp].float().cpu() - ro).abs().max()))
+            el = max(el, float((vl[:, grp, :, a_:b_].cpu() - rl).abs().max()))
+        out_line["varlen_gqa"] = {"value": vt, "unit": UNIT, "ms_per_step": med, "ms_best": best, "replays": v_reps, "timing": "median of CUDA-graph replays",
+                                  "frac_of_peak": vt / peaks["bf16_tflops"],
+                                  "parity": {"max_abs_o": eo, "max_abs_lse": el, "rows": f"sequences {picks} (lengths {[lens[i] for i in picks]}), groups 0 and 7",
+                                             "ok": bool(eo <= 2e-2 and el <= 1e-3), "tolerance": "O 2e-2, LSE 1e-3"},
                                   "workload": f"16 seqs U[256,4096] (total {total}), BlockDiagonalCausalMask, Hq=32 Hkv=8 D=128 bf16"}
-        del vq, vk, vv
+        launches += v_reps + 6
+        del vq, vk, vv, vo, vl
         torch.cuda.empty_cache()
     barrier()
 
     # ------------------------------------------------ long context (all ranks)
     if "long" in legs:
-        S, Hkv, G, D = 131072, 8, 8, 128
-        spans = zigzag_bounds(S, world, rank) if world > 1 else [(0, S)]
-        gd = torch.Generator(device=dev).manual_seed(1234)
+        import oracle
+
+        S, Hkv, G, D = (32768 if args.small else 131072), 8, 8, 128
+        gd = torch.Generator(device=dev).manual_seed(1234)  # the same tensors on every rank; a rank uses its key ranges only
         lq = torch.randn(1, S, Hkv, G, D, generator=gd, device=dev, dtype=torch.bfloat16)
         lk_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
         lv_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
-        lk = [lk_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
-        lv = [lv_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
-        fn = lambda: sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True)
-        l_steps = 3
-        ms, win = event_time_ms(fn, l_steps, 1, barrier)
-        windows.append(win)
-        ms = max_over_ranks(ms)
         lflops = 4.0 * S * S * D * Hkv * G / 2.0
-        lt = lflops / (ms / l_steps * 1e-3) / 1e12
-        out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms / l_steps, "scaling": "strong",
-                                    "ideal_speedup": float(world),
-                                    "workload": "1 x 131072 causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work), local merge, NCCL all-to-all of the partials by query slice, LSE merge of the slice, all-gather of the merged slices"}
-        del lq, lk, lv, lk_full, lv_full
+
+        def long_leg(spans, exchange, stripes, l_steps, l_warm):
+            lk = [lk_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
+            lv = [lv_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
+            res = {}
+
+            def fn():
+                res["out"], res["lse"] = sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True,
+                                                                      exchange=exchange, stripes=stripes)
+
+            ms, win = event_time_ms(fn, l_steps, l_warm, barrier)
+            windows.append(win)
+            ms = max_over_ranks(ms) / l_steps
+            # break-down of one more step: attention of this rank's keys / what the exchange adds after it
+            tm = {}
+            sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True, exchange=exchange, stripes=stripes, timings=tm)
+            torch.cuda.synchronize()
+            att = max_over_ranks(tm["start"].elapsed_time(tm["attention_done"]))
+            tot = max_over_ranks(tm["start"].elapsed_time(tm["done"]))
+            # parity of the leg's own output: rows at the start, the middle and the end of this rank's share of the queries
+            lo_r, hi_r = rank * (S // world), (rank + 1) * (S // world)
+            rows = sorted({lo_r, lo_r + 1, (lo_r + hi_r) // 2, hi_r - 2, hi_r - 1})
+            heads = [0, G - 1]
+            mask = torch.stack([oracle.causal_mask(1, S, kv_offset=-r)[0] for r in rows])
+            ro, rl = oracle.ref_attention_with_lse(lq[:, rows, 0][:, :, heads].float().cpu(), lk_full[:, :, 0].expand(-1, -1, len(heads), -1).float().cpu(),
+                                                   lv_full[:, :, 0].expand(-1, -1, len(heads), -1).float().cpu(), mask.expand(1, len(heads), len(rows), S))
+            eo = float((res["out"][:, rows, 0][:, :, heads].float().cpu() - ro).abs().max())
+            el = float((res["lse"][:, 0][:, heads][..., rows].cpu() - rl).abs().max())
+            if world > 1:
+                t = torch.tensor([eo, el], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                eo, el = float(t[0]), float(t[1])
+            del res
+            return ms, {"attention_ms": att, "step_ms": tot, "exchange_after_attention_ms": tot - att}, \
+                {"max_abs_o": eo, "max_abs_lse": el, "rows": f"5 rows of every rank's share of the queries, KV group 0, heads {heads} (max over ranks)",
+                 "ok": bool(eo <= 2e-2 and el <= 1e-3), "tolerance": "O 2e-2, LSE 1e-3"}
+
+        l_steps, l_warm = (10, 2) if not args.small else (3, 1)
+        spans = zigzag_bounds(S, world, rank) if world > 1 else [(0, S)]
+        n_str = 8 if world > 1 else 1
+        ms, brk, par = long_leg(spans, "all_to_all", n_str, l_steps, l_warm)
+        lt = lflops / (ms * 1e-3) / 1e12
+        out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms, "steps": l_steps, "warmup": l_warm, "scaling": "strong",
+                                    "ideal_speedup": float(world), "breakdown": brk, "parity": par, "query_stripes": n_str,
+                                    "workload": f"1 x {S} causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work) covered by one launch per query stripe; per stripe NCCL all-to-all of the fp32 partials by query slice, LSE merge of the slice, all-gather of the merged slices, on a side stream behind the next stripe's attention"}
+        launches += (l_steps + l_warm + 1) * n_str
+        if world > 1:
+            # the literal form of the baseline configuration: one contiguous key shard per rank, all-gather of the partials, one merge
+            from xformers_b200.ops.fmha.sharded import shard_bounds
+
+            c_steps, c_warm = (5, 1)
+            ms, brk, par = long_leg([shard_bounds(S, world, rank)], "all_gather", 1, c_steps, c_warm)
+            ct = lflops / (ms * 1e-3) / 1e12
+            r2 = world * world / (2.0 * world - 1.0)
+            out_line["long_context_contiguous"] = {"value": ct, "unit": UNIT, "ms_per_step": ms, "steps": c_steps, "warmup": c_warm, "scaling": "strong",
+                                                   "ideal_speedup": r2, "breakdown": brk, "parity": par,
+                                                   "workload": f"1 x {S} causal, contiguous key shards, NCCL all-gather of the fp32 partials, one LSE merge; causal work is imbalanced by construction: ideal speed-up R^2/(2R-1) = {r2:.2f}"}
+        del lq, lk_full, lv_full
         torch.cuda.empty_cache()
 
     if rank == 0:
@@ -669,6 +736,7 @@ def main():
                 "value": cflops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                 "sample": f"B={CPU_SAMPLE['B']} x H={CPU_SAMPLE['H']} heads of the headline configuration, best of {len(times)} runs (median {statistics.median(times):.3f} s); fp32 oracle",
             }
+        out_line["gpu_launches_all_legs"] = launches
         print(json.dumps(out_line), flush=True)
     if world > 1:
         dist.barrier()

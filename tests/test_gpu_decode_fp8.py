@@ -55,10 +55,15 @@ def _expand(t, G):
 @pytest.mark.parametrize("page_size", [64, 256])
 @pytest.mark.parametrize("Hkv,G", [(1, 1), (1, 8), (2, 8), (8, 8), (4, 4)])
 @pytest.mark.parametrize("B,Mkv", [(1, 2048), (5, 1024)])
-def test_rowwise_fp8(B, Mkv, Hkv, G, page_size, dtype, random_bytes):
+@pytest.mark.parametrize("replicated", [True, False])
+def test_rowwise_fp8(B, Mkv, Hkv, G, page_size, dtype, random_bytes, replicated):
     """tests/test_mem_eff_attention.py:2818-2881: the fp8 operator equals
-    attention on the dequantised cache; the paged cache equals the padded one."""
+    attention on the dequantised cache; the paged cache equals the padded one.
+    ``replicated``: the scale/shift word of a (token, kv head) entry is laid out once per
+    query head of the group, as the reference's helper does it (tests/utils.py:175-188);
+    otherwise one word per entry, expanded over the query heads with stride 0 like K and V."""
     require_cuda()
+    rep = (lambda t: t.contiguous()) if replicated else (lambda t: t)
     q, kw, vw, kss, vss, k_deq, v_deq = _fp8_case(B, Mkv, Hkv, G, dtype, random_bytes=random_bytes)
     g = torch.Generator().manual_seed(3)
     lens = torch.randint(1, Mkv + 1, (B,), generator=g).tolist()
@@ -68,7 +73,7 @@ def test_rowwise_fp8(B, Mkv, Hkv, G, page_size, dtype, random_bytes):
     cu = lambda t: t.cuda()
     inp = S.InputsFp8(
         query=cu(q), key=_expand(cu(kw), G), value=_expand(cu(vw), G), attn_bias=bias,
-        k_fp8_scale_shift=_expand(cu(kss), G).contiguous(), v_fp8_scale_shift=_expand(cu(vss), G).contiguous(),
+        k_fp8_scale_shift=rep(_expand(cu(kss), G)), v_fp8_scale_shift=rep(_expand(cu(vss), G)),
     )
     assert not S.FwOp.not_supported_reasons(inp)
     out, ctx = fmha._memory_efficient_attention_forward_requires_grad(inp, op=S.FwOp)
@@ -83,8 +88,8 @@ def test_rowwise_fp8(B, Mkv, Hkv, G, page_size, dtype, random_bytes):
     pbias = bias.make_paged(perm.cuda(), page_size, ab.PagedBlockDiagonalCausalWithOffsetPaddedKeysMask)
     inp_p = S.InputsFp8(
         query=cu(q), key=_expand(cu(sc(kw)), G), value=_expand(cu(sc(vw)), G), attn_bias=pbias,
-        k_fp8_scale_shift=_expand(cu(sc(kss.unsqueeze(-1)).squeeze(-1)), G).contiguous(),
-        v_fp8_scale_shift=_expand(cu(sc(vss.unsqueeze(-1)).squeeze(-1)), G).contiguous(),
+        k_fp8_scale_shift=rep(_expand(cu(sc(kss.unsqueeze(-1)).squeeze(-1)), G)),
+        v_fp8_scale_shift=rep(_expand(cu(sc(vss.unsqueeze(-1)).squeeze(-1)), G)),
     )
     out_p, ctx_p = fmha._memory_efficient_attention_forward_requires_grad(inp_p, op=S.FwOp)
     assert torch.equal(out_p, out) and torch.equal(ctx_p.lse, ctx.lse), "page placement must not change a single bit"

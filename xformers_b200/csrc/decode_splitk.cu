@@ -60,7 +60,8 @@ struct DecodeArgs {
   const int32_t* k_ss; // fp8: scale/shift words of K and V, strides in words
   const int32_t* v_ss;
   int64_t kss_m, kss_g, vss_m, vss_g;
-  int32_t ss_tma;      // fp8: the scale/shift words come by tiled copies of 16 bytes per (token, head), the word first
+  int32_t ss_tma;      // fp8: the scale/shift words come by tiled copies: 1 = 16 bytes per (token, head), the word first;
+                       // 2 = compact tensors, the words of the hb heads of a token adjacent
   int32_t ss_bytes;    // fp8: bytes of the scale/shift words of K (or V) in a stage
   int32_t copy_group;  // tokens per bulk copy (int4 only, mode 0)
   int32_t stages;         // depth of the shared-memory ring
@@ -706,11 +707,13 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
 // int4 row-wise cache with NG > 1 quantisation groups per row (the first NG
 // words of a row are the (scale | shift << 16) words of its groups of D / NG
 // elements).  Same products as consume_int4, but a scale now belongs to a
-// (token, group) pair and a k-step or an output tile may mix groups, so the
+// (token, group) pair.  K: the products of every group are accumulated on their
+// own and scaled in fp32 afterwards (the scores, hence the log-sum-exp, see no
+// rounding of K).  V: an output tile may mix groups along the token axis, so the
 // scales are folded into the unpacked elements themselves (one more half2
-// multiply per nibble pair, on the FMA pipe) instead of into the scores and the
-// probabilities; the shifts become per-group terms: shift_g x (sum of q over
-// group g) for K, sum_t p_t x shift_{t,g} added to the columns of group g for V.
+// multiply per nibble pair, on the FMA pipe).  The shifts become per-group
+// terms: shift_g x (sum of q over group g) for K, sum_t p_t x shift_{t,g} added
+// to the columns of group g for V.
 // ---------------------------------------------------------------------------
 template <int D, int NTQ, bool kBf16, int NG>
 __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const DecWarp& w) {
@@ -836,37 +839,93 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
       const int t0 = t_sub + r, t1 = t_sub + r + 8;
       const bool in0 = t0 < w.chunk_hi, in1 = t1 < w.chunk_hi;  // tokens past the end were not copied
 
-      // ------------------------------------------- S^T = K Q^T with K already scaled
-      float s[NTQ][4], s2[NTQ][4];
+      // ------------------------------------------- S^T = K Q^T, one fp32 partial sum per group
+      // A scale belongs to a (token, group) pair.  The nibbles go into the MMAs as they are (exact in f16), the
+      // products of every group are accumulated on their own and take their scale in fp32 afterwards, so that
+      // nothing of K is rounded before the scores exist.  The words of iteration i (4i .. 4i+3, one per thread
+      // of a quad) lie in one group when a group has at least four words; with two-word groups words c < 2 and
+      // c >= 2 belong to different groups and each takes its own pair of MMAs, the other threads feeding zeros.
+      float sc0[NTQ][2], sc1[NTQ][2];
 #pragma unroll
-      for (int nt = 0; nt < NTQ; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-        s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
-      }
+      for (int nt = 0; nt < NTQ; ++nt) sc0[nt][0] = sc0[nt][1] = sc1[nt][0] = sc1[nt][1] = 0.f;
+      auto unpack4 = [](uint32_t x, uint32_t (&out)[4]) {
+        constexpr uint32_t kMagic = 0x64006400u;
+        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+        const __half2 k64 = __half2half2(__ushort_as_half(0x5400));
+        const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));
+        const uint32_t hi = x >> 8;
+        uint32_t v0 = (x & 0x000F000Fu) | kMagic, v1 = (x & 0x00F000F0u) | kMagic;
+        uint32_t v2 = (hi & 0x000F000Fu) | kMagic, v3 = (hi & 0x00F000F0u) | kMagic;
+        __half2 h0 = __hsub2(*reinterpret_cast<__half2*>(&v0), k1024);
+        __half2 h1 = __hfma2(*reinterpret_cast<__half2*>(&v1), k16th, __hneg2(k64));
+        __half2 h2 = __hsub2(*reinterpret_cast<__half2*>(&v2), k1024);
+        __half2 h3 = __hfma2(*reinterpret_cast<__half2*>(&v3), k16th, __hneg2(k64));
+        out[0] = *reinterpret_cast<uint32_t*>(&h0);
+        out[1] = *reinterpret_cast<uint32_t*>(&h1);
+        out[2] = *reinterpret_cast<uint32_t*>(&h2);
+        out[3] = *reinterpret_cast<uint32_t*>(&h3);
+      };
+      auto add_group = [&](const float (&s)[NTQ][4], const float (&s2)[NTQ][4], int g) {
+        const float ksc0 = half_bits_to_float(k0[g] & 0xFFFFu), ksc1 = half_bits_to_float(k0[8 * rw + g] & 0xFFFFu);
 #pragma unroll
-      for (int i = 0; i < KS / 2; ++i) {
-        const int g = (4 * i + c) / GW;  // group of word 4i + c
-        const __half2 m0 = __half2half2(scale_of(k0[g])), m1 = __half2half2(scale_of(k0[8 * rw + g]));
-        uint32_t u0[4], u1[4];
-        unpack4s(k0[NG + 4 * i + c], m0, u0);
-        unpack4s(k0[8 * rw + NG + 4 * i + c], m1, u1);
-        const uint32_t ka[4] = {u0[0], u1[0], u0[1], u1[1]};
-        const uint32_t kb[4] = {u0[2], u1[2], u0[3], u1[3]};
+        for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
-        for (int nt = 0; nt < NTQ; ++nt) {
-          mma_16816<false>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
-          mma_16816<false>(s2[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+          for (int e = 0; e < 2; ++e) {
+            sc0[nt][e] = fmaf(ksc0, s[nt][e] + s2[nt][e], sc0[nt][e]);
+            sc1[nt][e] = fmaf(ksc1, s[nt][2 + e] + s2[nt][2 + e], sc1[nt][e]);
+          }
+      };
+      if constexpr (GW % 4 == 0) {
+        constexpr int IPG = GW / 4;  // iterations (four words each) per group
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          float s[NTQ][4], s2[NTQ][4];
+#pragma unroll
+          for (int nt = 0; nt < NTQ; ++nt) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+            s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+          }
+#pragma unroll
+          for (int ii = 0; ii < IPG; ++ii) {
+            const int i = g * IPG + ii;
+            uint32_t u0[4], u1[4];
+            unpack4(k0[NG + 4 * i + c], u0);
+            unpack4(k0[8 * rw + NG + 4 * i + c], u1);
+            const uint32_t ka[4] = {u0[0], u1[0], u0[1], u1[1]};
+            const uint32_t kb[4] = {u0[2], u1[2], u0[3], u1[3]};
+#pragma unroll
+            for (int nt = 0; nt < NTQ; ++nt) {
+              mma_16816<false>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
+              mma_16816<false>(s2[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+            }
+          }
+          add_group(s, s2, g);
+        }
+      } else {
+        static_assert(GW == 2, "groups of two words (16 elements) or of a multiple of four words");
+#pragma unroll
+        for (int i = 0; i < KS / 2; ++i) {
+          uint32_t u0[4], u1[4];
+          unpack4(k0[NG + 4 * i + c], u0);
+          unpack4(k0[8 * rw + NG + 4 * i + c], u1);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const bool mine = (c >> 1) == half;  // this thread's word belongs to group 2i + half
+            const uint32_t ka[4] = {mine ? u0[0] : 0u, mine ? u1[0] : 0u, mine ? u0[1] : 0u, mine ? u1[1] : 0u};
+            const uint32_t kb[4] = {mine ? u0[2] : 0u, mine ? u1[2] : 0u, mine ? u0[3] : 0u, mine ? u1[3] : 0u};
+            float s[NTQ][4], s2[NTQ][4];
+#pragma unroll
+            for (int nt = 0; nt < NTQ; ++nt) {
+              s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+              s2[nt][0] = s2[nt][1] = s2[nt][2] = s2[nt][3] = 0.f;
+              mma_16816<false>(s[nt], ka, qf[nt][2 * i][0], qf[nt][2 * i][1]);
+              mma_16816<false>(s2[nt], kb, qf[nt][2 * i + 1][0], qf[nt][2 * i + 1][1]);
+            }
+            add_group(s, s2, 2 * i + half);
+          }
         }
       }
       // shifts of K: one term per group
-      float sc0[NTQ][2], sc1[NTQ][2];
-#pragma unroll
-      for (int nt = 0; nt < NTQ; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          sc0[nt][e] = s[nt][e] + s2[nt][e];
-          sc1[nt][e] = s[nt][2 + e] + s2[nt][2 + e];
-        }
 #pragma unroll
       for (int g = 0; g < NG; ++g) {
         const float ksh0 = half_bits_to_float(k0[g] >> 16), ksh1 = half_bits_to_float(k0[8 * rw + g] >> 16);
@@ -1123,9 +1182,11 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
     const uint8_t* kst = w.stage_base + st * w.stage_bytes;
     const uint8_t* vst = kst + w.kv_bytes;
     // scale/shift words: [head][token] after the 4-byte copies, [token][head][4 words] after the tiled ones
-    const uint32_t* ssk = reinterpret_cast<const uint32_t*>(kst + 2 * w.kv_bytes) + (a.ss_tma ? hw * 4 : hw * w.tok_per_stage);
+    // scale/shift words of a stage: [token][head][4 words] (tiled copies of replicated words), [token][head]
+    // (tiled copies of compact words) or [head][token] (4-byte copies)
+    const uint32_t* ssk = reinterpret_cast<const uint32_t*>(kst + 2 * w.kv_bytes) + (a.ss_tma == 1 ? hw * 4 : a.ss_tma == 2 ? hw : hw * w.tok_per_stage);
     const uint32_t* ssv = ssk + a.ss_bytes / 4;
-    const int ss_step = a.ss_tma ? hb * 4 : 1;  // words from one token to the next
+    const int ss_step = a.ss_tma == 1 ? hb * 4 : a.ss_tma == 2 ? hb : 1;  // words from one token to the next
 #pragma unroll 1
     for (int sp = 0; sp < kSps; ++sp) {
       const int usub = w.sub + w.wph * sp;                                // this warp's sub-tile of the stage
@@ -1430,7 +1491,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
           const int nbox = (nvalid + a.box_tok - 1) / a.box_tok;
           const uint32_t box_bytes = uint32_t(a.box_tok) * hb * kHeadBytes;
           const bool ss_tma = kFp8 && a.ss_tma;
-          const uint32_t box_ss = uint32_t(a.box_tok) * hb * 16u;  // 16 bytes per (token, head)
+          const uint32_t box_ss = uint32_t(a.box_tok) * hb * (a.ss_tma == 2 ? 4u : 16u);  // per (token, head): the word, or the word and three replicas
           mbar_expect_tx(&full_bar[st], uint32_t(nbox) * (box_bytes + (ss_tma ? box_ss : 0u)) * 2u);
           for (int bx = 0; bx < nbox; ++bx) {
             const int64_t row = row_of(t0 + bx * a.box_tok);
@@ -1440,8 +1501,13 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
             tma_load_3d(vs + bx * box_bytes, &a.tm_v, &full_bar[st], 0, int(row), c2);
             if (ss_tma) {
               uint8_t* ss = ks + 2 * kv_bytes;
-              tma_load_3d(ss + bx * box_ss, &a.tm_kss, &full_bar[st], 0, head0, int(row));
-              tma_load_3d(ss + a.ss_bytes + bx * box_ss, &a.tm_vss, &full_bar[st], 0, head0, int(row));
+              if (a.ss_tma == 2) {  // compact: {kv heads, token rows}
+                tma_load_3d(ss + bx * box_ss, &a.tm_kss, &full_bar[st], head0, int(row), 0);
+                tma_load_3d(ss + a.ss_bytes + bx * box_ss, &a.tm_vss, &full_bar[st], head0, int(row), 0);
+              } else {  // {4 words, kv heads, token rows}
+                tma_load_3d(ss + bx * box_ss, &a.tm_kss, &full_bar[st], 0, head0, int(row));
+                tma_load_3d(ss + a.ss_bytes + bx * box_ss, &a.tm_vss, &full_bar[st], 0, head0, int(row));
+              }
             }
           }
         }
@@ -1686,7 +1752,7 @@ static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t
   const int kv_bytes = kFmt == kFmtFp8      ? Stage::tokens(a_in.hb) * a_in.hb * D
                        : a_in.copy_mode == 3 ? Stage::tokens(a_in.hb) * a_in.hb * D * 2
                                              : Stage::kv_bytes(a_in.hb);
-  const int ss_bytes = Stage::ss_bytes(a_in.hb) * (a_in.ss_tma ? 4 : 1);
+  const int ss_bytes = Stage::ss_bytes(a_in.hb) * (a_in.ss_tma == 1 ? 4 : 1);  // 16 bytes per entry when the replicas come along
   const size_t stage_bytes = 2 * size_t(kv_bytes) + 2 * size_t(ss_bytes);
   const size_t qbytes = size_t(kDecConsumerWarps) * ROWS * (D * 2);
   const size_t cmb = size_t(kDecConsumerWarps) * ROWS * (D + 2) * 4;
@@ -1929,6 +1995,30 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
       const CUresult rv = enc(&a.tm_vss, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(a.v_ss), dims, vs, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
       if (rk == CUDA_SUCCESS && rv == CUDA_SUCCESS) a.ss_tma = 1;
+    }
+  }
+  if (fp8 && a.copy_mode == 3 && a.ss_tma == 0 && hb >= 4) {
+    // Compact scale/shift tensors: one word per (token, kv head), the heads of a token adjacent (a [rows, kv
+    // heads] tensor, or the same expanded over the query heads with stride 0).  The words of the hb heads of a
+    // run of tokens then come by one tiled copy of hb * 4 >= 16 bytes per token: no byte of a replica is read.
+    auto compact = [&](const void* ptr, int64_t m, int64_t g) {
+      return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && g == 1 && m % 4 == 0 && m >= p->kv_heads;
+    };
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc != nullptr && compact(a.k_ss, a.kss_m, a.kss_g) && compact(a.v_ss, a.vss_m, a.vss_g)) {
+      const cuuint64_t rows = p->kv_rows > 0              ? cuuint64_t(p->kv_rows)
+                              : p->block_tables != nullptr ? (cuuint64_t(1) << 31)
+                                                           : cuuint64_t(p->batch) * p->kv_padding;
+      const cuuint64_t dims[3] = {cuuint64_t(p->kv_heads), rows, 1};
+      const cuuint32_t bx[3] = {cuuint32_t(hb), cuuint32_t(a.box_tok), 1};
+      const cuuint32_t estr[3] = {1, 1, 1};
+      const cuuint64_t ks[2] = {cuuint64_t(a.kss_m) * 4, cuuint64_t(a.kss_m) * 4 * rows};
+      const cuuint64_t vs[2] = {cuuint64_t(a.vss_m) * 4, cuuint64_t(a.vss_m) * 4 * rows};
+      const CUresult rk = enc(&a.tm_kss, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(a.k_ss), dims, ks, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      const CUresult rv = enc(&a.tm_vss, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(a.v_ss), dims, vs, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (rk == CUDA_SUCCESS && rv == CUDA_SUCCESS) a.ss_tma = 2;
     }
   }
 
