@@ -405,6 +405,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the operators")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    # stdout carries the one JSON line: whatever a library prints there meanwhile (NCCL's version banner) goes to stderr
+    json_out = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     legs = set(args.only.split(",")) if args.only else {"prefill", "e2e", "decode_bf16", "decode_int4", "decode_fp8", "rope", "varlen", "long", "cpu"}
@@ -667,22 +670,30 @@ def main():
         lk_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
         lv_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
         lflops = 4.0 * S * S * D * Hkv * G / 2.0
+        hp_group = None
+        sm_margin = int(os.environ.get("XFB200_BENCH_SM_MARGIN", "8"))
+        n_str_default = int(os.environ.get("XFB200_BENCH_STRIPES", "8"))
+        if world > 1:
+            from xformers_b200.ops.fmha.sharded import exchange_group
 
-        def long_leg(spans, exchange, stripes, l_steps, l_warm):
+            hp_group = exchange_group(max_ctas=sm_margin)
+
+        def long_leg(spans, exchange, stripes, l_steps, l_warm, group, sm_margin):
             lk = [lk_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
             lv = [lv_full[:, a:b].expand(-1, -1, -1, G, -1) for a, b in spans]
             res = {}
 
             def fn():
                 res["out"], res["lse"] = sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True,
-                                                                      exchange=exchange, stripes=stripes)
+                                                                      exchange=exchange, stripes=stripes, group=group, sm_margin=sm_margin)
 
             ms, win = event_time_ms(fn, l_steps, l_warm, barrier)
             windows.append(win)
             ms = max_over_ranks(ms) / l_steps
             # break-down of one more step: attention of this rank's keys / what the exchange adds after it
             tm = {}
-            sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True, exchange=exchange, stripes=stripes, timings=tm)
+            sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True, exchange=exchange, stripes=stripes, timings=tm,
+                                         group=group, sm_margin=sm_margin)
             torch.cuda.synchronize()
             att = max_over_ranks(tm["start"].elapsed_time(tm["attention_done"]))
             tot = max_over_ranks(tm["start"].elapsed_time(tm["done"]))
@@ -706,11 +717,11 @@ def main():
 
         l_steps, l_warm = (10, 2) if not args.small else (3, 1)
         spans = zigzag_bounds(S, world, rank) if world > 1 else [(0, S)]
-        n_str = 8 if world > 1 else 1
-        ms, brk, par = long_leg(spans, "all_to_all", n_str, l_steps, l_warm)
+        n_str = n_str_default if world > 1 else 1
+        ms, brk, par = long_leg(spans, "all_to_all", n_str, l_steps, l_warm, hp_group, sm_margin if world > 1 else 0)
         lt = lflops / (ms * 1e-3) / 1e12
         out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms, "steps": l_steps, "warmup": l_warm, "scaling": "strong",
-                                    "ideal_speedup": float(world), "breakdown": brk, "parity": par, "query_stripes": n_str,
+                                    "ideal_speedup": float(world), "breakdown": brk, "parity": par, "query_stripes": n_str, "sm_margin": sm_margin if world > 1 else 0,
                                     "workload": f"1 x {S} causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work) covered by one launch per query stripe; per stripe NCCL all-to-all of the fp32 partials by query slice, LSE merge of the slice, all-gather of the merged slices, on a side stream behind the next stripe's attention"}
         launches += (l_steps + l_warm + 1) * n_str
         if world > 1:
@@ -718,7 +729,7 @@ def main():
             from xformers_b200.ops.fmha.sharded import shard_bounds
 
             c_steps, c_warm = (5, 1)
-            ms, brk, par = long_leg([shard_bounds(S, world, rank)], "all_gather", 1, c_steps, c_warm)
+            ms, brk, par = long_leg([shard_bounds(S, world, rank)], "all_gather", 1, c_steps, c_warm, None, 0)
             ct = lflops / (ms * 1e-3) / 1e12
             r2 = world * world / (2.0 * world - 1.0)
             out_line["long_context_contiguous"] = {"value": ct, "unit": UNIT, "ms_per_step": ms, "steps": c_steps, "warmup": c_warm, "scaling": "strong",
@@ -737,7 +748,8 @@ def main():
                 "sample": f"B={CPU_SAMPLE['B']} x H={CPU_SAMPLE['H']} heads of the headline configuration, best of {len(times)} runs (median {statistics.median(times):.3f} s); fp32 oracle",
             }
         out_line["gpu_launches_all_legs"] = launches
-        print(json.dumps(out_line), flush=True)
+        json_out.write(json.dumps(out_line) + "\n")
+        json_out.flush()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -139,6 +139,11 @@ typedef struct {
    * 128; 0 = one range.  Dense inputs, XFB200_MASK_CAUSAL_TOP_LEFT, no window; tcgen05 path. */
   int32_t kv_split;
   int32_t kv_offset2;
+  /* The persistent tcgen05 kernel occupies every SM it is given for as long as it runs.  sm_margin > 0
+   * leaves that many SMs free, for kernels of other streams that are meant to run beside it (the
+   * collectives that exchange one stripe of a sharded sequence while the next one is computed). */
+  int32_t sm_margin;
+  int32_t reserved;
 } xfb200_prefill_params;
 
 XFB200_API int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stream);

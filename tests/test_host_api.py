@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol():
 def test_struct_sizes_match_header():
     # sizes computed by hand from include/xfb200.h (LP64)
     assert ctypes.sizeof(_lib.Strides) == 32
-    assert ctypes.sizeof(_lib.PrefillParams) == 8 * 8 + 8 * 4 + 4 * 32 + 3 * 8 + 6 * 4 + 8 + 2 * 4 + 4 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.PrefillParams) == 8 * 8 + 8 * 4 + 4 * 32 + 3 * 8 + 6 * 4 + 8 + 2 * 4 + 4 * 8 + 6 * 4
     assert ctypes.sizeof(_lib.DecodeParams) == 8 * 8 + 12 * 4 + 12 * 8 + 4 * 4 + 2 * 8 + 4 * 8 + 8 + 8 + 2 * 4
     assert ctypes.sizeof(_lib.MergeParams) == 16 + 8 + 16 + 32 + 24 + 16 + 32 + 24 + 8 * 4
 

@@ -87,6 +87,8 @@ class PrefillParams(C.Structure):
         ("debug_flags", C.c_int32),
         ("kv_split", C.c_int32),
         ("kv_offset2", C.c_int32),
+        ("sm_margin", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 

@@ -26,6 +26,7 @@ struct Sm100Args {
   // two key ranges in one tensor (persistent kernel, dense causal only): rows [0, kv_split) of k/v start at global key
   // kv_offset, rows from kv_split on at kv_offset2; 0 = one range
   int32_t kv_split, kv_offset2;
+  int32_t sm_margin;  // persistent kernel: SMs left free for kernels of other streams
   int32_t out_dtype;
   float scale_log2;
   int32_t q_tiles;  // blocks of 256 query rows per sequence (static bound)

@@ -94,6 +94,7 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   a.kv_offset = p->kv_offset, a.window_left = p->window_left, a.out_dtype = p->out_dtype;
   a.window_right = p->mask_type == XFB200_MASK_NONE ? -1 : p->mask_type == XFB200_MASK_LOCAL_BOTTOM_RIGHT ? p->window_right : 0;
   a.kv_split = p->kv_split, a.kv_offset2 = p->kv_offset2;
+  a.sm_margin = p->sm_margin > 0 ? p->sm_margin : 0;
   a.scale_log2 = p->scale * 1.4426950408889634f;
   a.q_tiles = (p->mq + 255) / 256;
   a.debug_flags = p->debug_flags;

@@ -1020,7 +1020,8 @@ static int launch_t(const Sm100Args& a, cudaStream_t stream) {
   }
   const int64_t items = int64_t(a.groups) * a.heads_per_group * a.batch * a.q_tiles;
   if (items > 0x3fffffff) return set_error(XFB200_E_UNSUPPORTED, "prefill: too many blocks of query rows");
-  const int sms = sm_count();
+  int sms = sm_count() - a.sm_margin;
+  if (sms < 1) sms = 1;
   const unsigned grid = unsigned(items < sms ? items : sms);
   kern<<<grid, kThreads, smem, stream>>>(a);
   return check_launch("prefill_sm100_persist_kernel");

@@ -206,10 +206,12 @@ class FwOp(AttentionFwOpBase):
         return cls._apply(inp, needs_gradient or inp.is_partial, kv_offset=0)
 
     @classmethod
-    def _apply(cls, inp: Inputs, want_lse: bool, kv_offset: int = 0, kv_split: int = 0, kv_offset2: int = 0) -> Tuple[torch.Tensor, Optional[Context]]:
+    def _apply(cls, inp: Inputs, want_lse: bool, kv_offset: int = 0, kv_split: int = 0, kv_offset2: int = 0,
+               sm_margin: int = 0) -> Tuple[torch.Tensor, Optional[Context]]:
         """``kv_offset``: global index of the first key (causal masks of a sharded key axis).  ``kv_split`` /
         ``kv_offset2``: the key tensor holds two ranges back to back, the second one (rows from ``kv_split`` on)
-        starting at global key ``kv_offset2``."""
+        starting at global key ``kv_offset2``.  ``sm_margin``: SMs the persistent kernel leaves free for kernels
+        of other streams."""
         if cls.OPERATOR is None:
             raise RuntimeError("libxfb200.so is not built; there is no fallback")
         q, k, v = inp.get_qkv_in_bmghk()
@@ -258,7 +260,7 @@ class FwOp(AttentionFwOpBase):
                     p.bias_stride_b, p.bias_stride_g, p.bias_stride_h, p.bias_stride_m = b5.stride(0), b5.stride(1), b5.stride(2), b5.stride(3)
                 p.mask_type, p.kv_offset, p.window_left, p.window_right = mask_type, kv_offset, window_left, window_right
                 p.scale = inp.scale_float
-                p.kv_split, p.kv_offset2 = kv_split, kv_offset2
+                p.kv_split, p.kv_offset2, p.sm_margin = kv_split, kv_offset2, sm_margin
                 p.kernel_path = cls.KERNEL_PATH
                 p.wait_budget_kcycles, p.debug_flags = cls._WAIT_BUDGET_KCYCLES, cls._DEBUG_FLAGS
                 lib = _lib.load()

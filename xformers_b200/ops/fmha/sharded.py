@@ -56,7 +56,7 @@ def zigzag_bounds(total: int, world_size: int, rank: int) -> List[Tuple[int, int
     return [span(rank), span(2 * world_size - 1 - rank)]
 
 
-def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype, kv_split: int = 0, kv_offset2: int = 0):
+def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype, kv_split: int = 0, kv_offset2: int = 0, sm_margin: int = 0):
     from . import b200
 
     inp = Inputs(q, k, v, LowerTriangularMask() if causal else None, scale=scale, output_dtype=partial_dtype, is_partial=True)
@@ -64,7 +64,7 @@ def _partial_on_gpu(q, k, v, causal: bool, kv_offset: int, scale, partial_dtype,
     reasons = b200.FwOp.not_supported_reasons(inp)
     if reasons:
         raise ValueError("sharded attention: " + "; ".join(reasons))
-    out, ctx = b200.FwOp._apply(inp, want_lse=True, kv_offset=kv_offset if causal else 0, kv_split=kv_split, kv_offset2=kv_offset2)
+    out, ctx = b200.FwOp._apply(inp, want_lse=True, kv_offset=kv_offset if causal else 0, kv_split=kv_split, kv_offset2=kv_offset2, sm_margin=sm_margin)
     return out, ctx.lse
 
 
@@ -83,13 +83,24 @@ def _cat_keeping_broadcast(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return torch.cat([a, b], dim=1)
 
 
+def exchange_group(ranks=None, max_ctas: int = 8):
+    """A process group over ``ranks`` (default: all) for the striped exchange: its NCCL kernels use at most
+    ``max_ctas`` CTAs, which fit the SMs the attention kernel leaves free (``sm_margin``), and run on a
+    high-priority stream."""
+    opts = dist.ProcessGroupNCCL.Options()
+    opts.is_high_priority_stream = True
+    opts.config.max_ctas = int(max_ctas)
+    opts.config.min_ctas = 1
+    return dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
+
+
 _COMM_STREAMS: Dict[int, "torch.cuda.Stream"] = {}
 
 
 def _comm_stream(device: torch.device):
     idx = device.index if device.index is not None else torch.cuda.current_device()
     if idx not in _COMM_STREAMS:
-        _COMM_STREAMS[idx] = torch.cuda.Stream(device=device)
+        _COMM_STREAMS[idx] = torch.cuda.Stream(device=device, priority=-1)
     return _COMM_STREAMS[idx]
 
 
@@ -107,6 +118,7 @@ def sharded_kv_attention_forward(
     merge_fn: Callable = _merge_on_gpu,
     exchange: str = "all_to_all",
     stripes: int = 1,
+    sm_margin: int = 0,
     timings: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
@@ -126,6 +138,12 @@ def sharded_kv_attention_forward(
 
     ``partial_fn`` / ``merge_fn`` exist so that the exchange logic can be
     exercised with CPU stand-ins under the gloo backend.
+
+    The attention kernel is persistent: it holds every SM it is given until it
+    ends, and the next stripe's kernel is queued right behind it, so a collective
+    of another stream would find no SM before the last stripe is done.  With
+    stripes, pass ``sm_margin`` (SMs the attention leaves free) and a ``group``
+    whose NCCL kernels fit into them (:func:`exchange_group`).
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if isinstance(key_shard, torch.Tensor):
@@ -143,13 +161,16 @@ def sharded_kv_attention_forward(
         (k0, v0, o0), (k1, v1, o1) = ranges
         fused = (_cat_keeping_broadcast(k0, k1), _cat_keeping_broadcast(v0, v1), k0.shape[1], o0, o1)
 
+    margin = 0  # set below, once it is known whether an exchange runs beside the attention
+
     def local_partial(a: int, b: int):
         """(out, lse) of this rank's keys for the query rows [a, b)."""
         q = query[:, a:b]
         if fused is not None:
             kc, vc, split, o0, o1 = fused
-            return partial_fn(q, kc, vc, True, o0 - a, scale, partial_dtype, kv_split=split, kv_offset2=o1 - a)
-        parts = [partial_fn(q, k, v, causal, off - a, scale, partial_dtype) for k, v, off in ranges]
+            return partial_fn(q, kc, vc, True, o0 - a, scale, partial_dtype, kv_split=split, kv_offset2=o1 - a, sm_margin=margin)
+        extra = {"sm_margin": margin} if (margin and partial_fn is _partial_on_gpu) else {}
+        parts = [partial_fn(q, k, v, causal, off - a, scale, partial_dtype, **extra) for k, v, off in ranges]
         if not parts:
             # this rank holds no keys at all: a partial of weight 0, shaped like a neighbour's (one key, then discarded)
             k0, v0 = key_shard[0], value_shard[0]
@@ -177,6 +198,7 @@ def sharded_kv_attention_forward(
     n_stripes = max(1, int(stripes)) if (use_a2a and on_gpu) else 1
     while n_stripes > 1 and (mq % n_stripes or (mq // n_stripes) % world):
         n_stripes -= 1
+    margin = int(sm_margin) if n_stripes > 1 else 0
 
     if not use_a2a:
         out_r, lse_r = local_partial(0, mq)
