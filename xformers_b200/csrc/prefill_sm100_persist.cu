@@ -25,30 +25,32 @@
 //   warp 15      idle
 //
 // Tensor memory (all 512 columns): S0 | S1 | O0 | O1, fp32.  The probabilities
-// P_t overwrite the first 64 columns of S_t as packed 16-bit pairs and feed the
-// PV product straight from tensor memory.  tcgen05 operations issued by one
+// P_t overwrite the last 64 columns of S_t as packed 16-bit pairs (keys 64-127
+// in columns 64-95, keys 0-63 in columns 96-127) and feed the PV product
+// straight from tensor memory.  tcgen05 operations issued by one
 // thread complete in order: when the barrier of QK(t, j) fires, PV(t, j-1) has
 // finished, so the softmax may rescale O_t and overwrite S_t / P_t without
 // further hand-shakes; across items the first PV of a tile waits until the
 // output warps have read the previous O_t out of tensor memory.
 //
-// Softmax: thread = row; a step is one pass over its 128 scores, 32 columns (a
-// chunk) at a time: out of tensor memory, masked (diagonal and ragged tiles
-// only), turned into probabilities against the row's reference maximum and
-// stored back as P at once.  The reference maximum is the running one of the
-// previous steps (the first chunk gives it for a fresh row); when a step's
-// maximum exceeds it by more than 2^8 the row is re-based at the start of the
-// next step, when O_t may be touched again.  Only a score more than 2^14 above
-// the reference -- its probability would leave the 16-bit range -- stops the
-// pass: the rest of the row is then scanned for its true maximum and what was
-// already stored is rescaled (rare, and exact either way).  The chunk body
-// exists once and runs four times per step.  Measured alternatives (all within
-// a few percent, none better on the causal 4k case): the whole row in registers
-// as in the one-CTA-per-block kernel; two passes over tensor memory (maximum,
-// then probabilities); the next chunk's load in flight behind the current one;
-// part of the exponentials as a cubic on the FMA pipe (slower at every
-// fraction).  The exponential unit, shared by the two tiles' warps of a
-// scheduler, and in-order issue of a warp that runs almost alone set the pace.
+// Softmax: thread = row.  A step reads the row's 128 scores out of tensor memory
+// twice.  First for their maximum: if it exceeds the row's reference maximum by
+// more than 2^8 the row is re-based at once (O_t is quiescent at that point, see
+// above), otherwise the reference stays and nothing is rescaled -- one vote and
+// one rarely taken branch per step.  Then for the probabilities, which are stored
+// back as P chunk by chunk.  The second pass starts with the two chunks (of 32
+// columns) the first one ended with, straight from registers, and P goes into
+// columns 64-127 in the order in which it is produced (keys 64-127 first), so
+// that only the first 64 columns are read a second time and their loads fly
+// behind the exponentials of the other half.  A warp runs almost alone on its
+// scheduler: every vote, branch or wait it executes is a bubble nobody fills, so
+// the step has no loop and no per-chunk test.  On diagonal and ragged tiles a
+// small loop first writes -inf over the hidden scores in tensor memory; the step
+// itself is one piece of code for every tile, which the instruction cache likes.  Measured
+// alternatives on the causal 4k case: one pass with a stale reference, a vote per
+// chunk and a fix-up path (10 % slower: the votes and branches); the whole row in
+// registers as in the one-CTA-per-block kernel; two threads per row; part of the
+// exponentials as a cubic on the FMA pipe (slower at every fraction).
 //
 // Masks are index arithmetic on (row, key) positions; K/V heads of a GQA group
 // are indexed, never expanded; V rows past a sequence's end are zeroed in
@@ -87,8 +89,7 @@ constexpr int kItemReaders = 14;  // warps that read every announced item (all b
 #endif
 constexpr int kRegsLaunch = 128, kRegsSoftmax = XFB_PST_REGS_SOFTMAX, kRegsOut = XFB_PST_REGS_OUT, kRegsAux = XFB_PST_REGS_AUX;
 static_assert(8 * kRegsSoftmax + 4 * kRegsOut + 4 * kRegsAux <= 16 * kRegsLaunch, "setmaxnreg would ask for more registers than the CTA owns");
-constexpr float kRescaleThreshold = 8.0f;  // a row is re-based when its maximum grew by more than 2^8
-constexpr float kOverflowLimit = 14.0f;    // probabilities up to 2^14 against a stale maximum are fine in f16 and bf16
+constexpr float kRescaleThreshold = 8.0f;  // a row is re-based when its maximum grew by more than 2^8: probabilities stay below 2^8
 constexpr uint32_t kHalfBytes = 128 * 128;  // one 64-column block of a 128-row tile
 
 // Geometry of a work item, worked out once by the scheduler warp and read by the others from shared memory.
@@ -107,7 +108,7 @@ struct __align__(8) Barriers {
   uint64_t sched_full[kSched], sched_empty[kSched];
   uint64_t q_full[kTiles], q_empty[kTiles];
   uint64_t k_full[kStages], v_full[kStages], k_empty[kStages], v_empty[kStages];
-  uint64_t s_full[kTiles], p_full[kTiles];
+  uint64_t s_full[kTiles], p_half[kTiles], p_full[kTiles];  // p_half: the probabilities of keys 64-127 are stored
   uint64_t o_full[kTiles], o_empty[kTiles];
   uint64_t stats_full[kTiles], stats_empty[kTiles];
   uint64_t turn[kTiles];  // token of the tensor pipe: the two MMA warps issue their blocks alternately
@@ -284,6 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         mbar_init(&bar->q_full[t], 1);
         mbar_init(&bar->q_empty[t], 1);
         mbar_init(&bar->s_full[t], 1);
+        mbar_init(&bar->p_half[t], 128);
         mbar_init(&bar->p_full[t], 128);
         mbar_init(&bar->o_full[t], 1);
         mbar_init(&bar->o_empty[t], 128);
@@ -482,12 +484,15 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             umma_ss(tmem_s, desc(q_lo + off), desc(kl + off), idesc_qk, kk > 0);
           }
         };
-        auto issue_pv = [&](int v_stage, bool accumulate) {
+        // the part of P_t V_j over keys [16 kk_lo, 16 kk_hi) of the step; `accumulate` false: its first product overwrites O_t
+        auto issue_pv = [&](int v_stage, int kk_lo, int kk_hi, bool accumulate) {
           const uint32_t vl = v_lo0 + v_stage * (L::kKV >> 4);
 #pragma unroll
           for (int kk = 0; kk < kBN / 16; ++kk) {
+            if (kk < kk_lo || kk >= kk_hi) continue;
             // A = P_t: packed 16-bit pairs, 8 columns of tensor memory per 16 keys
-            umma_ts(tmem_o, tmem_s + kk * 8, desc(vl + ((kk * 16 * 128) >> 4)), idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+            // (the pairs of keys 0-63 sit in columns 96-127, those of keys 64-127 in columns 64-95)
+            umma_ts(tmem_o, tmem_s + (kk < 4 ? 96 + kk * 8 : 32 + kk * 8), desc(vl + ((kk * 16 * 128) >> 4)), idesc_pv, (accumulate || kk > kk_lo) ? 1u : 0u);
           }
         };
 
@@ -604,9 +609,16 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             }
             XFB_MPROF_LAP(4)  // wait for the token
             if (act) {
-              ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag, budget);
+              // The probabilities of keys 64-127 are stored first: their half of the product runs while the
+              // softmax is still busy with keys 0-63.
+              ok = mbar_wait(&bar->p_half[t], cnt & 1, abort_flag, budget);
               // the first PV of an item overwrites O_t: the output warps must have read the previous one
               if (ok && j == cur.jlo && kp > 0) ok = mbar_wait(&bar->o_empty[t], (kp - 1) & 1, abort_flag, budget);
+              if (ok) {
+                tc_fence_after();
+                if (lane == 0) issue_pv(vs, kBN / 32, kBN / 16, j > cur.jlo);
+                ok = mbar_wait(&bar->p_full[t], cnt & 1, abort_flag, budget);
+              }
               if (!ok) {
                 if (lane == 0) give_up(a, 23 + t);
                 break;
@@ -616,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             XFB_MPROF_LAP(3)  // V tail, wait for P (and for the output warps at the first PV of an item)
             if (lane == 0) {
               if (act) {
-                issue_pv(vs, j > cur.jlo);
+                issue_pv(vs, 0, kBN / 32, true);
                 if (j == cur.jhi - 1) tc_commit(&bar->o_full[t]);
               }
               tc_commit(&bar->v_empty[vs]);
@@ -774,11 +786,13 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
       // visibility of the 32 columns starting at key `col0` for this thread's row: hidden scores become -inf
       int col_lo = 0, col_hi = 0;
       auto mask_chunk = [&](float* sc, int col0) {
+        // one bit per column, then a test and a select per score
+        const int hr = col_hi - col0, lr = col_lo - col0;
+        const uint32_t below_hi = hr >= 32 ? 0xffffffffu : (hr <= 0 ? 0u : (1u << hr) - 1u);
+        const uint32_t from_lo = lr <= 0 ? 0xffffffffu : (lr >= 32 ? 0u : ~((1u << lr) - 1u));
+        const uint32_t vis = below_hi & from_lo;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const int col = col0 + c;
-          sc[c] = (col >= col_lo && col < col_hi) ? sc[c] : -INFINITY;
-        }
+        for (int c = 0; c < 32; ++c) sc[c] = (vis & (1u << c)) != 0u ? sc[c] : -INFINITY;
       };
       auto chunk_max = [](const float* sc) -> float {
         float m0 = fmax3(sc[0], sc[1], sc[2]), m1 = fmax3(sc[3], sc[4], sc[5]), m2 = fmax3(sc[6], sc[7], sc[8]), m3 = fmax3(sc[9], sc[10], sc[11]);
@@ -788,8 +802,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
       };
       // 32 score columns -> 16 packed probability pairs against the maximum -m (nm2 = (-m, -m)), summed into
-      // sum2 and stored to columns [16c, 16c + 16) of S_t
-      auto exp_store = [&](const float* sc, int c, uint64_t nm2, uint64_t (&sum2)[4]) {
+      // sum2 and stored to the 16 columns of S_t that start at `col`
+      auto exp_store = [&](const uint32_t* sr, int col, uint64_t nm2, uint64_t (&sum2)[4]) {
         uint32_t pr[16];
         // (blocks of 16 independent elements: all FMAs, then all exp2, then the sums and packs -- a lone warp per
         // scheduler hides no latency by switching warps, the instruction stream has to)
@@ -797,7 +811,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         for (int h = 0; h < 32; h += 16) {
           float e[16];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2) f2_unpack(ffma2(f2_pack(sc[h + i], sc[h + i + 1]), sc2, nm2), e[i], e[i + 1]);
+          for (int i = 0; i < 16; i += 2)
+            f2_unpack(ffma2(f2_pack(__uint_as_float(sr[h + i]), __uint_as_float(sr[h + i + 1])), sc2, nm2), e[i], e[i + 1]);
 #pragma unroll
           for (int i = 0; i < 16; ++i) e[i] = fast_exp2(e[i]);
 #pragma unroll
@@ -806,7 +821,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             pr[(h + i) / 2] = pack_pair<kBf16>(e[i], e[i + 1]);
           }
         }
-        XFB_TMEM_ST_16(tmem_s + c * 16, pr);
+        XFB_TMEM_ST_16(tmem_s + col, pr);
       };
       // O_t *= alpha (per row), through registers
       auto rescale_o = [&](float alpha) {
@@ -851,10 +866,9 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         const bool causal = a.window_right >= 0;
         col_hi = causal ? min(it.klen, i_loc + it.shift + a.window_right + 1) : it.klen;
         col_lo = a.window_left >= 0 ? i_loc + it.shift - a.window_left : 0;
-        // m_run: the maximum the probabilities and O_t are taken against (log2 units); m_pend: what it becomes
-        // at the start of the next step (a raise is applied one step late, when O_t may be touched again);
-        // l_run: the row sum against m_run
-        float m_run = -INFINITY, m_pend = -INFINITY, l_run = 0.f;
+        // m_run: the reference maximum the probabilities and O_t are taken against (log2 units; at most 2^8 below
+        // the true running maximum); l_run: the row sum against m_run
+        float m_run = -INFINITY, l_run = 0.f;
 
         XFB_PROF_LAP(0)  // between items: statistics hand-over, next descriptor
         for (int j = jlo; j < jhi; ++j, ++cnt) {
@@ -877,99 +891,82 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           tc_fence_after();
           const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + a.window_right) ||
                                  (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
-          {
-            // ---- a raise of the reference maximum that the previous step left pending.  QK(t,j) completing
-            // implies PV(t,j-1) completed: O_t is quiescent here.
-            if (j > jlo && __any_sync(0xffffffffu, m_pend != m_run)) {
-              const float alpha = m_pend == m_run ? 1.f : (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_pend));
-              rescale_o(alpha);
-              l_run *= alpha;
-              m_run = m_pend;
-            }
-            uint64_t sum2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
-            float step_max = -INFINITY;  // of the raw scores of this step (visible ones)
-            uint32_t sa[32];
-            int bad = -1;  // first chunk that could not be taken against the current maximum (warp-uniform)
-            // One pass, 32 score columns (a chunk) at a time: masked (diagonal and ragged tiles only), checked, turned
-            // into 16 packed probability pairs that go straight back to tensor memory.  P chunk c lands in columns
-            // [16c, 16c + 16), which held scores that are in registers by then.  One chunk body run four times: the
-            // code of a step stays small, which a scheduler that runs this warp almost alone rewards.
+          if (need_mask) {
+            // Diagonal and ragged tiles: hidden scores are turned into -inf where they lie, in tensor memory, by this
+            // small loop; the step itself then is the same code for every tile (one copy of it in the instruction
+            // cache).  The rows of a warp are consecutive and both limits grow with the row, so the limits of the
+            // first and the last row tell which chunks are fully visible to the warp (left alone) or fully hidden
+            // (overwritten without being read).
+            const int hi_first = __shfl_sync(0xffffffffu, col_hi, 0), hi_last = __shfl_sync(0xffffffffu, col_hi, 31);
+            const int lo_first = __shfl_sync(0xffffffffu, col_lo, 0), lo_last = __shfl_sync(0xffffffffu, col_lo, 31);
+            uint32_t sm[32];
 #pragma unroll 1
             for (int c = 0; c < kBN / 32; ++c) {
-              XFB_TMEM_LD_32(tmem_s + c * 32, sa);
-              XFB_TMEM_WAIT_LD_32(sa);
-              float* sc = reinterpret_cast<float*>(sa);
-              if (need_mask) mask_chunk(sc, n0 + c * 32);
-              const float cm = chunk_max(sc);
-              step_max = fmaxf(step_max, cm);
-              const float cms = cm * sl2;  // scale > 0 (host guarantees)
-              if (c == 0 && j == jlo) m_run = m_pend = cms;  // a fresh row: the first chunk gives the provisional maximum
-              // the probabilities of a chunk must stay finite in 16 bits: at most 2^kOverflowLimit against the reference
-              if (__any_sync(0xffffffffu, cms > m_run + kOverflowLimit)) {
-                bad = c;
-                break;
+              const int col0 = n0 + c * 32;
+              if (col0 >= lo_last && col0 + 32 <= hi_first) continue;  // every row of the warp sees the whole chunk
+              if (col0 >= hi_last || col0 + 32 <= lo_first) {
+                // no row of the warp sees any of it
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sm[i] = 0xff800000u;
+              } else {
+                XFB_TMEM_LD_32(tmem_s + c * 32, sm);
+                XFB_TMEM_WAIT_LD_32(sm);
+                mask_chunk(reinterpret_cast<float*>(sm), col0);
               }
-              const float m_use = m_run == -INFINITY ? 0.f : m_run;
-              exp_store(sc, c, f2_pack(-m_use, -m_use), sum2);
+              XFB_TMEM_ST_32(tmem_s + c * 32, sm);
+              tc_wait_st();  // (the registers are written again in the next round)
             }
-            if (bad < 0) {
-              // a row whose maximum grew by more than the threshold is re-based at the start of the next step
-              const float sm = step_max * sl2;
-              if (sm > m_run + kRescaleThreshold) m_pend = sm;
-            } else {
+            XFB_PROF_COUNT(5)
+            XFB_PROF_LAP(3)  // the visibility test
+          }
+          {
+            uint32_t sa[32], sb[32];
+            // ---- first pass: the maximum of the scores
+            XFB_TMEM_LD_32(tmem_s, sa);
+            XFB_TMEM_LD_32(tmem_s + 32, sb);
+            XFB_TMEM_WAIT_LD_32(sa);
+            XFB_TMEM_WAIT_LD_32(sb);
+            float mx = fmaxf(chunk_max(reinterpret_cast<float*>(sa)), chunk_max(reinterpret_cast<float*>(sb)));
+            XFB_TMEM_LD_32(tmem_s + 64, sa);
+            XFB_TMEM_LD_32(tmem_s + 96, sb);
+            XFB_TMEM_WAIT_LD_32(sa);
+            XFB_TMEM_WAIT_LD_32(sb);
+            mx = fmaxf(mx, fmaxf(chunk_max(reinterpret_cast<float*>(sa)), chunk_max(reinterpret_cast<float*>(sb))));
+            const float ms = mx * sl2;  // scale > 0 (host guarantees)
+            // ---- the reference follows the maximum only when it has to (a fresh row: from -inf).  QK(t,j) completing
+            // implies PV(t,j-1) completed: O_t is quiescent here.
+            if (__any_sync(0xffffffffu, ms > m_run + kRescaleThreshold)) {
               XFB_PROF_COUNT(7)
-              // ---- rare: some score of the warp's rows lies more than 2^kOverflowLimit above its reference maximum
-              // (or the row had no maximum yet).  Chunks below `bad` are stored against the old maximum, the scores
-              // of the others are still in tensor memory: find the true maximum of the rest, re-base everything.
-              float mxr = -INFINITY;
-              for (int c = bad; c < kBN / 32; ++c) {
-                XFB_TMEM_LD_32(tmem_s + c * 32, sa);
-                XFB_TMEM_WAIT_LD_32(sa);
-                float* sc = reinterpret_cast<float*>(sa);
-                if (need_mask) mask_chunk(sc, n0 + c * 32);
-                mxr = fmaxf(mxr, chunk_max(sc));
-              }
-              const float m_new = fmaxf(m_run, mxr * sl2);
+              const float m_new = ms > m_run + kRescaleThreshold ? ms : m_run;
               const float alpha = m_new == m_run ? 1.f : (m_run == -INFINITY ? 0.f : fast_exp2(m_run - m_new));
               if (j > jlo) rescale_o(alpha);
-              {
-                float x0, x1, y0, y1;
-                f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
-                f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
-                l_run = (l_run + ((x0 + x1) + (y0 + y1))) * alpha;
-                sum2[0] = sum2[1] = sum2[2] = sum2[3] = f2_pack(0.f, 0.f);
-              }
-              for (int c = 0; c < bad; ++c) {
-                uint32_t pq[16];
-                XFB_TMEM_LD_16(tmem_s + c * 16, pq);
-                tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  float lo, hi;
-                  unpack_pair<kBf16>(pq[i], lo, hi);
-                  pq[i] = pack_pair<kBf16>(lo * alpha, hi * alpha);
-                }
-                XFB_TMEM_ST_16(tmem_s + c * 16, pq);
-              }
-              m_run = m_pend = m_new;
-              const float m_use = m_run == -INFINITY ? 0.f : m_run;
-              for (int c = bad; c < kBN / 32; ++c) {
-                XFB_TMEM_LD_32(tmem_s + c * 32, sa);
-                XFB_TMEM_WAIT_LD_32(sa);
-                if (need_mask) mask_chunk(reinterpret_cast<float*>(sa), n0 + c * 32);
-                tc_wait_st();  // (the store of an earlier round of this loop has read the registers it was given)
-                exp_store(reinterpret_cast<float*>(sa), c, f2_pack(-m_use, -m_use), sum2);
-              }
+              l_run *= alpha;
+              m_run = m_new;
             }
-            XFB_PROF_COUNT(6)
+            // ---- second pass: probabilities.  Keys 64-127 are in registers; keys 0-63 come back behind them.
+            const float m_use = m_run == -INFINITY ? 0.f : m_run;
+            const uint64_t nm2 = f2_pack(-m_use, -m_use);
+            uint64_t sum2[4] = {f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f), f2_pack(0.f, 0.f)};
+            exp_store(sa, 64, nm2, sum2);
+            XFB_TMEM_LD_32(tmem_s, sa);
+            exp_store(sb, 80, nm2, sum2);
+            XFB_TMEM_LD_32(tmem_s + 32, sb);
+            tc_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bar->p_half[t]);
+            XFB_TMEM_WAIT_LD_32(sa);
+            XFB_TMEM_WAIT_LD_32(sb);
+            exp_store(sa, 96, nm2, sum2);
+            exp_store(sb, 112, nm2, sum2);
             {
               float x0, x1, y0, y1;
               f2_unpack(fadd2(sum2[0], sum2[1]), x0, x1);
               f2_unpack(fadd2(sum2[2], sum2[3]), y0, y1);
               l_run += (x0 + x1) + (y0 + y1);
             }
-            XFB_PROF_LAP(2)
           }
+          XFB_PROF_LAP(2)  // the step proper
+          XFB_PROF_COUNT(6)
           tc_wait_st();
           tc_fence_before();
           mbar_arrive(&bar->p_full[t]);
