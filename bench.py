@@ -63,7 +63,7 @@ CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch: constants taken from the ncu captures
 # summarised under profiles/ (a run of this script does not measure them): bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
-NCU_TRAFFIC = {"prefill": 139.34e6 + 14.16e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
+NCU_TRAFFIC = {"prefill": 142.10e6 + 14.86e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
                "decode_fp8": (505.73e6 + 12.46e6) / 505.51e6, "rope": (100.70e6 + 55.24e6) / 201.33e6}
 
 
