@@ -62,7 +62,7 @@ enum { XFB200_MASK_NONE = 0, XFB200_MASK_CAUSAL_TOP_LEFT = 1, XFB200_MASK_CAUSAL
 /* kernel_path of xfb200_prefill_params: which kernel may run the call. */
 enum {
   XFB200_PREFILL_AUTO = 0,        /* the fastest kernel that covers the input            */
-  XFB200_PREFILL_MMA_SYNC = 1,    /* the mma.sync kernel (every head dim, additive bias) */
+  XFB200_PREFILL_MMA_SYNC = 1,    /* the mma.sync kernel (every head dim) */
   XFB200_PREFILL_TCGEN05 = 2,     /* fail unless a tcgen05 kernel covers the input       */
   XFB200_PREFILL_TCGEN05_CTA = 4, /* tcgen05, one CTA per block of 256 query rows        */
   XFB200_PREFILL_TCGEN05_PERSISTENT = 6 /* tcgen05, one persistent CTA per SM            */
@@ -122,7 +122,8 @@ typedef struct {
    * fmha/attn_bias.py:43; tests/test_mem_eff_attention.py:1440-1449): NULL, or
    * [batch, G, H, mq, mkv] with unit stride on the last axis and element strides
    * below (0 = broadcast), added to q k^T * scale before the mask and the softmax.
-   * Dense batches only; runs on the mma.sync kernel. */
+   * Dense batches only; runs on the persistent tcgen05 kernel (head dim 64 / 128) or on
+   * the mma.sync kernel. */
   const void* bias;
   int32_t bias_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
   int32_t window_right; /* XFB200_MASK_LOCAL_BOTTOM_RIGHT: keys j <= i + shift + window_right (>= 0); else ignored */

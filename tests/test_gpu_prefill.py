@@ -360,11 +360,13 @@ def test_custom_stream_and_output_dtype():
 @pytest.mark.parametrize("bias_dtype", [None, torch.float32])
 @pytest.mark.parametrize("layout", ["BMHK", "BMGHK", "BMK"])
 @pytest.mark.parametrize("Mq,Mkv,D", [(64, 64, 64), (100, 300, 128), (257, 129, 32)])
-@pytest.mark.parametrize("op", [P.FwOp, P.FwOp_Generic])
+@pytest.mark.parametrize("op", [P.FwOp, P.FwOp_Generic, P.FwOp_Tcgen05_Persistent])
 def test_additive_tensor_bias(op, Mq, Mkv, D, layout, bias_dtype):
     """A plain tensor as attn_bias is added to q k^T * scale before the softmax
     (tests/test_mem_eff_attention.py:420-440, 664-682)."""
     require_cuda()
+    if op is P.FwOp_Tcgen05_Persistent and D not in (64, 128):
+        pytest.skip("tcgen05 kernels: head dim 64 or 128")
     dtype = torch.bfloat16
     g = torch.Generator().manual_seed(31)
     B, G, H = 2, 2, 3
@@ -400,7 +402,11 @@ def test_causal_with_tensor_bias(Mq, Mkv):
     out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=P.FwOp)
     ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), ab.LowerTriangularMaskWithTensorBias(t.float().cpu()))
     assert_o_lse(out, lse, ro, rl, dtype, "causal + tensor bias")
-    assert P.FwOp_Tcgen05.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    # head dim 64: the persistent tcgen05 kernel takes it (and is what the automatic choice ran); the other tcgen05 kernel does not
+    assert not P.FwOp_Tcgen05_Persistent.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    assert P.FwOp_Tcgen05_M256.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    out2, lse2 = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=P.FwOp_Generic)
+    assert_o_lse(out2, lse2, ro, rl, dtype, "causal + tensor bias, mma.sync kernel")
 
 
 @gpu

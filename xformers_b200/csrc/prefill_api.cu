@@ -53,8 +53,9 @@ extern "C" int xfb200_prefill_forward(const xfb200_prefill_params* p, void* stre
   }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // (the tcgen05 kernels take no additive bias)
-  const bool can100 = p->kernel_path != XFB200_PREFILL_MMA_SYNC && p->mkv > 0 && p->bias == nullptr && prefill_sm100_supported(p);
+  // (of the tcgen05 kernels only the persistent one takes an additive bias)
+  const bool can100 = p->kernel_path != XFB200_PREFILL_MMA_SYNC && p->mkv > 0 &&
+                      (p->bias == nullptr || p->kernel_path != XFB200_PREFILL_TCGEN05_CTA) && prefill_sm100_supported(p);
   if (p->kernel_path >= XFB200_PREFILL_TCGEN05 && !can100) return set_error(XFB200_E_UNSUPPORTED, "prefill: the tcgen05 kernel does not cover this input");
   if (can100) return prefill_sm100_launch(p, st);
   if (p->kv_split != 0) return set_error(XFB200_E_UNSUPPORTED, "prefill: two key ranges in one call need the tcgen05 kernel (head dim 64 or 128)");

@@ -33,6 +33,12 @@ struct Sm100Args {
   uint32_t epoch;   // differs from launch to launch, never 0
   int32_t debug_flags;
   long long wait_budget;  // SM clocks after which a wait gives up
+  // additive bias (persistent kernel, dense batches): element strides of [batch, G, H, mq, mkv], unit stride on mkv;
+  // the kernel adds bias / scale to q k^T, so that the softmax sees q k^T * scale + bias
+  const void* bias;
+  int32_t bias_dtype;
+  float inv_scale;
+  int64_t bias_b, bias_g, bias_h, bias_m;
 };
 
 // One CTA per block of 256 query rows (two 128-row tiles sharing every K/V tile), 128-key steps.

@@ -99,9 +99,12 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   a.q_tiles = (p->mq + 255) / 256;
   a.debug_flags = p->debug_flags;
   a.wait_budget = p->wait_budget_kcycles > 0 ? 1000LL * p->wait_budget_kcycles : kDefaultWaitBudgetCycles;
+  a.bias = p->bias, a.bias_dtype = p->bias_dtype, a.inv_scale = 1.f / p->scale;
+  a.bias_b = p->bias_stride_b, a.bias_g = p->bias_stride_g, a.bias_h = p->bias_stride_h, a.bias_m = p->bias_stride_m;
   const bool bf16 = p->dtype == XFB200_BF16;
   if (p->kernel_path == XFB200_PREFILL_TCGEN05_CTA) {
     if (p->kv_split > 0) return set_error(XFB200_E_UNSUPPORTED, "prefill: two key ranges in one call need the persistent kernel");
+    if (p->bias != nullptr) return set_error(XFB200_E_UNSUPPORTED, "prefill: an additive bias needs the persistent or the mma.sync kernel");
     return prefill_sm100_m256_launch(a, D, bf16, stream);
   }
   return prefill_sm100_persist_launch(a, D, bf16, stream);

@@ -845,12 +845,14 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
 
       while (ok) {
         struct {
-          int jlo, jhi, m0, shift, shift2, n_base, klen;
+          int jlo, jhi, m0, shift, shift2, n_base, klen, qlen;
+          int64_t bias_off;  // of the item's (batch, head) in the additive bias, in elements
         } it;
         const int idx = pop_item(seq, [&](const Item& d) {
           it.jlo = t == 0 ? d.jlo[0] : d.jlo[1];
           it.jhi = t == 0 ? d.jhi[0] : d.jhi[1];
-          it.m0 = d.m0, it.shift = d.shift, it.shift2 = d.shift2, it.n_base = d.n_base, it.klen = d.klen;
+          it.m0 = d.m0, it.shift = d.shift, it.shift2 = d.shift2, it.n_base = d.n_base, it.klen = d.klen, it.qlen = d.qlen;
+          it.bias_off = a.bias != nullptr ? int64_t(d.b) * a.bias_b + int64_t(d.g) * a.bias_g + int64_t(d.h) * a.bias_h : 0;
         });
         if (idx < 0) {
           if (idx == -2) {
@@ -866,6 +868,10 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         const bool causal = a.window_right >= 0;
         col_hi = causal ? min(it.klen, i_loc + it.shift + a.window_right + 1) : it.klen;
         col_lo = a.window_left >= 0 ? i_loc + it.shift - a.window_left : 0;
+        // this thread's row of the additive bias (dense batches only), or null
+        const uint8_t* bias_row = nullptr;
+        if (a.bias != nullptr && i_loc < it.qlen)
+          bias_row = reinterpret_cast<const uint8_t*>(a.bias) + (it.bias_off + int64_t(i_loc) * a.bias_m) * (a.bias_dtype == XFB200_F32 ? 4 : 2);
         // m_run: the reference maximum the probabilities and O_t are taken against (log2 units; at most 2^8 below
         // the true running maximum); l_run: the row sum against m_run
         float m_run = -INFINITY, l_run = 0.f;
@@ -891,6 +897,30 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           tc_fence_after();
           const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + a.window_right) ||
                                  (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
+          if (a.bias != nullptr) {  // (warp-uniform: the tensor-memory accesses below are warp-wide)
+            // An additive bias is folded into the scores where they lie (as bias / scale, so that the step's
+            // scale * log2 e applies to the sum); rows past the end of the queries and keys past the end of the
+            // keys are left alone (the former are never written, the latter are masked below).
+            uint32_t sm[32];
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+              const int col0 = n0 + c * 32;
+              XFB_TMEM_LD_32(tmem_s + c * 32, sm);
+              XFB_TMEM_WAIT_LD_32(sm);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                float bv = 0.f;
+                if (bias_row != nullptr && col0 + i < klen) {
+                  if (a.bias_dtype == XFB200_F32) bv = reinterpret_cast<const float*>(bias_row)[col0 + i];
+                  else if (a.bias_dtype == XFB200_BF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias_row)[col0 + i]);
+                  else bv = __half2float(reinterpret_cast<const __half*>(bias_row)[col0 + i]);
+                }
+                sm[i] = __float_as_uint(fmaf(bv, a.inv_scale, __uint_as_float(sm[i])));
+              }
+              XFB_TMEM_ST_32(tmem_s + c * 32, sm);
+              tc_wait_st();  // (the registers are written again in the next round)
+            }
+          }
           if (need_mask) {
             // Diagonal and ragged tiles: hidden scores are turned into -inf where they lie, in tensor memory, by this
             // small loop; the step itself then is the same code for every tile (one copy of it in the instruction

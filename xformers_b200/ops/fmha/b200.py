@@ -4,8 +4,8 @@ Slots into the dispatcher next to the reference's forward operators
 (``fmha.cutlass_blackwell.FwOp``, ``fmha.flash.FwOp``; registration record as
 tests/test_mem_eff_attention.py:104-111 reads it).  The arithmetic is done by
 ``xfb200_prefill_forward`` of libxfb200.so: a persistent TMA + tcgen05/TMEM
-kernel for head dims 64 and 128, an mma.sync kernel for the other head dims
-and for additive tensor biases.
+kernel for head dims 64 and 128 (every mask, additive tensor biases included),
+an mma.sync kernel for the other head dims.
 """
 
 from __future__ import annotations
@@ -197,8 +197,8 @@ class FwOp(AttentionFwOpBase):
                 reasons.append("additive bias needs unit stride on its last axis")
             if bt.dtype not in _DTYPE_CODE:
                 reasons.append(f"additive bias dtype {bt.dtype}")
-            if cls.KERNEL_PATH >= _lib.PREFILL_TCGEN05:
-                reasons.append("additive biases run on the mma.sync kernel only")
+            if cls.KERNEL_PATH == _lib.PREFILL_TCGEN05_CTA:
+                reasons.append("additive biases run on the persistent tcgen05 kernel or on the mma.sync kernel")
         return reasons
 
     @classmethod
