@@ -22,7 +22,7 @@ def _worker(rank, world, init_file, out_file):
     import oracle
     from xformers_b200.ops import fmha
     from xformers_b200.ops.fmha import attn_bias as ab
-    from xformers_b200.ops.fmha.sharded import shard_bounds, sharded_kv_attention_forward, zigzag_bounds
+    from xformers_b200.ops.fmha.sharded import exchange_group, shard_bounds, sharded_kv_attention_forward, zigzag_bounds
 
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
@@ -41,6 +41,8 @@ def _worker(rank, world, init_file, out_file):
                                                torch.stack([oracle.causal_mask(1, S, kv_offset=-r)[0] for r in rows]).expand(1, Hkv, G, len(rows), S))
         cases = [("zigzag a2a", zigzag_bounds(S, world, rank), dict(exchange="all_to_all", stripes=1)),
                  ("zigzag a2a 4 stripes", zigzag_bounds(S, world, rank), dict(exchange="all_to_all", stripes=4)),
+                 ("zigzag a2a 4 stripes, SMs left free, a narrow group and the default group for the last stripe", zigzag_bounds(S, world, rank),
+                  dict(exchange="all_to_all", stripes=4, sm_margin=8, group=exchange_group(max_ctas=8), last_group=dist.group.WORLD)),
                  ("zigzag gather", zigzag_bounds(S, world, rank), dict(exchange="all_gather")),
                  ("contiguous gather", [shard_bounds(S, world, rank)], dict(exchange="all_gather")),
                  ("contiguous a2a 2 stripes", [shard_bounds(S, world, rank)], dict(exchange="all_to_all", stripes=2))]

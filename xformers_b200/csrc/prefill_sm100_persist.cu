@@ -182,9 +182,9 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi) {
 }
 
 #ifdef XFB_PST_PROFILE
-// Timing build only: per-CTA cycle counters of the MMA issuers (slots 0-15 / 16-31) and of one softmax warp per
-// tile (32-47 / 48-63), read back with xfb200_debug_read_prefill_profile.
-__device__ long long g_prof[160][64];
+// Timing build only: per-CTA cycle counters of the softmax warps (8 slots each, 0-63) and, with
+// -DXFB_PST_PROFILE_MMA, of the two MMA issuers (64-79 / 80-95), read back with xfb200_debug_read_prefill_profile.
+__device__ long long g_prof[160][96];
 #define XFB_PROF_DECL(n) long long prof_acc[n] = {0}; long long prof_t = clock64();
 #define XFB_PROF_LAP(k) { const long long _n = clock64(); prof_acc[k] += _n - prof_t; prof_t = _n; }
 #define XFB_PROF_COUNT(k) { prof_acc[k] += 1; }
@@ -285,8 +285,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
         mbar_init(&bar->q_full[t], 1);
         mbar_init(&bar->q_empty[t], 1);
         mbar_init(&bar->s_full[t], 1);
-        mbar_init(&bar->p_half[t], 128);
-        mbar_init(&bar->p_full[t], 128);
+        mbar_init(&bar->p_half[t], 4);  // one arrival per softmax warp of the tile
+        mbar_init(&bar->p_full[t], 4);
         mbar_init(&bar->o_full[t], 1);
         mbar_init(&bar->o_empty[t], 128);
         mbar_init(&bar->stats_full[t], 128);
@@ -673,7 +673,7 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             ks = ks1, kph = kph1;
             if (++vs == kStages) vs = 0, vph ^= 1;
           }
-          XFB_MPROF_STORE(t * 16, 16)
+          XFB_MPROF_STORE(64 + t * 16, 16)
         }
         if (!ok) *abort_flag = 1;
       }
@@ -888,6 +888,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             n0 -= second ? a.kv_split : 0;
             col_hi = min(klen, i_loc + shift + 1);
           }
+          const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + a.window_right) ||
+                                 (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
           ok = mbar_wait(&bar->s_full[t], cnt & 1, abort_flag, budget);
           XFB_PROF_LAP(1)  // wait for the scores
           if (!ok) {
@@ -895,8 +897,6 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             break;
           }
           tc_fence_after();
-          const bool need_mask = (n0 + kBN > klen) || (causal && n0 + kBN - 1 > mt0 + shift + a.window_right) ||
-                                 (a.window_left >= 0 && n0 < mt0 + kBM - 1 + shift - a.window_left);
           if (a.bias != nullptr) {  // (warp-uniform: the tensor-memory accesses below are warp-wide)
             // An additive bias is folded into the scores where they lie (as bias / scale, so that the step's
             // scale * log2 e applies to the sum); rows past the end of the queries and keys past the end of the
@@ -983,7 +983,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             XFB_TMEM_LD_32(tmem_s + 32, sb);
             tc_wait_st();
             tc_fence_before();
-            mbar_arrive(&bar->p_half[t]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar->p_half[t]);
             XFB_TMEM_WAIT_LD_32(sa);
             XFB_TMEM_WAIT_LD_32(sb);
             exp_store(sa, 96, nm2, sum2);
@@ -999,7 +1000,8 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
           XFB_PROF_COUNT(6)
           tc_wait_st();
           tc_fence_before();
-          mbar_arrive(&bar->p_full[t]);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar->p_full[t]);
           XFB_PROF_LAP(4)  // storing P
         }
         if (!ok) break;
@@ -1059,9 +1061,9 @@ static int launch_t(const Sm100Args& a, cudaStream_t stream) {
 #ifdef XFB_PST_PROFILE
 extern "C" __attribute__((visibility("default"))) int xfb200_debug_read_prefill_profile(long long* out, int clear) {
   cudaDeviceSynchronize();
-  cudaError_t e = cudaMemcpyFromSymbol(out, pst::g_prof, sizeof(long long) * 160 * 64);
+  cudaError_t e = cudaMemcpyFromSymbol(out, pst::g_prof, sizeof(long long) * 160 * 96);
   if (e == cudaSuccess && clear) {
-    static long long zeros[160 * 64] = {0};
+    static long long zeros[160 * 96] = {0};
     e = cudaMemcpyToSymbol(pst::g_prof, zeros, sizeof(zeros));
   }
   return e == cudaSuccess ? 0 : -3;

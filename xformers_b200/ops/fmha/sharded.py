@@ -119,6 +119,7 @@ def sharded_kv_attention_forward(
     exchange: str = "all_to_all",
     stripes: int = 1,
     sm_margin: int = 0,
+    last_group: Optional[dist.ProcessGroup] = None,
     timings: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
@@ -143,7 +144,10 @@ def sharded_kv_attention_forward(
     ends, and the next stripe's kernel is queued right behind it, so a collective
     of another stream would find no SM before the last stripe is done.  With
     stripes, pass ``sm_margin`` (SMs the attention leaves free) and a ``group``
-    whose NCCL kernels fit into them (:func:`exchange_group`).
+    whose NCCL kernels fit into them (:func:`exchange_group`).  The exchange of
+    the last stripe has the GPU to itself: ``last_group`` (same ranks; e.g. the
+    default group, whose kernels use as many SMs as NCCL likes) is used for it
+    when given.
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if isinstance(key_shard, torch.Tensor):
@@ -226,7 +230,7 @@ def sharded_kv_attention_forward(
     main = torch.cuda.current_stream(query.device) if on_gpu else None
     comm = _comm_stream(query.device) if (on_gpu and n_stripes > 1) else main
 
-    def exchange_stripe(a: int, out_s: torch.Tensor, lse_s: torch.Tensor):
+    def exchange_stripe(a: int, out_s: torch.Tensor, lse_s: torch.Tensor, group=group):
         B = out_s.shape[0]
         # partials of query slice w go to rank w: [world, B, msw, ...] (no copy for B == 1) and [world, B, .., msw]
         send_o = out_s.reshape(B, world, msw, *out_s.shape[2:]).transpose(0, 1).contiguous()
@@ -260,7 +264,10 @@ def sharded_kv_attention_forward(
         lse_s.record_stream(comm)
         with torch.cuda.stream(comm):
             comm.wait_event(ready)
-            exchange_stripe(a, out_s, lse_s)
+            if s == n_stripes - 1 and last_group is not None:
+                exchange_stripe(a, out_s, lse_s, last_group)
+            else:
+                exchange_stripe(a, out_s, lse_s)
     if timings is not None and on_gpu:
         timings["attention_done"] = torch.cuda.Event(enable_timing=True)
         timings["attention_done"].record(main)
