@@ -27,6 +27,7 @@ struct Sm100Args {
   // kv_offset, rows from kv_split on at kv_offset2; 0 = one range
   int32_t kv_split, kv_offset2;
   int32_t sm_margin;  // persistent kernel: SMs left free for kernels of other streams
+  int32_t heads_per_wave;  // persistent kernel: (batch, head) pairs whose row blocks are handed out together (>= 1)
   int32_t out_dtype;
   float scale_log2;
   int32_t q_tiles;  // blocks of 256 query rows per sequence (static bound)

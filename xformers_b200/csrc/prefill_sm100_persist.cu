@@ -208,8 +208,17 @@ __device__ __forceinline__ bool decode_item(const Sm100Args& a, int idx, Item& i
   it.idx = idx;
   const int n_heads = a.groups * a.heads_per_group;
   const int n_bh = n_heads * a.batch;
-  const int qt = a.q_tiles - 1 - idx / n_bh;  // heaviest (latest) row blocks first
-  const int bh = idx % n_bh;
+  // Heaviest (latest) row blocks first, but not over all heads at once: the CTAs of a launch run side by side, and
+  // the keys and values they read should fit the L2 (a K/V tile is read once per row block of its head: from DRAM
+  // the first time only, if it is still there).  Heads are taken in groups of heads_per_wave; inside a group the
+  // row blocks go from the last to the first, so the launch still ends with light items.
+  const int kHeadsPerWave = a.heads_per_wave;
+  const int grp = idx / (kHeadsPerWave * a.q_tiles);
+  const int first_bh = grp * kHeadsPerWave;
+  const int in_grp = min(kHeadsPerWave, n_bh - first_bh);
+  const int rr = idx - grp * kHeadsPerWave * a.q_tiles;
+  const int qt = a.q_tiles - 1 - rr / in_grp;
+  const int bh = first_bh + rr % in_grp;
   it.b = bh / n_heads;
   it.head = bh % n_heads;
   it.g = it.head / a.heads_per_group, it.h = it.head % a.heads_per_group;
