@@ -98,13 +98,14 @@ int prefill_sm100_launch(const xfb200_prefill_params* p, cudaStream_t stream) {
   {
     // Work items are handed out heaviest first inside groups of (batch, head) pairs whose keys and values fit the L2
     // together (measured on 4 x 4096 x 32 heads: 945 -> 1020 TFLOP/s causal with 16 or 32 heads per group against all
-    // 128 at once, 990 -> 1140-1200 without a mask with 8).  Causal launches take larger groups: their items differ
-    // in weight, and the more of them run side by side the shorter the tail of a group.
+    // 128 at once, 990 -> 1140-1200 without a mask with 8; on 16 packed sequences of 256..4096 tokens 872 with 64,
+    // 900 with 128, 830-840 with 8..32).  Causal launches take larger groups: their items differ in weight, and the
+    // more of them run side by side the shorter the tail of a group.
     const double keys = varlen ? double(p->mkv) / double(p->batch > 0 ? p->batch : 1) : double(p->mkv);
     const double per_head = 2.0 * keys * D * 2.0 / (kbc ? H : 1);  // K and V, 2 bytes per element; a GQA group shares them
-    const double budget = (p->mask_type == XFB200_MASK_NONE ? 16.0 : 32.0) * 1024.0 * 1024.0;
+    const double budget = (p->mask_type == XFB200_MASK_NONE ? 16.0 : 64.0) * 1024.0 * 1024.0;
     int hpw = 1;
-    while (hpw < 64 && 2.0 * hpw * per_head <= budget) hpw *= 2;
+    while (hpw < 256 && 2.0 * hpw * per_head <= budget) hpw *= 2;
     if (kbc && hpw < H) hpw = H;  // the heads of a GQA group read the same keys: keep them together
     a.heads_per_wave = hpw;
   }
