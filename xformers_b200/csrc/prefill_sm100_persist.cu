@@ -938,23 +938,26 @@ __global__ void __launch_bounds__(kThreads, 1) prefill_sm100_persist_kernel(cons
             // (overwritten without being read).
             const int hi_first = __shfl_sync(0xffffffffu, col_hi, 0), hi_last = __shfl_sync(0xffffffffu, col_hi, 31);
             const int lo_first = __shfl_sync(0xffffffffu, col_lo, 0), lo_last = __shfl_sync(0xffffffffu, col_lo, 31);
-            uint32_t sm[32];
+            uint32_t sm[32], ninf[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ninf[i] = 0xff800000u;
 #pragma unroll 1
             for (int c = 0; c < kBN / 32; ++c) {
               const int col0 = n0 + c * 32;
               if (col0 >= lo_last && col0 + 32 <= hi_first) continue;  // every row of the warp sees the whole chunk
               if (col0 >= hi_last || col0 + 32 <= lo_first) {
-                // no row of the warp sees any of it
+                // no row of the warp sees any of it (the same eight registers serve every store: nothing to wait for)
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sm[i] = 0xff800000u;
+                for (int i = 0; i < 4; ++i) XFB_TMEM_ST_8(tmem_s + c * 32 + i * 8, ninf);
               } else {
+                tc_wait_st();  // (an earlier round's store may still be reading the registers)
                 XFB_TMEM_LD_32(tmem_s + c * 32, sm);
                 XFB_TMEM_WAIT_LD_32(sm);
                 mask_chunk(reinterpret_cast<float*>(sm), col0);
+                XFB_TMEM_ST_32(tmem_s + c * 32, sm);
               }
-              XFB_TMEM_ST_32(tmem_s + c * 32, sm);
-              tc_wait_st();  // (the registers are written again in the next round)
             }
+            tc_wait_st();
             XFB_PROF_COUNT(5)
             XFB_PROF_LAP(3)  // the visibility test
           }

@@ -198,6 +198,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
                :                                                                                                       \
                : "memory")
 
+#define XFB_TMEM_ST_8(taddr, r)                                                                                       \
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"                                \
+               :                                                                                                       \
+               : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])    \
+               : "memory")
+
 #define XFB_TMEM_ST_16(taddr, r)                                                                                      \
   asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" \
                :                                                                                                       \
