@@ -671,7 +671,9 @@ def main():
         lv_full = torch.randn(1, S, Hkv, 1, D, generator=gd, device=dev, dtype=torch.bfloat16)
         lflops = 4.0 * S * S * D * Hkv * G / 2.0
         hp_group = None
-        sm_margin = int(os.environ.get("XFB200_BENCH_SM_MARGIN", "8"))
+        # SMs the attention leaves to the collectives that run beside it: the exchange of a stripe has one stripe of attention to
+        # finish behind, and that shrinks with the number of ranks while the exchange does not
+        sm_margin = int(os.environ.get("XFB200_BENCH_SM_MARGIN", "8" if world <= 4 else "16"))
         n_str_default = int(os.environ.get("XFB200_BENCH_STRIPES", "8"))
         if world > 1:
             from xformers_b200.ops.fmha.sharded import exchange_group
@@ -686,7 +688,7 @@ def main():
             def fn():
                 res["out"], res["lse"] = sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True,
                                                                       exchange=exchange, stripes=stripes, group=group, sm_margin=sm_margin,
-                                                                      last_group=last_group)
+                                                                      last_group=last_group, mirror_stripes=stripes > 1)
 
             ms, win = event_time_ms(fn, l_steps, l_warm, barrier)
             windows.append(win)
@@ -694,7 +696,7 @@ def main():
             # break-down of one more step: attention of this rank's keys / what the exchange adds after it
             tm = {}
             sharded_kv_attention_forward(lq, lk, lv, kv_offset=[a for a, _ in spans], causal=True, exchange=exchange, stripes=stripes, timings=tm,
-                                         group=group, sm_margin=sm_margin, last_group=last_group)
+                                         group=group, sm_margin=sm_margin, last_group=last_group, mirror_stripes=stripes > 1)
             torch.cuda.synchronize()
             att = max_over_ranks(tm["start"].elapsed_time(tm["attention_done"]))
             tot = max_over_ranks(tm["start"].elapsed_time(tm["done"]))
@@ -726,7 +728,7 @@ def main():
         lt = lflops / (ms * 1e-3) / 1e12
         out_line["long_context"] = {"value": lt, "unit": UNIT, "ms_per_step": ms, "steps": l_steps, "warmup": l_warm, "scaling": "strong",
                                     "ideal_speedup": float(world), "breakdown": brk, "parity": par, "query_stripes": n_str, "sm_margin": sm_margin if world > 1 else 0,
-                                    "workload": f"1 x {S} causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work) covered by one launch per query stripe; per stripe NCCL all-to-all of the fp32 partials by query slice, LSE merge of the slice, all-gather of the merged slices, on a side stream behind the next stripe's attention"}
+                                    "workload": f"1 x {S} causal, Hq=64 Hkv=8 D=128 bf16; keys sharded over ranks in two ranges each (chunks r and 2N-1-r of 2N: equal causal work) covered by one launch per query stripe; a stripe is a block of query rows and its mirror image (equal work on every rank); per stripe NCCL all-to-all of the partials (input dtype, LSE fp32) by query slice on a side stream, LSE merge of the slice on the main stream, all-gather of the merged slices on the side stream, behind the next stripe's attention"}
         launches += (l_steps + l_warm + 1) * n_str
         if world > 1:
             # the literal form of the baseline configuration: one contiguous key shard per rank, all-gather of the partials, one merge
@@ -738,7 +740,7 @@ def main():
             r2 = world * world / (2.0 * world - 1.0)
             out_line["long_context_contiguous"] = {"value": ct, "unit": UNIT, "ms_per_step": ms, "steps": c_steps, "warmup": c_warm, "scaling": "strong",
                                                    "ideal_speedup": r2, "breakdown": brk, "parity": par,
-                                                   "workload": f"1 x {S} causal, contiguous key shards, NCCL all-gather of the fp32 partials, one LSE merge; causal work is imbalanced by construction: ideal speed-up R^2/(2R-1) = {r2:.2f}"}
+                                                   "workload": f"1 x {S} causal, contiguous key shards, NCCL all-gather of the partials (input dtype, LSE fp32), one LSE merge; causal work is imbalanced by construction: ideal speed-up R^2/(2R-1) = {r2:.2f}"}
         del lq, lk_full, lv_full
         torch.cuda.empty_cache()
 

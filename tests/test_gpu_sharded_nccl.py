@@ -43,6 +43,8 @@ def _worker(rank, world, init_file, out_file):
                  ("zigzag a2a 4 stripes", zigzag_bounds(S, world, rank), dict(exchange="all_to_all", stripes=4)),
                  ("zigzag a2a 4 stripes, SMs left free, a narrow group and the default group for the last stripe", zigzag_bounds(S, world, rank),
                   dict(exchange="all_to_all", stripes=4, sm_margin=8, group=exchange_group(max_ctas=8), last_group=dist.group.WORLD)),
+                 ("zigzag a2a, 4 stripes of mirrored row blocks", zigzag_bounds(S, world, rank),
+                  dict(exchange="all_to_all", stripes=4, mirror_stripes=True, sm_margin=8, group=exchange_group(max_ctas=8), last_group=dist.group.WORLD)),
                  ("zigzag gather", zigzag_bounds(S, world, rank), dict(exchange="all_gather")),
                  ("contiguous gather", [shard_bounds(S, world, rank)], dict(exchange="all_gather")),
                  ("contiguous a2a 2 stripes", [shard_bounds(S, world, rank)], dict(exchange="all_to_all", stripes=2))]

@@ -120,6 +120,7 @@ def sharded_kv_attention_forward(
     stripes: int = 1,
     sm_margin: int = 0,
     last_group: Optional[dist.ProcessGroup] = None,
+    mirror_stripes: bool = False,
     timings: Optional[dict] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Every rank passes the full ``query`` ``[B, Mq, (G,) H, D]`` and its own
@@ -135,7 +136,9 @@ def sharded_kv_attention_forward(
     the queries into that many stripes whose exchanges overlap the attention of
     the following stripe (CUDA tensors, all-to-all exchange).  ``timings``, a
     dict, receives CUDA events (``start``, ``attention_done``, ``done``) for a
-    break-down.
+    break-down; if it holds a list under ``"stripes"``, one list of events per
+    unit of rows is appended to it (start, partials laid out, all-to-all done,
+    merge done, all-gather done).
 
     ``partial_fn`` / ``merge_fn`` exist so that the exchange logic can be
     exercised with CPU stand-ins under the gloo backend.
@@ -148,6 +151,13 @@ def sharded_kv_attention_forward(
     the last stripe has the GPU to itself: ``last_group`` (same ranks; e.g. the
     default group, whose kernels use as many SMs as NCCL likes) is used for it
     when given.
+
+    ``mirror_stripes``: a stripe is the query rows ``[i w, (i + 1) w)`` together
+    with their mirror image ``[Mq - (i + 1) w, Mq - i w)``.  With causal masks and
+    keys sharded in mirror-symmetric ranges (:func:`zigzag_bounds`) every rank
+    then has the same amount of work in every stripe (a row at x and the row at
+    Mq - x see, of any mirror pair of key ranges, the length of one range), so no
+    rank's exchange waits for another rank's attention.
     """
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     if isinstance(key_shard, torch.Tensor):
@@ -222,52 +232,114 @@ def sharded_kv_attention_forward(
         return res
 
     # ---- all-to-all by query slice, stripe by stripe
-    ms = mq // n_stripes       # rows of a stripe
-    msw = ms // world          # rows of a stripe that one rank merges
+    mirrored = bool(mirror_stripes) and n_stripes > 1 and mq % (2 * n_stripes) == 0 and (mq // (2 * n_stripes)) % world == 0
+    ms = mq // (2 * n_stripes) if mirrored else mq // n_stripes  # rows that are exchanged as a unit
+    msw = ms // world                                            # rows of a unit that one rank merges
     # the result is allocated by the calling stream; the side stream fills it stripe by stripe
     out = torch.empty(query.shape, dtype=query.dtype, device=query.device)
     lse = torch.empty((query.shape[0],) + tuple(query.shape[2:-1]) + (mq,), dtype=torch.float32, device=query.device)
     main = torch.cuda.current_stream(query.device) if on_gpu else None
     comm = _comm_stream(query.device) if (on_gpu and n_stripes > 1) else main
 
-    def exchange_stripe(a: int, out_s: torch.Tensor, lse_s: torch.Tensor, group=group):
+    detail = timings.get("stripes") if (timings is not None and on_gpu) else None
+
+    def mark(tag_list):
+        if detail is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            tag_list.append(e)
+
+    # The exchange of a unit (ms query rows) has three parts: the all-to-all of the partials by query slice, the merge of
+    # this rank's slice, the all-gather of the merged slices.  With a side stream the collectives run there and the
+    # merge runs on the calling stream, between two attention launches: a merge that had to share the few SMs the
+    # attention leaves free with the collectives took longer than both of them together.
+    def scatter(a: int, out_s: torch.Tensor, lse_s: torch.Tensor, grp):
         B = out_s.shape[0]
+        ev = []
+        if detail is not None:
+            detail.append(ev)
+        mark(ev)
         # partials of query slice w go to rank w: [world, B, msw, ...] (no copy for B == 1) and [world, B, .., msw]
         send_o = out_s.reshape(B, world, msw, *out_s.shape[2:]).transpose(0, 1).contiguous()
         send_l = lse_s.reshape(*lse_s.shape[:-1], world, msw).movedim(-2, 0).contiguous()
         recv_o, recv_l = torch.empty_like(send_o), torch.empty_like(send_l)
-        dist.all_to_all_single(recv_o, send_o, group=group)
-        dist.all_to_all_single(recv_l, send_l, group=group)
+        mark(ev)
+        dist.all_to_all_single(recv_o, send_o, group=grp)
+        dist.all_to_all_single(recv_l, send_l, group=grp)
+        mark(ev)
+        return a, recv_o, recv_l, grp, ev
+
+    def merge_unit(unit):
+        a, recv_o, recv_l, grp, ev = unit
         m_o, m_l = merge_fn(recv_o, recv_l, query.dtype)                       # [B, msw, ...], [B, .., msw]
         m_o, m_l = m_o.contiguous(), m_l.contiguous()
+        mark(ev)
+        return a, m_o, m_l, grp, ev
+
+    def gather(unit):
+        a, m_o, m_l, grp, ev = unit
+        B = m_o.shape[0]
         if B == 1:
-            # the merged slices of a stripe are consecutive rows of the result: gather them in place
-            dist.all_gather_into_tensor(out[0, a : a + ms], m_o[0], group=group)
+            # the merged slices of a unit are consecutive rows of the result: gather them in place
+            dist.all_gather_into_tensor(out[0, a : a + ms], m_o[0], group=grp)
         else:
             all_o = torch.empty((world,) + tuple(m_o.shape), dtype=m_o.dtype, device=m_o.device)
-            dist.all_gather_into_tensor(all_o.view(-1, *m_o.shape[1:]), m_o, group=group)
+            dist.all_gather_into_tensor(all_o.view(-1, *m_o.shape[1:]), m_o, group=grp)
             out[:, a : a + ms] = all_o.transpose(0, 1).reshape(B, ms, *m_o.shape[2:])
         all_l = torch.empty((world,) + tuple(m_l.shape), dtype=m_l.dtype, device=m_l.device)
-        dist.all_gather_into_tensor(all_l.view(-1, *m_l.shape[1:]), m_l, group=group)
+        dist.all_gather_into_tensor(all_l.view(-1, *m_l.shape[1:]), m_l, group=grp)
         lse[..., a : a + ms] = all_l.movedim(0, -2).reshape(*m_l.shape[:-1], ms)
+        mark(ev)
 
+    def finish(pending):
+        """Merge (calling stream) and all-gather (side stream) of the units whose all-to-all was queued earlier."""
+        units, scattered = pending
+        main.wait_event(scattered)
+        merged = []
+        for unit in units:
+            unit[1].record_stream(main)  # (allocated by the side stream, read by the calling stream)
+            unit[2].record_stream(main)
+            merged.append(merge_unit(unit))
+        done = torch.cuda.Event()
+        done.record(main)
+        with torch.cuda.stream(comm):
+            comm.wait_event(done)
+            for unit in merged:
+                unit[1].record_stream(comm)
+                unit[2].record_stream(comm)
+                gather(unit)
+
+    pending = None
     for s in range(n_stripes):
-        a = s * ms
-        out_s, lse_s = local_partial(a, a + ms)
+        # the row ranges of this stripe, each exchanged as a unit of ms rows
+        if mirrored:
+            starts = [s * ms, mq - (s + 1) * ms]
+        else:
+            starts = [s * ms]
+        parts = [(a,) + tuple(local_partial(a, a + ms)) for a in starts]
+        grp = last_group if (s == n_stripes - 1 and last_group is not None and comm is not main) else group
         if comm is main:
-            exchange_stripe(a, out_s, lse_s)
+            for a, out_s, lse_s in parts:
+                gather(merge_unit(scatter(a, out_s, lse_s, grp)))
             continue
         ready = torch.cuda.Event()
         ready.record(main)
-        # (allocated by the calling stream, consumed by the side stream: their memory must not be reused before that)
-        out_s.record_stream(comm)
-        lse_s.record_stream(comm)
         with torch.cuda.stream(comm):
             comm.wait_event(ready)
-            if s == n_stripes - 1 and last_group is not None:
-                exchange_stripe(a, out_s, lse_s, last_group)
-            else:
-                exchange_stripe(a, out_s, lse_s)
+            units = []
+            for a, out_s, lse_s in parts:
+                # (allocated by the calling stream, consumed by the side stream: their memory must not be reused before that)
+                out_s.record_stream(comm)
+                lse_s.record_stream(comm)
+                units.append(scatter(a, out_s, lse_s, grp))
+            scattered = torch.cuda.Event()
+            scattered.record(comm)
+        # the stripe before this one: its all-to-all had this stripe's attention to finish behind
+        if pending is not None:
+            finish(pending)
+        pending = (units, scattered)
+    if pending is not None:
+        finish(pending)
     if timings is not None and on_gpu:
         timings["attention_done"] = torch.cuda.Event(enable_timing=True)
         timings["attention_done"].record(main)
