@@ -215,9 +215,10 @@ typedef struct {
    * a row past the end (a bad page-table entry) reads as zero instead of foreign memory. */
   const int32_t* kv_seqstart;
   int64_t kv_rows;
-  /* Local attention for one query per sequence (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
-   * PagedBlockDiagonalCausalLocalPaddedKeysMask, fmha/attn_bias.py:29,43): 0, or the number of keys the
-   * query sees, the last window_size of its sequence.  Needs mq == 1 and the bottom-right causal mask. */
+  /* Local attention (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
+   * PagedBlockDiagonalCausalLocalPaddedKeysMask, fmha/attn_bias.py:29,43): 0, or the number of keys a
+   * query sees, the window_size keys that end at its own position (query i of the mq queries of a
+   * sequence stands at key kv_len - mq + i).  Needs the bottom-right causal mask. */
   int32_t window_size;
   int32_t reserved;
 } xfb200_decode_params;

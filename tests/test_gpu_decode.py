@@ -340,20 +340,22 @@ def test_decode_respects_current_stream_and_custom_scale():
 @pytest.mark.parametrize("split_k", [None, 1, 3])
 @pytest.mark.parametrize("window", [1, 100, 640, 5000])
 @pytest.mark.parametrize("kv_heads,group", [(8, 8), (1, 4)])
-def test_local_window_one_query(kv_heads, group, window, split_k, fmt):
+@pytest.mark.parametrize("Mq", [1, 3])
+def test_local_window(Mq, kv_heads, group, window, split_k, fmt):
     """BlockDiagonalCausalLocalAttentionPaddedKeysMask and its paged form
-    (bias list of tests/test_mem_eff_attention.py:283,395) with one query per
-    sequence: the query sees the last `window` keys of its sequence, i.e. the
-    sequence starts later; the same keys behind a block table give the same bits."""
+    (bias list of tests/test_mem_eff_attention.py:283,395): a query sees the
+    `window` keys that end at its own position (the last `window` keys of its
+    sequence with one query per sequence, i.e. the sequence starts later); the
+    same keys behind a block table give the same bits."""
     require_cuda()
     dtype, D, B, max_t, page = torch.bfloat16, 128, 4, 1536, 64
     g = torch.Generator().manual_seed(window)
-    lens = [max_t, 1, 700, 99]
-    q = torch.randn(1, B, kv_heads, group, D, generator=g).to(dtype).cuda()
+    lens = [max_t, Mq, 700, 99]
+    q = torch.randn(1, B * Mq, kv_heads, group, D, generator=g).to(dtype).cuda()
     kf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
     vf = torch.randn(1, B * max_t, kv_heads, 1, D, generator=g)
     expand = lambda t: t.expand(-1, -1, -1, group, -1)
-    pad_bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([1] * B, max_t, lens, window, device="cuda")
+    pad_bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([Mq] * B, max_t, lens, window, device="cuda")
     if fmt == "fp8":
         from oracle import fp8 as ofp8
 
@@ -389,7 +391,7 @@ def test_local_window_one_query(kv_heads, group, window, split_k, fmt):
     assert_o_lse(out_pad, lse_pad, ro, rl, dtype, f"window {window} {fmt}")
     # the plain causal mask with a window that covers everything is the same computation
     if window >= max_t:
-        full = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens([1] * B, max_t, lens, device="cuda")
+        full = ab.BlockDiagonalCausalWithOffsetPaddedKeysMask.from_seqlens([Mq] * B, max_t, lens, device="cuda")
         out_f, lse_f = run(k_pad, v_pad, full)
         assert torch.equal(out_pad, out_f) and torch.equal(lse_pad, lse_f)
     if fmt == "fp8":
@@ -408,21 +410,27 @@ def test_local_window_one_query(kv_heads, group, window, split_k, fmt):
     out, lse = run(k_pg, v_pg, bias)
     assert_o_lse(out, lse, ro, rl, dtype, f"paged window {window} {fmt}")
     # and the paged bias materialises to the same visible keys as the flat one (physical rows)
-    m = bias.to("cpu").materialize((B, n_pages * page)) == 0
-    assert int(m.sum()) == sum(min(n, window) for n in lens)
+    m = bias.to("cpu").materialize((B * Mq, n_pages * page)) == 0
+    assert int(m.sum()) == sum(min(n - Mq + i + 1, window) for n in lens for i in range(Mq))
 
 
 @gpu
-def test_local_window_needs_one_query():
+@pytest.mark.parametrize("Mq,window", [(2, 4), (5, 3), (4, 1), (16, 40)])
+def test_local_window_several_queries_small(Mq, window):
+    """Windows shorter than, equal to and longer than the number of queries of a sequence, sequences shorter than
+    the window: every row's lower limit lies in the first sub-tile of the first chunk."""
     require_cuda()
-    q = torch.randn(1, 4, 2, 128, device="cuda", dtype=torch.bfloat16)
-    k = torch.randn(1, 2 * 64, 2, 128, device="cuda", dtype=torch.bfloat16)
-    bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([2, 2], 64, [10, 20], 4, device="cuda")
-    assert any("one query per sequence" in r for r in S.FwOp.not_supported_reasons(fmha.Inputs(q, k, k, bias)))
-    # the dispatcher still finds an operator for it (the prefill operator takes windows with several queries)
-    out = fmha.memory_efficient_attention_forward(q, k, k, bias)
-    ro, _ = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), k.float().cpu(), bias.to("cpu"))
-    assert (out.float().cpu() - ro).abs().max() <= 2e-2
+    g = torch.Generator().manual_seed(Mq * 100 + window)
+    lens = [Mq, 64, Mq + window - 1, 37]
+    B, pad = len(lens), 64
+    q = torch.randn(1, B * Mq, 2, 128, generator=g).bfloat16().cuda()
+    k = torch.randn(1, B * pad, 2, 128, generator=g).bfloat16().cuda()
+    v = torch.randn(1, B * pad, 2, 128, generator=g).bfloat16().cuda()
+    bias = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([Mq] * B, pad, lens, window, device="cuda")
+    assert not S.FwOp.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=S.FwOp)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), bias.to("cpu"))
+    assert_o_lse(out, lse, ro, rl, torch.bfloat16, f"window {window}, {Mq} queries")
 
 
 @gpu

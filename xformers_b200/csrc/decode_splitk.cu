@@ -73,7 +73,8 @@ struct DecodeArgs {
   int32_t causal;
   int32_t out_dtype;
   float scale_log2;
-  int32_t window_size;  // 0: none; else (mq == 1 only) the query sees its sequence's last window_size keys
+  int32_t window_size;  // 0: none; else query i of a sequence sees the window_size keys that end at its own position
+  int32_t window_span;  // window_size + mq - 1: the keys any query of a sequence sees (0 without a window)
 };
 
 template <bool kBf16>
@@ -218,16 +219,21 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
       }
   }
 
-  // per-row visibility limit: token t visible iff t < lim
-  int lim[MT][2];
+  // per-row visibility limits: token t visible iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
+  int lim[MT][2], lo[MT][2];
+  const bool has_lo = a.window_size > 0 && a.mq > 1;  // uniform
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int hlf = 0; hlf < 2; ++hlf) {
       const int row = w.row0 + mt * 16 + r + hlf * 8;
-      int l = w.chunk_hi;
-      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
-      lim[mt][hlf] = l;
+      int l = w.chunk_hi, f = 0;
+      if (a.causal && row < R) {
+        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
+        l = min(l, own);
+        if (has_lo) f = max(own - a.window_size, 0);
+      }
+      lim[mt][hlf] = l, lo[mt][hlf] = f;
     }
 
   float acc[MT][NT][4];
@@ -291,6 +297,20 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
             s[mt][j][2 + e] = t < lim[mt][1] ? s[mt][j][2 + e] * a.scale_log2 : -INFINITY;
           }
         }
+      if (has_lo && t_sub < a.mq) {
+        // (the lower limits lie within the first mq - 1 tokens of the window: one sub-tile or two of the first chunk)
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int t = t_sub + j * 8 + 2 * c + e;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              if (t < lo[mt][0]) s[mt][j][e] = -INFINITY;
+              if (t < lo[mt][1]) s[mt][j][2 + e] = -INFINITY;
+            }
+          }
+      }
 
       uint32_t pa[MT][4];
 #pragma unroll
@@ -500,20 +520,29 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
   // per-query-row visibility limit: token t visible iff t < lim
-  int lim[NTQ][2];
-  int lim_min = w.chunk_hi;  // below it nothing is masked for any row of this warp
+  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
+  int lim[NTQ][2], lo[NTQ][2];
+  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
+  int lo_max = 0;
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi;
-      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
-      lim[nt][e] = l;
+      int l = w.chunk_hi, f = 0;
+      if (a.causal && row < R) {
+        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
+        l = min(l, own);
+        if (a.window_size > 0) f = max(own - a.window_size, 0);
+      }
+      lim[nt][e] = l, lo[nt][e] = f;
       lim_min = min(lim_min, l);
+      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
@@ -570,7 +599,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
       const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
       float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
       float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
-      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
+      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;  // warp-uniform
       float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
       bool need = false;
 #pragma unroll
@@ -589,8 +618,8 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
         for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
           }
       }
 #pragma unroll
@@ -791,20 +820,29 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
   __syncwarp();
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
-  int lim[NTQ][2];
-  int lim_min = w.chunk_hi;
+  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
+  int lim[NTQ][2], lo[NTQ][2];
+  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
+  int lo_max = 0;
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi;
-      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
-      lim[nt][e] = l;
+      int l = w.chunk_hi, f = 0;
+      if (a.causal && row < R) {
+        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
+        l = min(l, own);
+        if (a.window_size > 0) f = max(own - a.window_size, 0);
+      }
+      lim[nt][e] = l, lo[nt][e] = f;
       lim_min = min(lim_min, l);
+      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][NG][2];
@@ -835,7 +873,7 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
       if (t_sub >= w.chunk_hi) continue;
       const uint32_t* k0 = kst + (usub * 16 + r) * rw;  // token r; token r + 8 is 8 rows on
       const uint32_t* v0 = vst + (usub * 16 + r) * rw;
-      const bool all_visible = t_sub + 16 <= lim_min;
+      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;
       const int t0 = t_sub + r, t1 = t_sub + r + 8;
       const bool in0 = t0 < w.chunk_hi, in1 = t1 < w.chunk_hi;  // tokens past the end were not copied
 
@@ -945,8 +983,8 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
           sc0[nt][e] *= qfac[nt][e];
           sc1[nt][e] *= qfac[nt][e];
           if (!all_visible) {
-            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
           }
           need |= fmaxf(sc0[nt][e], sc1[nt][e]) > m_run[nt][e] + kLazy;
         }
@@ -1147,20 +1185,29 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
   __syncwarp();
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
-  int lim[NTQ][2];
-  int lim_min = w.chunk_hi;
+  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
+  int lim[NTQ][2], lo[NTQ][2];
+  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
+  int lo_max = 0;
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi;
-      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
-      lim[nt][e] = l;
+      int l = w.chunk_hi, f = 0;
+      if (a.causal && row < R) {
+        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
+        l = min(l, own);
+        if (a.window_size > 0) f = max(own - a.window_size, 0);
+      }
+      lim[nt][e] = l, lo[nt][e] = f;
       lim_min = min(lim_min, l);
+      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
+  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
@@ -1224,7 +1271,7 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
       const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
       float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
       float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
-      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
+      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;  // warp-uniform
       float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
       bool need = false;
 #pragma unroll
@@ -1243,8 +1290,8 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
         for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
           }
       }
 #pragma unroll
@@ -1398,8 +1445,8 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
   const int TOK = 16 * wph * kSps;
 
   int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
-  // a window (one query per sequence) is a sequence that starts win_skip keys later
-  const int win_skip = a.window_size > 0 ? max(kv_len - a.window_size, 0) : 0;
+  // a window is a sequence that starts win_skip keys later: the first key the first query of the sequence sees
+  const int win_skip = a.window_size > 0 ? max(kv_len - a.window_span, 0) : 0;
   kv_len -= win_skip;
   const int chunk_lo = split * a.chunk_tokens;
   const int chunk_hi = min(chunk_lo + a.chunk_tokens, kv_len);
@@ -1684,7 +1731,7 @@ __global__ void __launch_bounds__(256) decode_merge_kernel(const __grid_constant
   const int head = int((gw / R) % a.kv_heads);
   const int b = int(gw / (int64_t(R) * a.kv_heads));
   int kv_len = a.seqlen_k != nullptr ? min(max(a.seqlen_k[b], 0), a.kv_padding) : a.kv_padding;
-  if (a.window_size > 0) kv_len = min(kv_len, a.window_size);
+  if (a.window_size > 0) kv_len = min(kv_len, a.window_span);
   const int nsplit = min(a.split_k, (kv_len + a.chunk_tokens - 1) / a.chunk_tokens);
 
   float mx = -INFINITY;
@@ -1849,8 +1896,9 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   a.batch = p->batch, a.mq = p->mq, a.kv_heads = p->kv_heads, a.q_per_kv = p->q_per_kv;
   a.kv_padding = p->kv_padding, a.page_size = p->page_size, a.bt_stride = p->block_table_stride;
   a.split_k = p->split_k;
-  // with a window no sequence has more than window_size keys to read: the chunks divide that
-  a.chunk_tokens = decode_chunk_tokens(p->window_size > 0 && p->window_size < p->kv_padding ? p->window_size : p->kv_padding, p->split_k);
+  // with a window no sequence has more than window_size + mq - 1 keys to read: the chunks divide that
+  const int window_span = p->window_size > 0 ? p->window_size + p->mq - 1 : 0;
+  a.chunk_tokens = decode_chunk_tokens(window_span > 0 && window_span < p->kv_padding ? window_span : p->kv_padding, p->split_k);
   a.rows = R, a.row_blocks = row_blocks;
   a.q_sm = p->q_stride_m, a.q_sg = p->q_stride_g, a.q_sh = p->q_stride_h;
   a.k_sm = p->k_stride_m, a.k_sg = p->k_stride_g, a.v_sm = p->v_stride_m, a.v_sg = p->v_stride_g;
@@ -1926,10 +1974,10 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
   if (fp8 && a.copy_mode != 0) return set_error(XFB200_E_UNSUPPORTED, "decode: the heads of an fp8 cache row must be contiguous");
   a.box_tok = 16;
-  a.window_size = p->window_size;
+  a.window_size = p->window_size, a.window_span = window_span;
   if (p->window_size < 0) return set_error(XFB200_E_INVALID, "decode: window_size %d", p->window_size);
-  if (p->window_size > 0 && (p->mq != 1 || p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT))
-    return set_error(XFB200_E_UNSUPPORTED, "decode: a window needs one query per sequence and the bottom-right causal mask");
+  if (p->window_size > 0 && p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT)
+    return set_error(XFB200_E_UNSUPPORTED, "decode: a window needs the bottom-right causal mask");
   // a window moves the first key of a sequence like a gappy start does
   const bool gappy = p->kv_seqstart != nullptr || p->window_size > 0;
   if (gappy && p->block_tables == nullptr && p->kv_seqstart != nullptr && p->kv_rows <= 0)

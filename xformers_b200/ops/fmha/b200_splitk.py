@@ -118,7 +118,7 @@ class FwOp(AttentionFwOpBase):
         BlockDiagonalCausalWithOffsetGappyKeysMask,
         PagedBlockDiagonalGappyKeysMask,
         PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
-        BlockDiagonalCausalLocalAttentionPaddedKeysMask,  # one query per sequence
+        BlockDiagonalCausalLocalAttentionPaddedKeysMask,
         PagedBlockDiagonalCausalLocalPaddedKeysMask,
     )
     SUPPORTS_DROPOUT = False
@@ -188,8 +188,6 @@ class FwOp(AttentionFwOpBase):
             if B != 1:
                 reasons.append("padded/paged biases need batch 1")
             if isinstance(bias, _LOCAL_BIASES):
-                if mq != 1:
-                    reasons.append("local attention is supported for one query per sequence (use the prefill operator for more)")
                 if fp8 and isinstance(bias, PagedBlockDiagonalPaddedKeysMask):
                     reasons.append("a paged fp8 cache cannot be read through a window")
         else:
@@ -328,7 +326,7 @@ class FwOp(AttentionFwOpBase):
             if _lib.debug_checks():
                 _debug_check_decode(bias, p, k)
             row_bytes = D if fp8 else (D // 8 + cls.NUM_GROUPS) * 4 if quantized else D * 2
-            p.split_k = cls.get_split_k(p.batch, min(p.kv_padding, p.window_size) if p.window_size else p.kv_padding, p.kv_heads, row_bytes)
+            p.split_k = cls.get_split_k(p.batch, min(p.kv_padding, p.window_size + p.mq - 1) if p.window_size else p.kv_padding, p.kv_heads, row_bytes)
             lib = _lib.load()
             nbytes = lib.xfb200_decode_scratch_bytes(p.batch, p.mq, p.kv_heads, p.q_per_kv, D, p.split_k)
             scratch = torch.empty((nbytes,), dtype=torch.uint8, device=q.device) if nbytes else None
