@@ -673,7 +673,7 @@ def main():
         hp_group = None
         # SMs the attention leaves to the collectives that run beside it: the exchange of a stripe has one stripe of attention to
         # finish behind, and that shrinks with the number of ranks while the exchange does not
-        sm_margin = int(os.environ.get("XFB200_BENCH_SM_MARGIN", "8" if world <= 4 else "16"))
+        sm_margin = int(os.environ.get("XFB200_BENCH_SM_MARGIN", "8" if world <= 4 else "12"))
         n_str_default = int(os.environ.get("XFB200_BENCH_STRIPES", "8"))
         if world > 1:
             from xformers_b200.ops.fmha.sharded import exchange_group
