@@ -212,7 +212,7 @@ def sharded_kv_attention_forward(
     n_stripes = max(1, int(stripes)) if (use_a2a and on_gpu) else 1
     while n_stripes > 1 and (mq % n_stripes or (mq // n_stripes) % world):
         n_stripes -= 1
-    margin = int(sm_margin) if n_stripes > 1 else 0
+    margin = 0
 
     if not use_a2a:
         out_r, lse_r = local_partial(0, mq)
@@ -316,6 +316,8 @@ def sharded_kv_attention_forward(
             starts = [s * ms, mq - (s + 1) * ms]
         else:
             starts = [s * ms]
+        # (no collective runs beside the first stripe's attention: it may have every SM)
+        margin = int(sm_margin) if (n_stripes > 1 and s > 0) else 0
         parts = [(a,) + tuple(local_partial(a, a + ms)) for a in starts]
         grp = last_group if (s == n_stripes - 1 and last_group is not None and comm is not main) else group
         if comm is main:
