@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define XFB200_ABI_VERSION 3
+#define XFB200_ABI_VERSION 4
 
 #if defined(__GNUC__)
 #define XFB200_API __attribute__((visibility("default")))
@@ -221,6 +221,15 @@ typedef struct {
    * sequence stands at key kv_len - mq + i).  Needs the bottom-right causal mask. */
   int32_t window_size;
   int32_t reserved;
+  /* Additive bias (a plain tensor as attn_bias; the reference's split-K operator takes one,
+   * xformers/ops/fmha/triton_splitk.py:18-27): NULL, or [batch, kv_heads, q_per_kv, mq, keys] with unit
+   * stride on the last axis and the element strides below (0 = broadcast), added to q k^T * scale
+   * before the mask and the softmax.  16-bit caches in the plain layout (no sequence lengths, no
+   * page table). */
+  const void* bias;
+  int32_t bias_dtype; /* XFB200_BF16 | XFB200_F16 | XFB200_F32 */
+  int32_t reserved2;
+  int64_t bias_stride_b, bias_stride_kvh, bias_stride_q, bias_stride_m;
 } xfb200_decode_params;
 
 XFB200_API size_t xfb200_decode_scratch_bytes(int32_t batch, int32_t mq, int32_t kv_heads, int32_t q_per_kv, int32_t head_dim,

@@ -415,6 +415,40 @@ def test_local_window(Mq, kv_heads, group, window, split_k, fmt):
 
 
 @gpu
+@pytest.mark.parametrize("bias_dtype", [None, torch.float32])
+@pytest.mark.parametrize("split_k", [None, 1, 4])
+@pytest.mark.parametrize("layout,Mq", [("gqa", 1), ("gqa", 3), ("mha", 2), ("mha", 1)])
+def test_decode_additive_tensor_bias(layout, Mq, split_k, bias_dtype):
+    """A plain tensor as attn_bias on the split-K operator (the reference's takes one,
+    xformers/ops/fmha/triton_splitk.py:18-27): added to q k^T * scale before the softmax;
+    -inf entries hide keys."""
+    require_cuda()
+    dtype, D, B, Mkv = torch.bfloat16, 128, 2, 700
+    g = torch.Generator().manual_seed(17 + Mq)
+    if layout == "gqa":
+        G, H = 2, 4
+        q = torch.randn(B, Mq, G, H, D, generator=g).to(dtype).cuda()
+        k = torch.randn(B, Mkv, G, 1, D, generator=g).to(dtype).cuda().expand(-1, -1, -1, H, -1)
+        v = torch.randn(B, Mkv, G, 1, D, generator=g).to(dtype).cuda().expand(-1, -1, -1, H, -1)
+        bshape = (B, G, H, Mq, Mkv)
+    else:
+        H = 3
+        q = torch.randn(B, Mq, H, D, generator=g).to(dtype).cuda()
+        k = torch.randn(B, Mkv, H, D, generator=g).to(dtype).cuda()
+        v = torch.randn(B, Mkv, H, D, generator=g).to(dtype).cuda()
+        bshape = (B, H, Mq, Mkv)
+    bias = (torch.randn(bshape, generator=g) * 2).to(bias_dtype or dtype)
+    bias[..., 0, : Mkv // 3] = float("-inf")
+    bias = bias.cuda()
+    op = S.FwOp if split_k is None else type("Op", (S.FwOp,), {"SPLIT_K": split_k})
+    assert not op.not_supported_reasons(fmha.Inputs(q, k, v, bias))
+    out, lse = fmha.memory_efficient_attention_forward_requires_grad(q, k, v, bias, op=op)
+    ro, rl = oracle.ref_attention_with_lse(q.float().cpu(), k.float().cpu(), v.float().cpu(), bias.float().cpu())
+    assert_o_lse(out, lse, ro, rl, dtype, f"decode with a tensor bias, {layout}")
+    assert fmha.b200_splitk.decode_device_status() == 0
+
+
+@gpu
 @pytest.mark.parametrize("Mq,window", [(2, 4), (5, 3), (4, 1), (16, 40)])
 def test_local_window_several_queries_small(Mq, window):
     """Windows shorter than, equal to and longer than the number of queries of a sequence, sequences shorter than

@@ -25,14 +25,14 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/xfb200.h but not exported"
     assert set(declared) == set(_lib.EXPORTED_SYMBOLS)
-    assert _lib.load().xfb200_abi_version() == _lib.ABI_VERSION == 3
+    assert _lib.load().xfb200_abi_version() == _lib.ABI_VERSION == 4
 
 
 def test_struct_sizes_match_header():
     # sizes computed by hand from include/xfb200.h (LP64)
     assert ctypes.sizeof(_lib.Strides) == 32
     assert ctypes.sizeof(_lib.PrefillParams) == 8 * 8 + 8 * 4 + 4 * 32 + 3 * 8 + 6 * 4 + 8 + 2 * 4 + 4 * 8 + 6 * 4
-    assert ctypes.sizeof(_lib.DecodeParams) == 8 * 8 + 12 * 4 + 12 * 8 + 4 * 4 + 2 * 8 + 4 * 8 + 8 + 8 + 2 * 4
+    assert ctypes.sizeof(_lib.DecodeParams) == 8 * 8 + 12 * 4 + 12 * 8 + 4 * 4 + 2 * 8 + 4 * 8 + 8 + 8 + 2 * 4 + 8 + 2 * 4 + 4 * 8
     assert ctypes.sizeof(_lib.MergeParams) == 16 + 8 + 16 + 32 + 24 + 16 + 32 + 24 + 8 * 4
 
 

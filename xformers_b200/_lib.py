@@ -12,7 +12,7 @@ import os
 from pathlib import Path
 from typing import Optional
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 XFB200_OK = 0
 XFB200_E_INVALID = -1
@@ -140,6 +140,13 @@ class DecodeParams(C.Structure):
         ("kv_rows", C.c_int64),
         ("window_size", C.c_int32),
         ("reserved", C.c_int32),
+        ("bias", C.c_void_p),
+        ("bias_dtype", C.c_int32),
+        ("reserved2", C.c_int32),
+        ("bias_stride_b", C.c_int64),
+        ("bias_stride_kvh", C.c_int64),
+        ("bias_stride_q", C.c_int64),
+        ("bias_stride_m", C.c_int64),
     ]
 
 

@@ -75,6 +75,12 @@ struct DecodeArgs {
   float scale_log2;
   int32_t window_size;  // 0: none; else query i of a sequence sees the window_size keys that end at its own position
   int32_t window_span;  // window_size + mq - 1: the keys any query of a sequence sees (0 without a window)
+  // additive bias (16-bit cache, plain layout): element strides of [batch, kv_heads, q_per_kv, mq, keys]; bias / scale is
+  // added to q k^T, so that the softmax sees q k^T * scale + bias
+  const void* bias;
+  int32_t bias_dtype;
+  float inv_scale;
+  int64_t bias_b, bias_kvh, bias_q, bias_m;
 };
 
 template <bool kBf16>
@@ -115,6 +121,9 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t bits16) {
 // Shared-memory geometry of one stage.
 // cache formats (the template parameter kFmt of what follows)
 constexpr int kFmtPlain = 0, kFmtInt4 = 1, kFmtFp8 = 2;
+// the plain layout read by the variant of its consumer that knows additive biases and per-row lower limits (windows with
+// several queries per sequence): a kernel of its own, so that the common one stays as lean as it is
+constexpr int kFmtPlainX = 3;
 
 template <int D, int kFmt, int NG = 1>
 struct DecStage {
@@ -180,7 +189,7 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 // of the MMAs, tokens the N columns of QK^T and the K dimension of PV.
 // Leaves the un-normalised partial (acc, running max, row sum) in w.mine.
 // ---------------------------------------------------------------------------
-template <int D, int MT, bool kBf16>
+template <int D, int MT, bool kBf16, bool kExtras>
 __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp& w) {
   constexpr int KS = D / 16;  // k-steps of the QK^T product
   constexpr int NT = D / 8;   // n-tiles of the PV product
@@ -221,7 +230,7 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
 
   // per-row visibility limits: token t visible iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
   int lim[MT][2], lo[MT][2];
-  const bool has_lo = a.window_size > 0 && a.mq > 1;  // uniform
+  const bool has_lo = kExtras && a.window_size > 0 && a.mq > 1;  // uniform
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -285,6 +294,32 @@ __device__ __forceinline__ void consume_plain(const DecodeArgs& a, const DecWarp
         }
       }
 
+      if (kExtras && a.bias != nullptr) {
+        // additive bias: one value per (query row, token), read where it lies (plain loads: this path is for small inputs)
+        const int esz = a.bias_dtype == XFB200_F32 ? 4 : 2;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            const int row = w.row0 + mt * 16 + r + hlf * 8;
+            if (row >= R) continue;
+            const uint8_t* brow = reinterpret_cast<const uint8_t*>(a.bias) +
+                                  (int64_t(w.b) * a.bias_b + int64_t(w.head) * a.bias_kvh + int64_t(row % a.q_per_kv) * a.bias_q +
+                                   int64_t(row / a.q_per_kv) * a.bias_m) * esz;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int t = t_sub + j * 8 + 2 * c + e;
+                if (t >= w.chunk_hi) continue;
+                float bv;
+                if (a.bias_dtype == XFB200_F32) bv = reinterpret_cast<const float*>(brow)[t];
+                else if (a.bias_dtype == XFB200_BF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(brow)[t]);
+                else bv = __half2float(reinterpret_cast<const __half*>(brow)[t]);
+                s[mt][j][hlf * 2 + e] = fmaf(bv, a.inv_scale, s[mt][j][hlf * 2 + e]);
+              }
+          }
+      }
       // -------------------------------- scale, mask, online softmax (log2 domain)
 #pragma unroll
       for (int j = 0; j < 2; ++j)
@@ -1418,7 +1453,7 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
 template <int D, int MT, int kFmt, bool kBf16, int NG = 1>
 __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) decode_splitk_kernel(const __grid_constant__ DecodeArgs a) {
   using Stage = DecStage<D, kFmt, NG>;
-  constexpr bool kInt4 = kFmt == kFmtInt4, kFp8 = kFmt == kFmtFp8, kQuant = kFmt != kFmtPlain;
+  constexpr bool kInt4 = kFmt == kFmtInt4, kFp8 = kFmt == kFmtFp8, kQuant = kFmt == kFmtInt4 || kFmt == kFmtFp8;
   using T = typename Half2Type<kBf16>::T;
   constexpr int W = NG + D / 8;  // int4 words per row (NG scale/shift words, then the nibbles)
   // query rows of one kv head per CTA: MT m-tiles of 16 (16-bit cache) or MT
@@ -1665,7 +1700,7 @@ __global__ void __launch_bounds__(kDecThreads, DecOccupancy<kFmt>::kCtasPerSm) d
   else if constexpr (kFp8)
     consume_fp8<D, MT, kBf16>(a, w);
   else
-    consume_plain<D, MT, kBf16>(a, w);
+    consume_plain<D, MT, kBf16, kFmt == kFmtPlainX>(a, w);
   asm volatile("bar.sync 1, %0;" ::"n"(kDecConsumerWarps * 32) : "memory");
   // warps of head hw share the rows: warp `sub` finalises rows sub, sub+wph, ...
   const bool direct = a.split_k == 1;
@@ -1793,7 +1828,7 @@ int decode_chunk_tokens(int kv_bound, int split_k) {
 template <int D, int MT, int kFmt, bool kBf16, int NG = 1>
 static int launch_decode_t(const DecodeArgs& a_in, int head_blocks, cudaStream_t stream) {
   using Stage = DecStage<D, kFmt, NG>;
-  constexpr bool kQuant = kFmt != kFmtPlain;
+  constexpr bool kQuant = kFmt == kFmtInt4 || kFmt == kFmtFp8;
   constexpr int ROWS = kQuant ? 8 * MT : 16 * MT;
   // tiled copies need no row padding
   const int kv_bytes = kFmt == kFmtFp8      ? Stage::tokens(a_in.hb) * a_in.hb * D
@@ -1974,6 +2009,16 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (!int4 && a.copy_mode == 2) return set_error(XFB200_E_INVALID, "decode: K/V rows must be 16-byte aligned");
   if (fp8 && a.copy_mode != 0) return set_error(XFB200_E_UNSUPPORTED, "decode: the heads of an fp8 cache row must be contiguous");
   a.box_tok = 16;
+  a.bias = p->bias, a.bias_dtype = p->bias_dtype, a.inv_scale = p->scale > 0.f ? 1.f / p->scale : 0.f;
+  a.bias_b = p->bias_stride_b, a.bias_kvh = p->bias_stride_kvh, a.bias_q = p->bias_stride_q, a.bias_m = p->bias_stride_m;
+  if (p->bias != nullptr) {
+    if (int4 || fp8) return set_error(XFB200_E_UNSUPPORTED, "decode: an additive bias needs a 16-bit cache");
+    if (p->seqlen_k != nullptr || p->block_tables != nullptr || p->kv_seqstart != nullptr)
+      return set_error(XFB200_E_UNSUPPORTED, "decode: an additive bias needs the plain cache layout (no sequence lengths, no page table)");
+    if (p->bias_dtype != XFB200_BF16 && p->bias_dtype != XFB200_F16 && p->bias_dtype != XFB200_F32)
+      return set_error(XFB200_E_INVALID, "decode: bad bias_dtype %d", p->bias_dtype);
+    if (!(p->scale > 0.f)) return set_error(XFB200_E_UNSUPPORTED, "decode: an additive bias needs a positive scale");
+  }
   a.window_size = p->window_size, a.window_span = window_span;
   if (p->window_size < 0) return set_error(XFB200_E_INVALID, "decode: window_size %d", p->window_size);
   if (p->window_size > 0 && p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT)
@@ -2075,10 +2120,14 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool bf16 = p->dtype == XFB200_BF16;
+  const bool extras = p->bias != nullptr || (p->window_size > 0 && p->mq > 1);  // 16-bit cache: the consumer variant that knows them
 #define XFB_DISPATCH(DD)                                                                                          \
   if (int4) {                                                                                                     \
     return bf16 ? launch_decode_mt<DD, kFmtInt4, true>(a, mt, head_blocks, st)                                    \
                 : launch_decode_mt<DD, kFmtInt4, false>(a, mt, head_blocks, st);                                  \
+  } else if (extras) {                                                                                            \
+    return bf16 ? launch_decode_mt<DD, kFmtPlainX, true>(a, mt, head_blocks, st)                                  \
+                : launch_decode_mt<DD, kFmtPlainX, false>(a, mt, head_blocks, st);                                \
   } else {                                                                                                        \
     return bf16 ? launch_decode_mt<DD, kFmtPlain, true>(a, mt, head_blocks, st)                                   \
                 : launch_decode_mt<DD, kFmtPlain, false>(a, mt, head_blocks, st);                                 \

@@ -120,6 +120,7 @@ class FwOp(AttentionFwOpBase):
         PagedBlockDiagonalCausalWithOffsetGappyKeysMask,
         BlockDiagonalCausalLocalAttentionPaddedKeysMask,
         PagedBlockDiagonalCausalLocalPaddedKeysMask,
+        torch.Tensor,
     )
     SUPPORTS_DROPOUT = False
     SUPPORTS_CUSTOM_SCALE = True
@@ -207,7 +208,22 @@ class FwOp(AttentionFwOpBase):
         if d.output_dtype is not None and d.output_dtype not in _DTYPE_CODE:
             reasons.append(f"output_dtype={d.output_dtype}")
         if isinstance(bias, torch.Tensor):
-            reasons.append("additive tensor biases are not supported")
+            # the bias in the query layout: [B, G, H, Mq, Mkv]
+            want = (B, G, H, Mq, k.shape[1])
+            shape5 = tuple(bias.shape) if bias.ndim == 5 else (tuple(bias.shape[:1]) + (1,) + tuple(bias.shape[1:]) if bias.ndim == 4 else
+                                                                tuple(bias.shape[:1]) + (1, 1) + tuple(bias.shape[1:]) if bias.ndim == 3 else None)
+            if shape5 != want:
+                reasons.append(f"additive bias of shape {tuple(bias.shape)}: expected [B, (G,) H, Mq, Mkv] = {want}")
+            elif bias.stride(-1) != 1:
+                reasons.append("additive bias needs unit stride on its last axis")
+            if bias.dtype not in _DTYPE_CODE:
+                reasons.append(f"additive bias dtype {bias.dtype}")
+            if quantized or fp8:
+                reasons.append("additive biases need a 16-bit cache")
+            if d.scale is not None and not d.scale > 0:
+                reasons.append("additive biases need a positive scale")
+            if not broadcast and G > 1 and H > 1 and bias.ndim == 5 and bias.stride(1) != H * bias.stride(2):
+                reasons.append("additive bias: head axes (G, H) of non-broadcast K/V must flatten to one stride")
         return reasons
 
     # ------------------------------------------------------------------ split
@@ -321,6 +337,15 @@ class FwOp(AttentionFwOpBase):
                 p.batch, p.mq = B, Mq
                 p.seqlen_k = None
                 p.kv_padding = k.shape[1]
+                if isinstance(bias, torch.Tensor):
+                    b5 = bias if bias.ndim == 5 else bias.unsqueeze(1) if bias.ndim == 4 else bias.unsqueeze(1).unsqueeze(1)
+                    p.bias, p.bias_dtype = b5.data_ptr(), _DTYPE_CODE[b5.dtype]
+                    p.bias_stride_b, p.bias_stride_m = b5.stride(0), b5.stride(3)
+                    if broadcast:
+                        p.bias_stride_kvh, p.bias_stride_q = b5.stride(1), b5.stride(2)
+                    else:
+                        # one KV head per query head: (G, H) flattened
+                        p.bias_stride_kvh, p.bias_stride_q = (b5.stride(2) if H > 1 else b5.stride(1)), 0
             # token rows of the cache tensors: bounds the tiled copies, so that a bad page-table entry reads zeros
             p.kv_rows = B * k.shape[1]
             if _lib.debug_checks():
