@@ -218,7 +218,8 @@ typedef struct {
   /* Local attention (BlockDiagonalCausalLocalAttentionPaddedKeysMask,
    * PagedBlockDiagonalCausalLocalPaddedKeysMask, fmha/attn_bias.py:29,43): 0, or the number of keys a
    * query sees, the window_size keys that end at its own position (query i of the mq queries of a
-   * sequence stands at key kv_len - mq + i).  Needs the bottom-right causal mask. */
+   * sequence stands at key kv_len - mq + i).  Needs the bottom-right causal mask; over an int4 or fp8
+   * cache, mq == 1. */
   int32_t window_size;
   int32_t reserved;
   /* Additive bias (a plain tensor as attn_bias; the reference's split-K operator takes one,

@@ -348,6 +348,8 @@ def test_local_window(Mq, kv_heads, group, window, split_k, fmt):
     sequence with one query per sequence, i.e. the sequence starts later); the
     same keys behind a block table give the same bits."""
     require_cuda()
+    if Mq > 1 and fmt != "bf16":
+        pytest.skip("windows with several queries per sequence: 16-bit caches")
     dtype, D, B, max_t, page = torch.bfloat16, 128, 4, 1536, 64
     g = torch.Generator().manual_seed(window)
     lens = [max_t, Mq, 700, 99]

@@ -555,29 +555,22 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
   // per-query-row visibility limit: token t visible iff t < lim
-  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
-  int lim[NTQ][2], lo[NTQ][2];
-  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
-  int lo_max = 0;
+  // per-query-row visibility limit: token t visible iff t < lim (a window with several queries per sequence, which
+  // also has lower limits, is served by the 16-bit consumer only)
+  int lim[NTQ][2];
+  int lim_min = w.chunk_hi;  // below it nothing is masked for any row of this warp
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi, f = 0;
-      if (a.causal && row < R) {
-        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
-        l = min(l, own);
-        if (a.window_size > 0) f = max(own - a.window_size, 0);
-      }
-      lim[nt][e] = l, lo[nt][e] = f;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
       lim_min = min(lim_min, l);
-      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
@@ -634,7 +627,7 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
       const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
       float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
       float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
-      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;  // warp-uniform
+      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
       float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
       bool need = false;
 #pragma unroll
@@ -653,8 +646,8 @@ __device__ __forceinline__ void consume_int4(const DecodeArgs& a, const DecWarp&
         for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
           }
       }
 #pragma unroll
@@ -855,29 +848,22 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
   __syncwarp();
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
-  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
-  int lim[NTQ][2], lo[NTQ][2];
-  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
-  int lo_max = 0;
+  // per-query-row visibility limit: token t visible iff t < lim (a window with several queries per sequence, which
+  // also has lower limits, is served by the 16-bit consumer only)
+  int lim[NTQ][2];
+  int lim_min = w.chunk_hi;  // below it nothing is masked for any row of this warp
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi, f = 0;
-      if (a.causal && row < R) {
-        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
-        l = min(l, own);
-        if (a.window_size > 0) f = max(own - a.window_size, 0);
-      }
-      lim[nt][e] = l, lo[nt][e] = f;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
       lim_min = min(lim_min, l);
-      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][NG][2];
@@ -908,7 +894,7 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
       if (t_sub >= w.chunk_hi) continue;
       const uint32_t* k0 = kst + (usub * 16 + r) * rw;  // token r; token r + 8 is 8 rows on
       const uint32_t* v0 = vst + (usub * 16 + r) * rw;
-      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;
+      const bool all_visible = t_sub + 16 <= lim_min;
       const int t0 = t_sub + r, t1 = t_sub + r + 8;
       const bool in0 = t0 < w.chunk_hi, in1 = t1 < w.chunk_hi;  // tokens past the end were not copied
 
@@ -1018,8 +1004,8 @@ __device__ __forceinline__ void consume_int4_groups(const DecodeArgs& a, const D
           sc0[nt][e] *= qfac[nt][e];
           sc1[nt][e] *= qfac[nt][e];
           if (!all_visible) {
-            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
           }
           need |= fmaxf(sc0[nt][e], sc1[nt][e]) > m_run[nt][e] + kLazy;
         }
@@ -1220,29 +1206,22 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
   __syncwarp();
   if (lane == 0) mbar_arrive(w.q_done_bar);
 
-  // token t is visible to a row iff lo <= t < lim (lo > 0 only with a window and several queries per sequence)
-  int lim[NTQ][2], lo[NTQ][2];
-  int lim_min = w.chunk_hi;  // between lo_max and lim_min nothing is masked for any row of this warp
-  int lo_max = 0;
+  // per-query-row visibility limit: token t visible iff t < lim (a window with several queries per sequence, which
+  // also has lower limits, is served by the 16-bit consumer only)
+  int lim[NTQ][2];
+  int lim_min = w.chunk_hi;  // below it nothing is masked for any row of this warp
 #pragma unroll
   for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int row = w.row0 + nt * 8 + 2 * c + e;
-      int l = w.chunk_hi, f = 0;
-      if (a.causal && row < R) {
-        const int own = w.kv_len - a.mq + row / a.q_per_kv + 1;  // one past the row's own position
-        l = min(l, own);
-        if (a.window_size > 0) f = max(own - a.window_size, 0);
-      }
-      lim[nt][e] = l, lo[nt][e] = f;
+      int l = w.chunk_hi;
+      if (a.causal && row < R) l = min(l, w.kv_len - a.mq + row / a.q_per_kv + 1);
+      lim[nt][e] = l;
       lim_min = min(lim_min, l);
-      lo_max = max(lo_max, f);
     }
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 1));
   lim_min = min(lim_min, __shfl_xor_sync(0xffffffffu, lim_min, 2));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 1));
-  lo_max = max(lo_max, __shfl_xor_sync(0xffffffffu, lo_max, 2));
 
   float acc[MTV][NTQ][4];
   float m_run[NTQ][2], l_run[NTQ][2], corr[NTQ][2];
@@ -1306,7 +1285,7 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
       const float ksc1 = half_bits_to_float(kw1 & 0xFFFFu), ksh1 = half_bits_to_float(kw1 >> 16);
       float vsc0 = half_bits_to_float(vw0 & 0xFFFFu), vsh0 = half_bits_to_float(vw0 >> 16);
       float vsc1 = half_bits_to_float(vw1 & 0xFFFFu), vsh1 = half_bits_to_float(vw1 >> 16);
-      const bool all_visible = t_sub + 16 <= lim_min && t_sub >= lo_max;  // warp-uniform
+      const bool all_visible = t_sub + 16 <= lim_min;  // warp-uniform
       float sc0[NTQ][2], sc1[NTQ][2];                  // scores of tokens r / r+8, log2 domain
       bool need = false;
 #pragma unroll
@@ -1325,8 +1304,8 @@ __device__ __forceinline__ void consume_fp8(const DecodeArgs& a, const DecWarp& 
         for (int nt = 0; nt < NTQ; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            if (t0 >= lim[nt][e] || t0 < lo[nt][e]) sc0[nt][e] = -INFINITY;
-            if (t1 >= lim[nt][e] || t1 < lo[nt][e]) sc1[nt][e] = -INFINITY;
+            if (t0 >= lim[nt][e]) sc0[nt][e] = -INFINITY;
+            if (t1 >= lim[nt][e]) sc1[nt][e] = -INFINITY;
           }
       }
 #pragma unroll
@@ -2023,6 +2002,8 @@ extern "C" int xfb200_decode_forward(const xfb200_decode_params* p, void* stream
   if (p->window_size < 0) return set_error(XFB200_E_INVALID, "decode: window_size %d", p->window_size);
   if (p->window_size > 0 && p->mask_type != XFB200_MASK_CAUSAL_BOTTOM_RIGHT)
     return set_error(XFB200_E_UNSUPPORTED, "decode: a window needs the bottom-right causal mask");
+  if (p->window_size > 0 && p->mq != 1 && (int4 || fp8))
+    return set_error(XFB200_E_UNSUPPORTED, "decode: a window over a quantised cache needs one query per sequence");
   // a window moves the first key of a sequence like a gappy start does
   const bool gappy = p->kv_seqstart != nullptr || p->window_size > 0;
   if (gappy && p->block_tables == nullptr && p->kv_seqstart != nullptr && p->kv_rows <= 0)

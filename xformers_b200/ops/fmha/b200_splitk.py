@@ -189,6 +189,8 @@ class FwOp(AttentionFwOpBase):
             if B != 1:
                 reasons.append("padded/paged biases need batch 1")
             if isinstance(bias, _LOCAL_BIASES):
+                if mq != 1 and quantized:
+                    reasons.append("local attention over a quantised cache is supported for one query per sequence")
                 if fp8 and isinstance(bias, PagedBlockDiagonalPaddedKeysMask):
                     reasons.append("a paged fp8 cache cannot be read through a window")
         else:
