@@ -63,7 +63,7 @@ CPU_SAMPLE = dict(B=1, H=4)  # slice of CFG2 timed on the host
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one launch: constants taken from the ncu captures
 # summarised under profiles/ (a run of this script does not measure them): bytes for the B=1 prefill case (every batch element adds the same), and traffic per algorithmic
 # byte for the decode kernels (measured on 16 sequences; traffic grows with the tokens streamed).
-NCU_TRAFFIC = {"prefill": 142.10e6 + 14.86e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
+NCU_TRAFFIC = {"prefill": 546.44e6 + 114.17e6, "decode_bf16": (980.12e6 + 14.07e6) / 979.88e6, "decode_int4": (261.43e6 + 4.82e6) / 260.67e6,
                "decode_fp8": (505.73e6 + 12.46e6) / 505.51e6, "rope": (100.70e6 + 55.24e6) / 201.33e6}
 
 
@@ -469,8 +469,8 @@ def main():
         out_line["parity"] = parity_block(po[:1, :, hs], pl[:1, hs], ro, rl, f"batch 0, heads {hs}, all {M} rows (rank {rank})")
         del po, pl
         out_line["roofline"] = {"bound": "tensor", "achieved": tfs, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                                "frac": tfs / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill"] * (B / 1),
-                                "traffic_unit": "bytes per launch (constant from profiles/: ncu on the B=1 case, scaled by B)",
+                                "frac": tfs / peaks["bf16_tflops"], "traffic": NCU_TRAFFIC["prefill"] * (B / 4),
+                                "traffic_unit": "bytes per launch (constant from profiles/: ncu on the full-size B=4 launch, scaled by B)",
                                 "kernel": "prefill_sm100_persist_kernel<128, bf16>",
                                 "of": peaks["source"], "frac_of_nominal_2250": tfs / 2250.0, "device_status": status}
         out_line["sustained"] = {"value": s_tfs * world, "unit": UNIT, "steps": s_steps, "timed_region_s": s_ms * 1e-3, "ms_per_step": s_ms / s_steps,
