@@ -57,6 +57,13 @@ def _worker(rank, world, init_file, fail_rank, result_file, zigzag=False):
                 causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge, exchange="all_gather",
             )
             assert (out - out_g).abs().max() < 1e-5 and (lse - lse_g).abs().max() < 1e-5
+            # query stripes, plain and as mirrored row blocks: the same rows end up in the same places
+            for extra in (dict(stripes=3), dict(stripes=3, mirror_stripes=True), dict(stripes=5, mirror_stripes=True)):
+                out_s, lse_s = sharded_kv_attention_forward(
+                    q, [k[:, a:b] for a, b in spans], [v[:, a:b] for a, b in spans], kv_offset=[a for a, _ in spans],
+                    causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge, **extra,
+                )
+                assert (out - out_s).abs().max() < 1e-5 and (lse - lse_s).abs().max() < 1e-5, extra
         else:
             out, lse = sharded_kv_attention_forward(
                 q, k[:, lo:hi], v[:, lo:hi], kv_offset=lo, causal=True, partial_fn=_cpu_partial, merge_fn=_cpu_merge

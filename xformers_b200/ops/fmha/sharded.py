@@ -209,7 +209,8 @@ def sharded_kv_attention_forward(
         return res
 
     use_a2a = exchange == "all_to_all" and mq % world == 0
-    n_stripes = max(1, int(stripes)) if (use_a2a and on_gpu) else 1
+    # (without CUDA streams the stripes simply run one after the other: the bookkeeping is the same)
+    n_stripes = max(1, int(stripes)) if use_a2a else 1
     while n_stripes > 1 and (mq % n_stripes or (mq // n_stripes) % world):
         n_stripes -= 1
     margin = 0
