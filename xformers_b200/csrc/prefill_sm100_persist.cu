@@ -2,11 +2,13 @@
 //
 // A work item is a block of 256 query rows of one (sequence, query head): two
 // 128-row query tiles that share every K/V tile TMA brings in.  Items are
-// numbered heaviest first (the last row block of every head, then the one
-// before, ...) and handed out by one atomic counter, so the SMs stay evenly
-// loaded whatever the sequence lengths are, and everything a CTA sets up --
-// tensor memory, barriers, tensor-map prefetch -- is paid once per SM instead
-// of once per block of rows.  The roles of the 16 warps:
+// handed out by one atomic counter, heaviest first (the last row block of every
+// head, then the one before, ...) inside groups of heads whose keys and values
+// fit the L2 together, so the SMs stay evenly loaded whatever the sequence
+// lengths are, a K/V tile comes from DRAM once and from the L2 for the other row
+// blocks of its head, and everything a CTA sets up -- tensor memory, barriers,
+// tensor-map prefetch -- is paid once per SM instead of once per block of rows.
+// The roles of the 16 warps:
 //
 //   warps 0-3    softmax of query tile 0   (thread <-> row <-> TMEM lane)
 //   warps 4-7    softmax of query tile 1
@@ -46,7 +48,11 @@
 // scheduler: every vote, branch or wait it executes is a bubble nobody fills, so
 // the step has no loop and no per-chunk test.  On diagonal and ragged tiles a
 // small loop first writes -inf over the hidden scores in tensor memory; the step
-// itself is one piece of code for every tile, which the instruction cache likes.  Measured
+// itself is one piece of code for every tile, which the instruction cache likes.
+// An additive bias is folded into the scores the same way (bias / scale added in
+// tensor memory).  When the first half of P (keys 64-127) is stored the softmax
+// arrives on a barrier of its own and the MMA warp issues that half of PV while
+// the other half is still being computed.  Measured
 // alternatives on the causal 4k case: one pass with a stale reference, a vote per
 // chunk and a fix-up path (10 % slower: the votes and branches); the whole row in
 // registers as in the one-CTA-per-block kernel; two threads per row; part of the
