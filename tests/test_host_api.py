@@ -180,6 +180,34 @@ def test_not_supported_reasons_strings():
     assert any("this is a prefill" in s for s in r)
 
 
+def test_tensor_bias_and_window_rules_of_the_operators():
+    """Which operator takes an additive tensor bias or a window, judged from the records alone (no GPU)."""
+    from xformers_b200.ops.fmha import attn_bias as ab
+
+    only_device = lambda reasons: [r for r in reasons if "device=" not in r]
+    q = torch.randn(2, 4, 2, 128, dtype=torch.bfloat16)
+    k = torch.randn(2, 40, 2, 128, dtype=torch.bfloat16)
+    bias = torch.randn(2, 2, 4, 40, dtype=torch.bfloat16)
+    # prefill: the automatic choice, the persistent tcgen05 kernel and the mma.sync kernel take it; the other tcgen05 kernel does not
+    for op in (fmha.b200.FwOp, fmha.b200.FwOp_Tcgen05_Persistent, fmha.b200.FwOp_Generic):
+        assert not only_device(op.not_supported_reasons(fmha.Inputs(q, k, k, bias))), op.NAME
+    assert any("additive biases" in r for r in fmha.b200.FwOp_Tcgen05_M256.not_supported_reasons(fmha.Inputs(q, k, k, bias)))
+    # decode: 16-bit caches only, shape and stride rules
+    S = fmha.b200_splitk.FwOp
+    assert not only_device(S.not_supported_reasons(fmha.Inputs(q, k, k, bias)))
+    assert any("expected [B, (G,) H, Mq, Mkv]" in r for r in S.not_supported_reasons(fmha.Inputs(q, k, k, bias[..., :39])))
+    assert any("unit stride" in r for r in S.not_supported_reasons(fmha.Inputs(q, k, k, torch.randn(2, 2, 4, 80, dtype=torch.bfloat16)[..., ::2])))
+    ki = torch.zeros(2, 40, 2, 17, dtype=torch.int32)
+    assert any("16-bit cache" in r for r in S.not_supported_reasons(fmha.Inputs(q, ki, ki, bias)))
+    # windows with several queries per sequence: the decode operator on 16-bit caches, not on quantised ones
+    q1 = torch.randn(1, 2 * 3, 2, 128, dtype=torch.bfloat16)
+    k1 = torch.randn(1, 2 * 64, 2, 128, dtype=torch.bfloat16)
+    local = ab.BlockDiagonalCausalLocalAttentionPaddedKeysMask.from_seqlens_local([3, 3], 64, [10, 20], 4)
+    assert not only_device(S.not_supported_reasons(fmha.Inputs(q1, k1, k1, local)))
+    k1i = torch.zeros(1, 2 * 64, 2, 17, dtype=torch.int32)
+    assert any("one query per sequence" in r for r in S.not_supported_reasons(fmha.Inputs(q1, k1i, k1i, local)))
+
+
 def _first(q, kv):
     return fmha._dispatch_fw_priority_list(fmha.Inputs(q, kv, kv), False)[0]
 
